@@ -1,0 +1,245 @@
+"""CPU oracle for the batched decode step -- TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference arm may import this module.
+The product (qwental_b200) never imports it and has no CPU fallback.
+
+Two layers:
+  * ctypes bindings of oracle/_build/libqw_oracle.so (oracle/qw_oracle.c): bit-exact block decode,
+    canonical-order fp32 matvec / router, FP64 matvec, top-k;
+  * numpy FP64 layer references restated from the reference's Python checkers and bench CPU checks:
+      MoE layer        tools/moe_ref.py:60,72-82 and bench/moe_decode.c:133-177
+      decode attention bench/qsa.c:181-200 + output gate kernels/qsa_dec.metal:643-644
+      GDN step         bench/gdn_decode.c:74-85 and tools/dn_ref.py:63-80 (norms, decay, gated RMSNorm,
+                       fp16 rounding points)
+Parity pin: see tests/test_oracle_pins.py (gguf.quants 0.19.0 on golden blocks; reference src/ggml_dq.c
+compiled into oracle/_ref for Q8_0).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "_build", "libqw_oracle.so")
+REF_LIB = os.path.join(HERE, "_ref", "libggml_dq_ref.so")
+REF_DQCPU = os.path.join(HERE, "_ref", "dqcpu")
+
+IQ3_S, Q8_0 = 21, 8
+_u8p, _u16p, _f32p, _f64p, _i32p = (C.POINTER(t) for t in (C.c_uint8, C.c_uint16, C.c_float, C.c_double, C.c_int32))
+
+
+def build(force: bool = False) -> None:
+    """Compile the oracle (and oracle/_ref when the reference tree is present)."""
+    if force or not os.path.exists(LIB):
+        subprocess.run(["make", "-C", HERE], check=True, capture_output=True)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB):
+            build()
+        _lib = C.CDLL(LIB)
+        _lib.orc_row_bytes.restype = C.c_long
+    return _lib
+
+
+def _p(a: np.ndarray, t):
+    return a.ctypes.data_as(t)
+
+
+def row_bytes(qtype: int, K: int) -> int:
+    return {IQ3_S: K // 256 * 110, Q8_0: K // 32 * 34}[qtype]
+
+
+def dq_rows(qtype: int, W: np.ndarray, K: int) -> np.ndarray:
+    """Decode rows of ggml blocks (uint8 [N][row_bytes]) to fp32 [N][K], bit-exact."""
+    W = np.ascontiguousarray(W, dtype=np.uint8).reshape(-1, row_bytes(qtype, K))
+    out = np.empty((W.shape[0], K), np.float32)
+    rc = lib().orc_dq_rows(qtype, _p(W, _u8p), W.shape[0], K, _p(out, _f32p))
+    assert rc == 0
+    return out
+
+
+def qmv_canon(qtype: int, W: np.ndarray, K: int, x16: np.ndarray) -> np.ndarray:
+    """Canonical-order fp32 matvec: x16 fp16 [B][K] -> fp32 [B][N] (bit-exact target of the FMA kernels)."""
+    W = np.ascontiguousarray(W, dtype=np.uint8).reshape(-1, row_bytes(qtype, K))
+    x16 = np.ascontiguousarray(x16, dtype=np.float16).reshape(-1, K)
+    N, B = W.shape[0], x16.shape[0]
+    y = np.empty((B, N), np.float32)
+    rc = lib().orc_qmv_canon(qtype, _p(W, _u8p), N, K, _p(x16.view(np.uint16), _u16p), B, K, _p(y, _f32p), N)
+    assert rc == 0
+    return y
+
+
+def qmv_f64(qtype: int, W: np.ndarray, K: int, x16: np.ndarray) -> np.ndarray:
+    W = np.ascontiguousarray(W, dtype=np.uint8).reshape(-1, row_bytes(qtype, K))
+    x16 = np.ascontiguousarray(x16, dtype=np.float16).reshape(-1, K)
+    N, B = W.shape[0], x16.shape[0]
+    y = np.empty((B, N), np.float64)
+    rc = lib().orc_qmv_f64(qtype, _p(W, _u8p), N, K, _p(x16.view(np.uint16), _u16p), B, K, _p(y, _f64p), N)
+    assert rc == 0
+    return y
+
+
+def qmv_cpu(qtype: int, W: np.ndarray, K: int, xf: np.ndarray, nthreads: int = 0):
+    """The timed CPU baseline: decode each row to fp32, fp32 dot per token.  Returns (y, threads used)."""
+    W = np.ascontiguousarray(W, dtype=np.uint8).reshape(-1, row_bytes(qtype, K))
+    xf = np.ascontiguousarray(xf, dtype=np.float32).reshape(-1, K)
+    N, B = W.shape[0], xf.shape[0]
+    y = np.empty((B, N), np.float32)
+    used = lib().orc_qmv_cpu(qtype, _p(W, _u8p), N, K, _p(xf, _f32p), B, _p(y, _f32p), nthreads)
+    assert used > 0
+    return y, used
+
+
+def router_canon(Wr16: np.ndarray, x16: np.ndarray) -> np.ndarray:
+    """fp16 router rows [E][D] x fp16 tokens [B][D] -> fp32 logits [B][E] in the canonical order."""
+    Wr16 = np.ascontiguousarray(Wr16, dtype=np.float16)
+    x16 = np.ascontiguousarray(x16, dtype=np.float16)
+    E, D = Wr16.shape
+    B = x16.shape[0]
+    lg = np.empty((B, E), np.float32)
+    lib().orc_router_canon(_p(Wr16.view(np.uint16), _u16p), E, D, _p(x16.view(np.uint16), _u16p), B, _p(lg, _f32p), E)
+    return lg
+
+
+def topk(logits: np.ndarray, k: int):
+    """Per token: ids (ties -> lowest id) and softmax weights over the picked logits."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    B, E = logits.shape
+    ids = np.empty((B, k), np.int32)
+    w = np.empty((B, k), np.float32)
+    for t in range(B):
+        lib().orc_topk(_p(logits[t], _f32p), E, k, _p(ids[t], _i32p), _p(w[t], _f32p))
+    return ids, w
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+# ----------------------------------------------------------------------------------------------- reference build
+def ref_dq_q8_0_rows(W: np.ndarray, K: int) -> np.ndarray:
+    """Q8_0 rows decoded by the reference's own src/ggml_dq.c (qw_ggml_dq_row), compiled into oracle/_ref."""
+    r = C.CDLL(REF_LIB)
+    r.qw_ggml_dq_row.restype = C.c_bool
+    W = np.ascontiguousarray(W, dtype=np.uint8).reshape(-1, row_bytes(Q8_0, K))
+    out = np.empty((W.shape[0], K), np.float32)
+    for i in range(W.shape[0]):
+        ok = r.qw_ggml_dq_row(8, _p(W[i], _u8p), _p(out[i], _f32p), K)
+        assert ok
+    return out
+
+
+# ----------------------------------------------------------------------------------------------- FP64 layer references
+def silu(v):
+    return v / (1.0 + np.exp(-v))
+
+
+def sigmoid(v):
+    return 1.0 / (1.0 + np.exp(-v))
+
+
+def h16(a):
+    """Round through fp16 (the reference's rounding points, tools/dn_ref.py:58)."""
+    return np.asarray(a).astype(np.float16).astype(np.float64)
+
+
+def moe_ref(x16, Wr16, wsg16, gate, up, down, sh_gate, sh_up, sh_down, D, I, topk_n=10, ids=None):
+    """FP64 MoE layer (tools/moe_ref.py:60,72-82).  gate/up: raw IQ3_S [E][I][rb(D)], down: [E][D][rb(I)];
+    shared expert the same shapes without the E axis.  `ids` (optional [B][topk]) overrides the FP64
+    selection so the output can be compared for the experts a device actually chose.
+    Returns (out [B][D] float64, ids64 [B][topk], gap [B] = 10th minus 11th FP64 logit)."""
+    x = np.asarray(x16, np.float16).astype(np.float64)
+    Wr = np.asarray(Wr16, np.float16).astype(np.float64)
+    B = x.shape[0]
+    lg = x @ Wr.T
+    ids64 = np.argsort(-lg, axis=1, kind="stable")[:, :topk_n]
+    srt = -np.sort(-lg, axis=1)
+    gap = srt[:, topk_n - 1] - srt[:, topk_n]
+    use = ids64 if ids is None else np.asarray(ids)
+    SG, SU, SD = (dq_rows(IQ3_S, sh_gate, D).astype(np.float64), dq_rows(IQ3_S, sh_up, D).astype(np.float64),
+                  dq_rows(IQ3_S, sh_down, I).astype(np.float64))
+    out = np.zeros((B, D))
+    cache = {}
+    for t in range(B):
+        l = lg[t, use[t]]
+        w = np.exp(l - l.max())
+        w /= w.sum()
+        for e, we in zip(use[t], w):
+            e = int(e)
+            if e not in cache:
+                cache[e] = (dq_rows(IQ3_S, gate[e], D).astype(np.float64), dq_rows(IQ3_S, up[e], D).astype(np.float64),
+                            dq_rows(IQ3_S, down[e], I).astype(np.float64))
+            G, U, Dn = cache[e]
+            out[t] += we * (Dn @ (silu(G @ x[t]) * (U @ x[t])))
+        sgl = float(np.asarray(wsg16, np.float16).astype(np.float64) @ x[t])
+        out[t] += sigmoid(sgl) * (SD @ (silu(SG @ x[t]) * (SU @ x[t])))
+    return out, ids64, gap
+
+
+def attn_ref(q16, K16, V16, gate16):
+    """FP64 decode attention of one slot (bench/qsa.c:181-200) with the output gate of
+    kernels/qsa_dec.metal:643-644.  q16 [QH][HD], K16/V16 [L][KVH][HD], gate16 [QH][HD] (pre-sigmoid).
+    Returns y [QH][HD] float64 = fp16(o) * sigmoid(gate)."""
+    q = np.asarray(q16, np.float16).astype(np.float64)
+    K = np.asarray(K16, np.float16).astype(np.float64)
+    V = np.asarray(V16, np.float16).astype(np.float64)
+    g = np.asarray(gate16, np.float16).astype(np.float64)
+    QH, HD = q.shape
+    KVH = K.shape[1]
+    y = np.empty((QH, HD))
+    for h in range(QH):
+        kv = h // (QH // KVH)
+        s = K[:, kv, :] @ q[h] / np.sqrt(HD)
+        p = np.exp(s - s.max())
+        o = (p / p.sum()) @ V[:, kv, :]
+        y[h] = h16(o) * sigmoid(g[h])
+    return y
+
+
+def rope_ref(v, pos, rd=64, theta=1e7):
+    """Partial RoPE on the first rd dims, pairs (i, i + rd/2) (kernels/qsa_dec.metal:40-60)."""
+    v = np.array(v, np.float64)
+    i = np.arange(rd // 2)
+    f = theta ** (-2.0 * i / rd) * pos
+    c, s = np.cos(f), np.sin(f)
+    a, b = v[..., :rd // 2].copy(), v[..., rd // 2:rd].copy()
+    v[..., :rd // 2] = a * c - b * s
+    v[..., rd // 2:rd] = b * c + a * s
+    return v
+
+
+def rmsnorm_ref(x, w, eps=1e-6):
+    x = np.asarray(x, np.float64)
+    return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * np.asarray(w, np.float64)
+
+
+def gdn_step_ref(S, q16, k16, v16, la, beta, z16, nw, hk_of, eps=1e-6):
+    """FP64 Gated DeltaNet step of one slot (bench/gdn_decode.c:74-85, tools/dn_ref.py:63-80).
+    S [HV][DK][DV] (updated copy returned), q16/k16 [HK][DK] raw conv outputs (normalised here: q also
+    times DK^-1/2, both rounded to fp16 as dn_ref.py:63-64), v16 [HV][DV], la/beta [HV],
+    z16 [HV][DV], nw [DV].  Returns (S_new, o16 [HV][DV] (fp16-rounded), y [HV][DV] gated RMSNorm)."""
+    S = np.array(S, np.float64)
+    q = np.asarray(q16, np.float16).astype(np.float64)
+    k = np.asarray(k16, np.float16).astype(np.float64)
+    v = np.asarray(v16, np.float16).astype(np.float64)
+    DK = q.shape[-1]
+    qn = h16(q / np.sqrt((q * q).mean(-1, keepdims=True) + eps) / DK)
+    kn = h16(k / np.sqrt((k * k).mean(-1, keepdims=True) + eps) / np.sqrt(DK))
+    kk, qq = kn[hk_of], qn[hk_of]
+    S *= np.exp(np.asarray(la, np.float64))[:, None, None]
+    mem = np.einsum("hkd,hk->hd", S, kk)
+    d = np.asarray(beta, np.float64)[:, None] * (v - mem)
+    S += kk[:, :, None] * d[:, None, :]
+    o = h16(np.einsum("hkd,hk->hd", S, qq))
+    r = 1.0 / np.sqrt((o * o).mean(-1, keepdims=True) + eps)
+    y = o * r * np.asarray(nw, np.float64) * sigmoid(np.asarray(z16, np.float16).astype(np.float64))
+    return S, o, y
