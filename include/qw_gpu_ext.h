@@ -1,0 +1,44 @@
+/* qw_gpu_ext.h -- additions to qw_gpu.h that the reference's unified-memory device layer has no need for.
+ * None of these has a counterpart in src/gpu.h; a host that only uses qw_gpu.h still works, it just keeps
+ * every buffer in managed memory.
+ */
+#ifndef QW_GPU_EXT_H
+#define QW_GPU_EXT_H
+#include "qw_gpu.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Where a buffer lives.  SHARED = what qw_buf_new gives (managed, ptr valid on both sides).
+ * DEVICE = HBM only, ptr == NULL: per-slot KV pages, recurrent state, scratch, weights.
+ * HOSTIO = pinned host memory mapped into the device: small per-step inputs/outputs (token ids, sampled ids)
+ * that the host touches every step. */
+enum { QW_BUF_SHARED = 0, QW_BUF_DEVICE = 1, QW_BUF_HOSTIO = 2 };
+bool qw_buf_new_kind(qw_gpu *g, size_t size, int kind, qw_buf *out);
+
+/* Copies between host memory and any buffer, ordered after everything already submitted on the current
+ * stream; they return when the copy is complete.  false on a range or CUDA error. */
+bool qw_buf_upload(qw_gpu *g, const qw_buf *dst, size_t offset, const void *src, size_t len);
+bool qw_buf_download(qw_gpu *g, const qw_buf *src, size_t offset, void *dst, size_t len);
+bool qw_buf_zero(qw_gpu *g, const qw_buf *dst, size_t offset, size_t len);
+
+/* Device address of a buffer (for interop with other CUDA code in the same process). */
+void *qw_buf_device_ptr(const qw_buf *b);
+/* cudaStream_t of stream s (0 or 1), as an opaque pointer. */
+void *qw_gpu_stream_handle(qw_gpu *g, int s);
+/* Message of the most recent failure on this device ("" if none). */
+const char *qw_gpu_last_error(const qw_gpu *g);
+/* Number of kernel launches issued by batches since qw_gpu_open (graph replays count their nodes). */
+unsigned long long qw_gpu_launch_count(const qw_gpu *g);
+/* Replay identical batches as CUDA graphs (default off; QW_GRAPH=1 in the environment turns it on). */
+void qw_gpu_set_graphs(qw_gpu *g, bool on);
+
+/* Precompiled kernel families that qw_gpu_compile can register. */
+int qw_gpu_family_count(void);
+const char *qw_gpu_family_name(int i);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

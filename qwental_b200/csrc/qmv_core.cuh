@@ -1,0 +1,122 @@
+// Shared core of the tensor-core quantized matvec kernels (dense qmv_mma, MoE gate/up and down).
+//
+// Work is cut into "units": 256 consecutive K values of 16 weight rows (one IQ3_S super-block per row, or eight
+// Q8_0 blocks per row).  A warp owns a unit and walks its eight 32-value sub-blocks.  For each sub-block it
+// builds the m16n8k16 A fragments straight from the raw block bytes in shared memory -- the weights' integer
+// part (codebook value x sign for IQ3_S, the int8 for Q8_0) is exact in fp16/bf16 -- runs two MMAs per
+// 8-token column tile against the activations, and applies the row's sub-block scale d*(1+2*scale) to the
+// fp32 partial sums.  The dequantised weights never exist in memory.
+//
+// K is permuted inside each MMA so that a thread's four A values per MMA are one codebook word: thread
+// (g = lane/4, t = lane%4) decodes weights 8t..8t+7 of the sub-block for rows g and g+8; k-slots
+// (2t, 2t+1, 2t+8, 2t+9) of MMA 0 carry weights 8t..8t+3 and of MMA 1 weights 8t+4..8t+7; the B fragment of
+// column g is the matching 16 bytes x[8t..8t+7].
+//
+// Every output column is a function of that column's activations only, with a fixed instruction sequence, so a
+// token's result does not depend on how many other tokens are in the batch or which column it sits in.
+#pragma once
+#include "common.cuh"
+
+namespace qw {
+
+// IQ3_S codebook in shared memory as 4 fp16 (or bf16) values per entry; REP interleaved copies so that the 16
+// lanes of a half-warp read different banks (REP = 16) or one compact copy (REP = 1).
+template <int REP>
+struct GridTab {
+    const uint2 *tab;
+    uint32_t c;
+    __device__ __forceinline__ uint2 get(uint32_t e) const { return tab[e * REP + c]; }
+};
+
+// Decode this thread's 8 weights of sub-block ib of the IQ3_S super-block at blk (kernels/moe_iq.metal:102-118:
+// qs @2, qh @66, signs @74, scales @106).  w[0..3] = packed pairs (w0,w1) (w2,w3) (w4,w5) (w6,w7) as signed
+// integer-valued halves.  Returns the 4-bit scale field.
+template <int REP>
+__device__ __forceinline__ uint32_t iq3s_sub(const uint8_t *blk, int ib, int t, const GridTab<REP> &gt, uint32_t (&w)[4]) {
+    const uint32_t qs = ldu16(blk + 2 + 8 * ib + 2 * t);
+    const uint32_t qh = blk[66 + ib];
+    const uint32_t sg = blk[74 + 4 * ib + t];
+    const uint32_t sc = (blk[106 + (ib >> 1)] >> (4 * (ib & 1))) & 15;
+    const uint32_t i0 = (qs & 255) | ((qh << (8 - 2 * t)) & 256);
+    const uint32_t i1 = (qs >> 8) | ((qh << (7 - 2 * t)) & 256);
+    const uint2 g0 = gt.get(i0), g1 = gt.get(i1);
+    // sign bit 2j -> bit 15, sign bit 2j+1 -> bit 31 of pair j: one multiply spreads both, no carries
+    w[0] = g0.x ^ ((sg * 0x40008000u) & 0x80008000u);
+    w[1] = g0.y ^ ((sg * 0x10002000u) & 0x80008000u);
+    w[2] = g1.x ^ ((sg * 0x04000800u) & 0x80008000u);
+    w[3] = g1.y ^ ((sg * 0x01000200u) & 0x80008000u);
+    return sc;
+}
+
+// Decode this thread's 8 int8 weights of the Q8_0 block at blk (src/ggml_dq.c:34-37: d @0, qs[32] @2) to
+// integer-valued fp16 pairs: (q ^ 0x80) | 0x6400 is the half 1024 + (q + 128); subtracting 1152 is exact.
+__device__ __forceinline__ void q8_sub(const uint8_t *blk, int t, uint32_t (&w)[4]) {
+    const uint8_t *q = blk + 2 + 8 * t;
+    const uint32_t lo = (ldu16(q) | ((uint32_t)ldu16(q + 2) << 16)) ^ 0x80808080u;
+    const uint32_t hi = (ldu16(q + 4) | ((uint32_t)ldu16(q + 6) << 16)) ^ 0x80808080u;
+    const uint32_t bias = 0x64806480u;
+    const __half2 b2 = *(const __half2 *)&bias;
+    uint32_t v[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342), __byte_perm(hi, 0x64646464u, 0x4140),
+                     __byte_perm(hi, 0x64646464u, 0x4342)};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half2 r = __hsub2(*(const __half2 *)&v[j], b2);
+        w[j] = *(const uint32_t *)&r;
+    }
+}
+
+// One unit (256 K values) for rows r0 (lanes' row g) and r1 (row g + 8): u0 / u1 point at the unit's bytes of
+// those two rows in shared memory.  xcol[nt] (xlo[nt] for the low bf16 plane) is the activation row of column
+// g + 8 nt in 16-byte units, nullptr for an absent column; k8 = index of the unit's first 16-byte chunk.
+template <int GF, int NT, int REP, bool BF16>
+__device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, const GridTab<REP> &gt, int t, const uint4 *const (&xcol)[NT],
+                                         const uint4 *const (&xlo)[NT], int k8, float (&acc)[NT][4]) {
+    float d0, d1;
+    if (GF == 21) {
+        d0 = h2f(ldu16(u0));
+        d1 = h2f(ldu16(u1));
+    }
+#pragma unroll 2
+    for (int ib = 0; ib < 8; ib++) {
+        uint32_t wa[4], wb[4];
+        float dba, dbb;
+        if (GF == 21) {
+            const uint32_t sa = iq3s_sub<REP>(u0, ib, t, gt, wa);
+            const uint32_t sb = iq3s_sub<REP>(u1, ib, t, gt, wb);
+            dba = __fmul_rn(d0, (float)(1 + 2 * (int)sa));
+            dbb = __fmul_rn(d1, (float)(1 + 2 * (int)sb));
+        } else {
+            q8_sub(u0 + 34 * ib, t, wa);
+            q8_sub(u1 + 34 * ib, t, wb);
+            dba = h2f(ldu16(u0 + 34 * ib));
+            dbb = h2f(ldu16(u1 + 34 * ib));
+        }
+        const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+        const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+        const int kk = k8 + 4 * ib + t;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            if (xcol[nt] == nullptr) continue;
+            const uint4 xv = __ldg(xcol[nt] + kk);
+            float p[4] = {0.f, 0.f, 0.f, 0.f};
+            if (BF16) {
+                const uint4 xl = __ldg(xlo[nt] + kk);
+                mma_bf16(p, a0, xv.x, xv.y, p);
+                mma_bf16(p, a1, xv.z, xv.w, p);
+                mma_bf16(p, a0, xl.x, xl.y, p);
+                mma_bf16(p, a1, xl.z, xl.w, p);
+            } else {
+                mma_f16(p, a0, xv.x, xv.y, p);
+                mma_f16(p, a1, xv.z, xv.w, p);
+            }
+            acc[nt][0] = fmaf(dba, p[0], acc[nt][0]);
+            acc[nt][1] = fmaf(dba, p[1], acc[nt][1]);
+            acc[nt][2] = fmaf(dbb, p[2], acc[nt][2]);
+            acc[nt][3] = fmaf(dbb, p[3], acc[nt][3]);
+        }
+    }
+}
+
+__host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }
+
+}  // namespace qw
