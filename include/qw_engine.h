@@ -1,0 +1,94 @@
+/* qw_engine.h -- the batched (continuous-batching) decode step as a C ABI: the "par" part of the reference's
+ * engine interface (src/engine.h:77-127 in hy-ong/qwental), built only on the device interface of qw_gpu.h.
+ *
+ * The reference's qw_engine_par_step (src/engine.c:8795) splits more than 8 slots into groups that each re-read
+ * all weights; here one step advances up to QW_PAR_MAX slots with a single pass over the weights.
+ * Out of scope here (see the reference for them): prefill, speculative decoding, prefix cache, snapshots, the
+ * tokenizer and server.  Because prefill is out of scope a slot's context is created by qw_engine_par_seed.
+ */
+#ifndef QW_ENGINE_H
+#define QW_ENGINE_H
+#include "qw_gpu.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct qw_engine qw_engine;
+enum { QW_PAR_MAX = 64 }; /* src/engine.h:79 */
+
+/* Shape of the model (the reference fixes these in src/model.h:9-24 for its one model). */
+typedef struct {
+    int hidden;        /* D, 2048 */
+    int layers;        /* 48 */
+    int attn_every;    /* every attn_every-th layer is gated attention, the others Gated DeltaNet (4) */
+    int vocab;         /* 151936 */
+    int experts;       /* 512 */
+    int topk;          /* 10 */
+    int expert_inter;  /* 512 (routed and shared expert) */
+    int qh, kvh, hd;   /* 16, 2, 256 */
+    int hk, hv;        /* GDN key / value heads 16, 32 (head dims 128) */
+    int max_slots;     /* conversation slots to keep state for (<= QW_PAR_MAX) */
+    int max_ctx;       /* longest context per slot, tokens */
+    int kv_pages;      /* pages of 256 tokens in the KV pool (0: max_slots * max_ctx / 256) */
+    int ep_rank, ep_size; /* expert-parallel slice: this process holds experts [rank*E/size, (rank+1)*E/size) */
+    int fma;           /* 1: dense matvecs use the fp32 FMA kernels in the oracle's order (qmv_gg); 0: tensor cores */
+    unsigned long long seed; /* master seed of the synthetic weights: per-tensor seed = hash(layer, name) */
+} qw_model_cfg;
+
+/* Defaults = the Qwen3-Next-80B-A3B shape of the benchmark. */
+void qw_model_cfg_default(qw_model_cfg *c);
+
+/* Opens a model with seeded random-init weights generated on the device (no checkpoint is read; role of
+ * qw_engine_open, src/engine.c:978-1211, minus the loaders).  NULL on failure (message: qw_engine_error(NULL)). */
+qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg);
+void qw_engine_close(qw_engine *e);
+const char *qw_engine_error(const qw_engine *e);
+qw_gpu *qw_engine_gpu(qw_engine *e);                 /* src/engine.h:66 */
+
+int qw_engine_par_slots(qw_engine *e);               /* src/engine.h:78 */
+/* src/engine.h:80: a slot whose bit in `busy` is clear, preferring never-used ones, else the least recently
+ * used; -1 if none.  (The prompt is not used for prefix matching: the prefix cache is out of scope.) */
+int qw_engine_par_pick(qw_engine *e, const int32_t *prompt, int np, unsigned long long busy);
+/* Stands in for qw_engine_par_prefill (src/engine.h:81): gives slot sid a context of ctx_len tokens whose KV
+ * pages, GDN state and conv state are seeded synthetic values (K, V ~ N(0,1); S ~ N(0, 0.01)).  0 or -1. */
+int qw_engine_par_seed(qw_engine *e, int sid, int ctx_len, unsigned long long seed);
+/* src/engine.h:91.  One decode step for B slots (sids distinct, 1 <= B <= QW_PAR_MAX): returns [B][vocab] fp32
+ * logits in host-visible memory, valid until the next step; NULL on failure.  *gpu_ms = device time. */
+const float *qw_engine_par_step(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms);
+/* The same step with the arg-max fused on the device (ties -> lowest id, as src/engine.c:6144-6148):
+ * returns B token ids in host-visible memory; logits are not copied to the host. */
+const int32_t *qw_engine_par_step_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms);
+/* nsteps greedy steps back to back with no host round trip between them (each step's ids feed the next);
+ * out_ids [nsteps][B].  Returns nsteps or -1. */
+int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, int nsteps, int32_t *out_ids, double *gpu_ms);
+void qw_engine_par_finish(qw_engine *e, int sid, const int32_t *gen, int ngen); /* src/engine.h:92: frees the slot */
+double qw_engine_par_cost(qw_engine *e, int B);      /* src/engine.h:95: EMA of the wall ms of a B-slot step, 0 = unknown */
+size_t qw_engine_par_mem(qw_engine *e);              /* src/engine.h:96: bytes of slot state in use */
+int qw_engine_par_pos(qw_engine *e, int sid);        /* tokens in slot sid's context, -1 if unused */
+
+/* Algorithmic bytes one step over these slots must move (weights of the distinct experts the last step chose,
+ * dense weights, KV of the contexts, GDN state read + write): the numerator of the HBM roofline. */
+typedef struct {
+    double moe, dense, lm_head, kv, gdn_state, other, total;
+    int unique_experts_sum; /* sum over layers of distinct experts chosen in the last step */
+    long long ctx_tokens;   /* sum of context lengths attended in the last step */
+} qw_step_bytes;
+void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *out);
+
+/* Debug taps for the parity tests (role of the reference's QW_MOE_TEST / QW_DN_TAP dumps, src/engine.c:7942-7999):
+ * copy a named internal buffer to the host; dst == NULL returns the size.  Last step: "h" fp32 [B][D],
+ * "x" fp16 [B][D], "logits" fp32 [B][V], "sel" (layer index: the MoE selection record).  Weights by layer index:
+ * "w_in", "w_out", "small", "router", "exg", "exu", "exd", "shg", "shu", "shd"; "emb", "lm_head", "final_norm".
+ * State: "sstate" / "cstate" / "pages" by slot, "kvpage" by page id.  Returns bytes copied, 0 on error. */
+size_t qw_engine_tap(qw_engine *e, const char *name, int index, void *dst, size_t cap);
+
+/* Expert-parallel plumbing (no counterpart in the reference, which is single-device): the communicator is
+ * created from a 128-byte NCCL unique id that rank 0 obtained from qw_ep_unique_id and shared with the others. */
+int qw_ep_unique_id(void *id128);
+int qw_engine_ep_init(qw_engine *e, const void *id128);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -14,7 +14,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 // where and returns, the host sees it at the batch's wait.
 enum : unsigned { ST_OK = 0, ST_MBAR_TIMEOUT = 0x100, ST_BAD_ARG = 0x200 };
 __device__ __forceinline__ void set_status(unsigned *status, unsigned code) {
-    if (status) atomicCAS(status, 0u, code);
+    if (status) *(volatile unsigned *)status = code;  // plain store: the word lives in host memory
 }
 
 // ---- mbarrier
@@ -36,11 +36,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: about a second at most, then false (the caller records ST_MBAR_TIMEOUT and leaves).
+// Bounded wait: polls for at most about two seconds of wall time (the global nanosecond timer), then gives up
+// with false; the caller records ST_MBAR_TIMEOUT and leaves.
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
-    for (unsigned i = 0; i < (1u << 22); i++)
+    for (int i = 0; i < 64; i++)
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    const uint64_t t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > 2000000000ull) return false;
+    }
 }
 
 // ---- 1-D bulk copy global -> shared, completion counted on an mbarrier.  dst, src 16-byte aligned,

@@ -1,0 +1,532 @@
+// MoE decode layer for up to 64 tokens (one per slot): router, top-k + grouping by expert, gathered SwiGLU
+// expert FFN (gate/up then down) with the shared expert as one more group, rank-ordered weighted combine.
+// Replaces the reference's moe_pre_gg / gg_select / moe_gu_gg / moe_dn_gg / moe_cmb_gg
+// (kernels/moe_gg.metal:118-189, 534-663; host src/engine.c:568-646).  What is kept from the reference:
+//   - router logits in fp32 with one fixed summation order (so the chosen experts are reproducible),
+//   - top-k by repeated arg-max, equal logits -> lowest expert id; weights = softmax over the picked logits
+//     with the exponentials summed in rank order; shared-expert gate = sigmoid of an extra router row,
+//   - every distinct expert's weights are read and decoded once per step and applied to each token that chose
+//     it; a token's arithmetic does not depend on which other tokens are in the batch,
+//   - H = silu(gate x) * (up x) is kept at better than fp16 precision between the two halves (here as a
+//     bf16 high + low pair, 16 mantissa bits; the reference keeps fp32, src/engine.c:157),
+//   - combine in rank order, then the shared expert, one rounding to fp16 (kernels/moe_gg.metal:655-663).
+// What is new: groups hold up to 64 tokens (the reference's gg_sel has 8-bit masks), the contraction runs on
+// tensor cores from raw IQ3_S blocks staged by bulk (TMA) copies, and experts can be restricted to a range
+// [e_lo, e_hi) for expert-parallel execution.
+#include "qmv_core.cuh"
+#include "qw_kern.h"
+
+using namespace qw;
+
+#define MOE_MAXB 64
+#define MOE_MAXK 16
+#define MOE_MAXE 1024
+
+// Result of the selection, read by the gate/up, down and combine kernels (role of struct gg_sel,
+// kernels/moe_gg.metal:110-116).  Groups are in expert-id order; a group's entries are in token order.
+struct moe_sel {
+    uint32_t U;                               // groups (distinct experts in [e_lo, e_hi) that were chosen)
+    uint32_t nb, topk, pad;
+    int32_t ids[MOE_MAXB][MOE_MAXK];          // chosen experts per token, rank order
+    float w[MOE_MAXB][MOE_MAXK + 1];          // routed weights, then the shared gate at [topk]
+    uint32_t ue[MOE_MAXE];                    // expert of group u
+    uint32_t off[MOE_MAXE + 1];               // entries of group u: ent[off[u] .. off[u+1])
+    uint16_t ent[MOE_MAXB * MOE_MAXK];        // token << 8 | rank
+};
+
+// ------------------------------------------------------------------------------------------------ router
+// logits [nb][E+1] fp32; row E is the shared-expert gate.  One warp per row, lane owns the 8-value chunks
+// lane, lane+32, ...: a single fma chain per lane, then the xor butterfly (bit-exact against the CPU oracle).
+// binds: 0 = Wr fp16 [E][D], 1 = Wsg fp16 [D], 2 = x fp16 [nb][D], 3 = logits, 14 = nb.  grid ceil((E+1)/8) x 256
+template <int D>
+__global__ void __launch_bounds__(256) moe_router_k(const __half *Wr, const __half *Wsg, const __half *x, float *logits, uint32_t E, uint32_t nb) {
+    constexpr int CH = D / 8 / 32;
+    const uint32_t r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r > E) return;
+    const uint4 *w = (const uint4 *)(r < E ? Wr + (size_t)r * D : Wsg);
+    uint4 wr[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) wr[c] = __ldg(w + lane + 32 * c);
+    for (uint32_t t = 0; t < nb; t++) {
+        const uint4 *xt = (const uint4 *)(x + (size_t)t * D);
+        float acc = 0.f;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+            const uint4 xv = __ldg(xt + lane + 32 * c);
+            const uint32_t a4[4] = {wr[c].x, wr[c].y, wr[c].z, wr[c].w}, b4[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 a = __half22float2(*(const __half2 *)&a4[j]), b = __half22float2(*(const __half2 *)&b4[j]);
+                acc = __fmaf_rn(a.x, b.x, acc);
+                acc = __fmaf_rn(a.y, b.y, acc);
+            }
+        }
+        const float v = warp_sum_canon(acc);
+        if (lane == 0) logits[(size_t)t * (E + 1) + r] = v;
+    }
+}
+
+static cudaError_t launch_moe_router(const QwLaunch &L) {
+    const uint32_t E = (uint32_t)L.def("E", 512), D = (uint32_t)L.def("D", 2048);
+    const uint32_t nb = L.bytes<uint32_t>(14);
+    QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && L.buf<void>(2) && L.buf<void>(3) && nb >= 1 && nb <= MOE_MAXB);
+    QW_CHECK_ARG(L.avail(0) >= (size_t)E * D * 2 && L.avail(1) >= (size_t)D * 2 && L.avail(2) >= (size_t)nb * D * 2 &&
+                 L.avail(3) >= (size_t)nb * (E + 1) * 4);
+    QW_CHECK_ARG(L.tx == 256 && L.gx == (E + 1 + 7) / 8);
+    if (D == 2048) moe_router_k<2048><<<L.gx, 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
+    else if (D == 256) moe_router_k<256><<<L.gx, 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
+    else return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_router, launch_moe_router, 256)
+
+// ------------------------------------------------------------------------------------------------ select + group
+// One block of 1024 threads.  binds: 0 = logits [nb][E+1], 1 = moe_sel, 2 = {nb, e_lo, e_hi}.
+struct sel_args {
+    uint32_t nb, e_lo, e_hi;
+};
+
+__global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
+    __shared__ uint32_t cnt[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];
+    __shared__ uint16_t sid[MOE_MAXB * MOE_MAXK];
+    __shared__ uint32_t wsum[2][32];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t PER = E / 32;
+    for (uint32_t e = tid; e < MOE_MAXE; e += 1024) cnt[e] = 0;
+    // 1. top-k per token (one warp per token; lane owns experts lane*PER .. lane*PER+PER-1)
+    for (uint32_t t = warp; t < a.nb; t += 32) {
+        const float *lg = logits + (size_t)t * (E + 1);
+        float v[32];
+#pragma unroll
+        for (uint32_t j = 0; j < 32; j++) v[j] = j < PER ? lg[lane * PER + j] : -INFINITY;
+        float pk = 0.f;
+        for (uint32_t k = 0; k < topk; k++) {
+            float b0 = v[0];
+            uint32_t j0 = 0;
+#pragma unroll
+            for (uint32_t j = 1; j < 32; j++)
+                if (j < PER && v[j] > b0) { b0 = v[j]; j0 = j; }
+            const float m = warp_max(b0);
+            const uint32_t Lw = __ffs(__ballot_sync(0xffffffffu, b0 == m)) - 1;  // equal values: lowest lane = lowest id
+            const uint32_t bj = __shfl_sync(0xffffffffu, j0, Lw);
+            if (lane == 0) {
+                ms->ids[t][k] = (int32_t)(Lw * PER + bj);
+                sid[t * MOE_MAXK + k] = (uint16_t)(Lw * PER + bj);
+            }
+            if (lane == k) pk = m;
+#pragma unroll
+            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == Lw && j == bj) ? -INFINITY : v[j];
+        }
+        const float mx = __shfl_sync(0xffffffffu, pk, 0), ex = expf(pk - mx);
+        float sm = 0.f;
+        for (uint32_t k = 0; k < topk; k++) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, ex, k));  // rank order
+        if (lane < topk) ms->w[t][lane] = ex / sm;
+        if (lane == topk) ms->w[t][topk] = 1.0f / (1.0f + expf(-lg[E]));
+    }
+    __syncthreads();
+    // 2. group by expert: count, number the non-empty experts of [e_lo, e_hi) in id order, fill in token order
+    for (uint32_t i = tid; i < a.nb * topk; i += 1024) {
+        const uint32_t e = sid[(i / topk) * MOE_MAXK + i % topk];
+        if (e >= a.e_lo && e < a.e_hi) atomicAdd(&cnt[e], 1u);
+    }
+    __syncthreads();
+    {   // exclusive scans over experts (thread e = expert e): entries and non-empty flags
+        const uint32_t c = tid < E ? cnt[tid] : 0, f = c ? 1u : 0u;
+        uint32_t sc = c, sf = f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t tc = __shfl_up_sync(0xffffffffu, sc, o), tf = __shfl_up_sync(0xffffffffu, sf, o);
+            if (lane >= (uint32_t)o) { sc += tc; sf += tf; }
+        }
+        if (lane == 31) { wsum[0][warp] = sc; wsum[1][warp] = sf; }
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t xc = wsum[0][lane], xf = wsum[1][lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t tc = __shfl_up_sync(0xffffffffu, xc, o), tf = __shfl_up_sync(0xffffffffu, xf, o);
+                if (lane >= (uint32_t)o) { xc += tc; xf += tf; }
+            }
+            wsum[0][lane] = xc;
+            wsum[1][lane] = xf;
+        }
+        __syncthreads();
+        const uint32_t bc = warp ? wsum[0][warp - 1] : 0, bf = warp ? wsum[1][warp - 1] : 0;
+        if (tid < MOE_MAXE) {
+            pos[tid] = bc + sc - c;   // first entry of expert tid
+            grp[tid] = bf + sf - f;   // group number of expert tid (if non-empty)
+        }
+        if (tid == 1023) {
+            ms->U = bf + sf;
+            ms->nb = a.nb;
+            ms->topk = topk;
+            ms->off[bf + sf] = bc + sc;
+        }
+    }
+    __syncthreads();
+    if (tid < E && cnt[tid]) {
+        const uint32_t u = grp[tid];
+        ms->ue[u] = tid;
+        ms->off[u] = pos[tid];
+        uint32_t o = pos[tid];
+        for (uint32_t i = 0; i < a.nb * topk; i++) {
+            const uint32_t t = i / topk, k = i % topk;
+            if (sid[t * MOE_MAXK + k] == tid) ms->ent[o++] = (uint16_t)((t << 8) | k);
+        }
+    }
+}
+
+static cudaError_t launch_moe_select(const QwLaunch &L) {
+    const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
+    sel_args a = L.bytes<sel_args>(2);
+    QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && L.has_bytes(2, 12));
+    QW_CHECK_ARG(E % 32 == 0 && E <= MOE_MAXE && topk >= 1 && topk < MOE_MAXK && topk <= E && a.nb >= 1 && a.nb <= MOE_MAXB);
+    QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * (E + 1) * 4 && L.avail(1) >= sizeof(moe_sel));
+    if (a.e_hi > E) a.e_hi = E;
+    moe_select_k<<<1, 1024, 0, L.stream>>>(L.buf<float>(0), L.buf<moe_sel>(1), E, topk, a);
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_select, launch_moe_select, 1024)
+
+// ------------------------------------------------------------------------------------------------ gate/up and down
+// Persistent blocks of 8 warps; item = (group u, row tile).  Group U (one past the routed groups) is the
+// shared expert with every token at rank topk.
+struct MoeP {
+    const uint8_t *Wa, *Wb;     // gate/up: routed gate and up [E][I][rb]; down: routed down [E][D][rb] in Wa
+    const uint8_t *Sa, *Sb;     // shared expert's matrices (same shapes without the E axis); nullptr: no shared expert
+    const __half *x;            // gate/up: tokens fp16 [nb][D]
+    uint16_t *Hhi, *Hlo;        // [nb][topk+1][I] bf16 planes
+    float *Pg;                  // down: [nb][topk+1][D]
+    const moe_sel *ms;
+    const QwTables *tab;
+    unsigned *status;
+    uint32_t D, I, rbD, rbI, tiles;
+    uint32_t ebase;             // id of the first expert stored in Wa / Wb (expert-parallel slice)
+};
+
+constexpr int MOE_STAGES = 3;
+constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
+
+// gate/up: tile = 16 rows of gate + the same 16 rows of up (28 KB at D = 2048); warps 0-3 take gate, 4-7 up,
+// each a quarter of the units.
+__global__ void __launch_bounds__(256, 1) moe_gu_k(const MoeP p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = (uint64_t *)smem;                    // [0..2] stages, [3] table
+    uint2 *tab = (uint2 *)(smem + 128);
+    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES); // [8 warps][32]
+    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 8 * 32 * 16;
+    const uint32_t half_bytes = 16 * p.rbD, tile_bytes = 2 * half_bytes;
+    const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mat = warp >> 2, ks = warp & 3;
+    const moe_sel *ms = p.ms;
+    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
+    const uint32_t groups = U + (p.Sa ? 1u : 0u), items = groups * p.tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < MOE_STAGES + 1; s++) mbar_init(&bars[s], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const uint32_t first = blockIdx.x, step = gridDim.x;
+    auto issue = [&](uint32_t j) {
+        const uint32_t item = first + j * step;
+        if (item >= items) return;
+        const uint32_t u = item / p.tiles, tile = item % p.tiles;
+        const int s = j % MOE_STAGES;
+        const uint8_t *ga, *ua;
+        if (u < U) {
+            const size_t o = ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * p.rbD;
+            ga = p.Wa + o;
+            ua = p.Wb + o;
+        } else {
+            const size_t o = (size_t)tile * 16 * p.rbD;
+            ga = p.Sa + o;
+            ua = p.Sb + o;
+        }
+        mbar_expect_tx(&bars[s], tile_bytes);
+        bulk_g2s(stage0 + (size_t)s * stage_stride, ga, half_bytes, &bars[s]);
+        bulk_g2s(stage0 + (size_t)s * stage_stride + half_bytes, ua, half_bytes, &bars[s]);
+    };
+    if (tid == 0) {
+        mbar_expect_tx(&bars[MOE_STAGES], MOE_TAB_BYTES);
+        bulk_g2s(tab, p.tab->grid_h4, MOE_TAB_BYTES, &bars[MOE_STAGES]);
+        for (uint32_t j = 0; j < MOE_STAGES - 1; j++) issue(j);
+    }
+    bool ok = mbar_wait(&bars[MOE_STAGES], 0);
+    const GridTab<16> gt{tab, (uint32_t)(lane & 15)};
+    const int units = p.D / 256;
+
+    for (uint32_t j = 0; ok; j++) {
+        const uint32_t item = first + j * step;
+        if (item >= items) break;
+        if (tid == 0) issue(j + MOE_STAGES - 1);
+        const int s = j % MOE_STAGES;
+        if (!mbar_wait(&bars[s], (j / MOE_STAGES) & 1)) {
+            ok = false;
+            break;
+        }
+        const uint32_t u = item / p.tiles, tile = item % p.tiles;
+        const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+        const uint8_t *rows = stage0 + (size_t)s * stage_stride + (size_t)mat * half_bytes;
+        for (uint32_t c0 = 0; c0 < cnt; c0 += 8) {
+            // this lane's column: entry c0 + g
+            uint32_t tok = 0, rank = 0;
+            const bool have = c0 + g < cnt;
+            if (have) {
+                if (u < U) {
+                    const uint32_t en = ms->ent[e0 + c0 + g];
+                    tok = en >> 8;
+                    rank = en & 255;
+                } else {
+                    tok = c0 + g;
+                    rank = topk;
+                }
+            }
+            const uint4 *xcol[1] = {have ? (const uint4 *)(p.x + (size_t)tok * p.D) : nullptr};
+            const uint4 *xlo[1] = {nullptr};
+            const uint32_t tile_on = tiles_on<1>(xcol);
+            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+            for (int un = ks; un < units; un += 4)
+                unit_mma<21, 1, 16, false>(rows + (size_t)g * p.rbD + (size_t)un * 110, rows + (size_t)(g + 8) * p.rbD + (size_t)un * 110, gt, t,
+                                           xcol, xlo, tile_on, un * 32, acc);
+            red[warp * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+            __syncthreads();
+            if (tid < 128) {
+                // element (row, col) of the 16 x 8 tile: gate and up sums over the 4 K-slices in slice order
+                const int jj = tid & 3, ln = tid >> 2;
+                float gs = 0.f, us = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < 4; k2++) {
+                    gs += ((const float *)&red[k2 * 32 + ln])[jj];
+                    us += ((const float *)&red[(4 + k2) * 32 + ln])[jj];
+                }
+                const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
+                if (c0 + col < cnt) {
+                    uint32_t tk, rk;
+                    if (u < U) {
+                        const uint32_t en = ms->ent[e0 + c0 + col];
+                        tk = en >> 8;
+                        rk = en & 255;
+                    } else {
+                        tk = c0 + col;
+                        rk = topk;
+                    }
+                    const float h = gs / (1.0f + expf(-gs)) * us;
+                    const __nv_bfloat16 hi = __float2bfloat16_rn(h);
+                    const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
+                    const size_t o = ((size_t)tk * (topk + 1) + rk) * p.I + row;
+                    p.Hhi[o] = __bfloat16_as_ushort(hi);
+                    p.Hlo[o] = __bfloat16_as_ushort(lo);
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 2);
+}
+
+// down: tile = 64 rows (4 m-tiles) of the [D][I] matrix; warp = (m-tile, K-slice of 2).  B operand = H planes.
+__global__ void __launch_bounds__(256, 1) moe_dn_k(const MoeP p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = (uint64_t *)smem;
+    uint2 *tab = (uint2 *)(smem + 128);
+    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES);
+    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 8 * 32 * 16;
+    const uint32_t tile_bytes = 64 * p.rbI;
+    const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int mt = warp >> 1, ks = warp & 1;
+    const moe_sel *ms = p.ms;
+    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
+    const uint32_t groups = U + (p.Sa ? 1u : 0u), items = groups * p.tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < MOE_STAGES + 1; s++) mbar_init(&bars[s], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const uint32_t first = blockIdx.x, step = gridDim.x;
+    auto issue = [&](uint32_t j) {
+        const uint32_t item = first + j * step;
+        if (item >= items) return;
+        const uint32_t u = item / p.tiles, tile = item % p.tiles;
+        const int s = j % MOE_STAGES;
+        const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * 64) * p.rbI : p.Sa + (size_t)tile * 64 * p.rbI;
+        mbar_expect_tx(&bars[s], tile_bytes);
+        bulk_g2s(stage0 + (size_t)s * stage_stride, src, tile_bytes, &bars[s]);
+    };
+    if (tid == 0) {
+        mbar_expect_tx(&bars[MOE_STAGES], MOE_TAB_BYTES);
+        bulk_g2s(tab, p.tab->grid_b4, MOE_TAB_BYTES, &bars[MOE_STAGES]);
+        for (uint32_t j = 0; j < MOE_STAGES - 1; j++) issue(j);
+    }
+    bool ok = mbar_wait(&bars[MOE_STAGES], 0);
+    const GridTab<16> gt{tab, (uint32_t)(lane & 15)};
+    const int units = p.I / 256;
+
+    for (uint32_t j = 0; ok; j++) {
+        const uint32_t item = first + j * step;
+        if (item >= items) break;
+        if (tid == 0) issue(j + MOE_STAGES - 1);
+        const int s = j % MOE_STAGES;
+        if (!mbar_wait(&bars[s], (j / MOE_STAGES) & 1)) {
+            ok = false;
+            break;
+        }
+        const uint32_t u = item / p.tiles, tile = item % p.tiles;
+        const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+        const uint8_t *rows = stage0 + (size_t)s * stage_stride + (size_t)(16 * mt) * p.rbI;
+        for (uint32_t c0 = 0; c0 < cnt; c0 += 8) {
+            uint32_t tok = 0, rank = 0;
+            const bool have = c0 + g < cnt;
+            if (have) {
+                if (u < U) {
+                    const uint32_t en = ms->ent[e0 + c0 + g];
+                    tok = en >> 8;
+                    rank = en & 255;
+                } else {
+                    tok = c0 + g;
+                    rank = topk;
+                }
+            }
+            const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
+            const uint4 *xcol[1] = {have ? (const uint4 *)(p.Hhi + ho) : nullptr};
+            const uint4 *xlo[1] = {have ? (const uint4 *)(p.Hlo + ho) : nullptr};
+            const uint32_t tile_on = tiles_on<1>(xcol);
+            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+            for (int un = ks; un < units; un += 2)
+                unit_mma<21, 1, 16, true>(rows + (size_t)g * p.rbI + (size_t)un * 110, rows + (size_t)(g + 8) * p.rbI + (size_t)un * 110, gt, t,
+                                          xcol, xlo, tile_on, un * 32, acc);
+            red[warp * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+            __syncthreads();
+            for (int e = tid; e < 4 * 128; e += 256) {
+                const int jj = e & 3, ln = (e >> 2) & 31, m = e >> 7;
+                float sum = ((const float *)&red[(2 * m) * 32 + ln])[jj];
+                if (units > 1) sum += ((const float *)&red[(2 * m + 1) * 32 + ln])[jj];
+                const uint32_t row = tile * 64 + m * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
+                if (c0 + col < cnt) {
+                    uint32_t tk, rk;
+                    if (u < U) {
+                        const uint32_t en = ms->ent[e0 + c0 + col];
+                        tk = en >> 8;
+                        rk = en & 255;
+                    } else {
+                        tk = c0 + col;
+                        rk = topk;
+                    }
+                    p.Pg[((size_t)tk * (topk + 1) + rk) * p.D + row] = sum;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 3);
+}
+
+// binds (gate/up): 0 = Wg, 1 = Wu, 2 = shared gate, 3 = shared up (used unless SHARED is defined 0), 4 = x, 5 = moe_sel,
+//                  6 = Hhi, 7 = Hlo.   (down): 0 = Wd, 2 = shared down, 5 = moe_sel, 6 = Hhi, 7 = Hlo, 9 = Pg.
+//                  both: 10 = id of the first expert held in the weight buffers (optional, default 0).
+// defines: E, D, I, TOPK, EL (experts held locally, default E).  The host's grid is ignored (persistent, one block per SM); block 256.
+static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &topk, bool down) {
+    E = (uint32_t)L.def("E", 512);
+    topk = (uint32_t)L.def("TOPK", 10);
+    p.D = (uint32_t)L.def("D", 2048);
+    p.I = (uint32_t)L.def("I", 512);
+    QW_CHECK_ARG(p.D % 256 == 0 && p.I % 256 == 0 && p.I % 16 == 0 && p.D % 64 == 0 && L.tx == 256);
+    p.rbD = p.D / 256 * 110;
+    p.rbI = p.I / 256 * 110;
+    QW_CHECK_ARG((16 * p.rbD) % 16 == 0 && (64 * p.rbI) % 16 == 0);
+    p.Wa = L.buf<uint8_t>(0);
+    p.Wb = L.buf<uint8_t>(1);
+    const bool shared = L.def("SHARED", 1) != 0;  // bind slots persist across dispatches: optional inputs are opted into by a define
+    p.Sa = shared ? L.buf<uint8_t>(2) : nullptr;
+    p.Sb = shared && !down ? L.buf<uint8_t>(3) : nullptr;
+    QW_CHECK_ARG(!shared || p.Sa);
+    p.x = L.buf<__half>(4);
+    p.ms = L.buf<moe_sel>(5);
+    p.Hhi = L.buf<uint16_t>(6);
+    p.Hlo = L.buf<uint16_t>(7);
+    p.Pg = L.buf<float>(9);
+    p.tab = (const QwTables *)L.tables;
+    p.status = L.status;
+    // experts held in the bound weight buffers: EL of them starting at id bytes(10) (default: all E from 0);
+    // moe_select must have been given the same range
+    const uint32_t EL = (uint32_t)L.def("EL", E);
+    p.ebase = L.has_bytes(10, 4) ? L.bytes<uint32_t>(10) : 0;
+    QW_CHECK_ARG(EL >= 1 && p.ebase + EL <= E);
+    const size_t wsz = (size_t)EL * p.I * p.rbD;  // == EL * D * rbI
+    QW_CHECK_ARG(p.Wa && p.ms && p.Hhi && p.Hlo && L.avail(0) >= wsz && L.avail(5) >= sizeof(moe_sel));
+    QW_CHECK_ARG(((uintptr_t)p.Wa & 15) == 0 && ((uintptr_t)p.Sa & 15) == 0 && ((uintptr_t)p.Hhi & 15) == 0 && ((uintptr_t)p.Hlo & 15) == 0);
+    const size_t hsz = (size_t)MOE_MAXB * (topk + 1) * p.I * 2;
+    QW_CHECK_ARG(L.avail(6) >= hsz && L.avail(7) >= hsz);
+    if (p.Sa) QW_CHECK_ARG(L.avail(2) >= (size_t)p.I * p.rbD);
+    if (!down) {
+        QW_CHECK_ARG(p.Wb && p.x && L.avail(1) >= wsz && ((uintptr_t)p.Wb & 15) == 0 && ((uintptr_t)p.x & 15) == 0 && ((uintptr_t)p.Sb & 15) == 0);
+        QW_CHECK_ARG((p.Sa == nullptr) == (p.Sb == nullptr));
+        if (p.Sb) QW_CHECK_ARG(L.avail(3) >= (size_t)p.I * p.rbD);
+        p.tiles = p.I / 16;
+    } else {
+        QW_CHECK_ARG(p.Pg && L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
+        p.tiles = p.D / 64;
+    }
+    return cudaSuccess;
+}
+
+static cudaError_t launch_moe_gu(const QwLaunch &L) {
+    MoeP p;
+    uint32_t E, topk;
+    cudaError_t e = moe_fill(L, p, E, topk, false);
+    if (e != cudaSuccess) return e;
+    const size_t smem = 128 + MOE_TAB_BYTES + 8 * 32 * 16 + (size_t)MOE_STAGES * ((2 * 16 * p.rbD + 127) & ~127u);
+    QW_CHECK_ARG(smem <= 227 * 1024);
+    e = cudaFuncSetAttribute(moe_gu_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    moe_gu_k<<<L.sm_count, 256, smem, L.stream>>>(p);
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_gu, launch_moe_gu, 256)
+
+static cudaError_t launch_moe_dn(const QwLaunch &L) {
+    MoeP p;
+    uint32_t E, topk;
+    cudaError_t e = moe_fill(L, p, E, topk, true);
+    if (e != cudaSuccess) return e;
+    const size_t smem = 128 + MOE_TAB_BYTES + 8 * 32 * 16 + (size_t)MOE_STAGES * ((64 * p.rbI + 127) & ~127u);
+    QW_CHECK_ARG(smem <= 227 * 1024);
+    e = cudaFuncSetAttribute(moe_dn_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    moe_dn_k<<<L.sm_count, 256, smem, L.stream>>>(p);
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_dn, launch_moe_dn, 256)
+
+// ------------------------------------------------------------------------------------------------ combine
+// out[t][r] = fp16( sum_{s < topk, rank order} w[t][s] * Pg[t][s][r]  +  w[t][topk] * Pg[t][topk][r] )
+// binds: 3 = moe_sel, 4 = out fp16 [nb][D], 9 = Pg, 8 = nb; with RESID defined 1 also 5 = residual fp32 [nb][D]
+// updated in place (h += out, the plain residual that stands in for the reference's hyper-connection mix).
+// grid (D/256, nb) x 256
+__global__ void __launch_bounds__(256) moe_cmb_k(const moe_sel *ms, __half *out, const float *Pg, float *resid, uint32_t D, uint32_t topk, uint32_t nb) {
+    const uint32_t row = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
+    if (row >= D || t >= nb) return;
+    float o = 0.f;
+    for (uint32_t s = 0; s <= topk; s++) o = fmaf(ms->w[t][s], Pg[((size_t)t * (topk + 1) + s) * D + row], o);
+    const __half h = __float2half_rn(o);
+    out[(size_t)t * D + row] = h;
+    if (resid) resid[(size_t)t * D + row] += __half2float(h);
+}
+
+static cudaError_t launch_moe_cmb(const QwLaunch &L) {
+    const uint32_t D = (uint32_t)L.def("D", 2048), topk = (uint32_t)L.def("TOPK", 10);
+    const uint32_t nb = L.bytes<uint32_t>(8);
+    QW_CHECK_ARG(L.buf<void>(3) && L.buf<void>(4) && L.buf<void>(9) && nb >= 1 && nb <= MOE_MAXB);
+    QW_CHECK_ARG(L.avail(3) >= sizeof(moe_sel) && L.avail(4) >= (size_t)nb * D * 2 && L.avail(9) >= (size_t)nb * (topk + 1) * D * 4);
+    float *resid = L.def("RESID", 0) ? L.buf<float>(5) : nullptr;
+    if (L.def("RESID", 0)) QW_CHECK_ARG(resid && L.avail(5) >= (size_t)nb * D * 4);
+    moe_cmb_k<<<dim3((D + 255) / 256, nb), 256, 0, L.stream>>>(L.buf<moe_sel>(3), L.buf<__half>(4), L.buf<float>(9), resid, D, topk, nb);
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_cmb, launch_moe_cmb, 256)
+
+// size of struct moe_sel for hosts that allocate it (bind 1 of moe_select)
+extern "C" size_t qw_moe_sel_bytes(void) { return sizeof(moe_sel); }

@@ -211,6 +211,7 @@ __global__ void __launch_bounds__(256) qmv_mma_k(const QmvMmaP p) {
         xlo[nt] = nullptr;
     }
     const GridTab<1> gt{tab, 0};
+    const uint32_t tile_on = tiles_on<NT>(xcol);
     const int units = p.K / 256;
     bool ok = true;
 
@@ -229,7 +230,7 @@ __global__ void __launch_bounds__(256) qmv_mma_k(const QmvMmaP p) {
         for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
         for (int u = ks; u < units; u += KS)
             unit_mma<GF, NT, 1, false>(tile + (size_t)g * p.rb + (size_t)u * unit_bytes(GF), tile + (size_t)(g + 8) * p.rb + (size_t)u * unit_bytes(GF),
-                                       gt, t, xcol, xlo, u * 32, acc);
+                                       gt, t, xcol, xlo, tile_on, u * 32, acc);
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) red[(warp * NT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
         __syncthreads();  // partial tiles visible; every warp is done reading stage s

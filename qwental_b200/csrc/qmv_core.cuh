@@ -67,10 +67,21 @@ __device__ __forceinline__ void q8_sub(const uint8_t *blk, int t, uint32_t (&w)[
 
 // One unit (256 K values) for rows r0 (lanes' row g) and r1 (row g + 8): u0 / u1 point at the unit's bytes of
 // those two rows in shared memory.  xcol[nt] (xlo[nt] for the low bf16 plane) is the activation row of column
-// g + 8 nt in 16-byte units, nullptr for an absent column; k8 = index of the unit's first 16-byte chunk.
+// g + 8 nt in 16-byte units, nullptr for an absent column (it then contributes zeros); k8 = index of the unit's
+// first 16-byte chunk.  The MMAs are warp-wide instructions: every lane of the warp must reach them, so a column
+// tile is skipped only when it is absent for the whole warp (tile_on, a warp-uniform mask).
+template <int NT>
+__device__ __forceinline__ uint32_t tiles_on(const uint4 *const (&xcol)[NT]) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+        if (__any_sync(0xffffffffu, xcol[nt] != nullptr)) m |= 1u << nt;
+    return m;
+}
+
 template <int GF, int NT, int REP, bool BF16>
 __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, const GridTab<REP> &gt, int t, const uint4 *const (&xcol)[NT],
-                                         const uint4 *const (&xlo)[NT], int k8, float (&acc)[NT][4]) {
+                                         const uint4 *const (&xlo)[NT], uint32_t tile_on, int k8, float (&acc)[NT][4]) {
     float d0, d1;
     if (GF == 21) {
         d0 = h2f(ldu16(u0));
@@ -96,11 +107,12 @@ __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, c
         const int kk = k8 + 4 * ib + t;
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
-            if (xcol[nt] == nullptr) continue;
-            const uint4 xv = __ldg(xcol[nt] + kk);
+            if (!(tile_on >> nt & 1)) continue;  // warp-uniform
+            const uint4 zero = make_uint4(0, 0, 0, 0);
+            const uint4 xv = xcol[nt] ? __ldg(xcol[nt] + kk) : zero;
             float p[4] = {0.f, 0.f, 0.f, 0.f};
             if (BF16) {
-                const uint4 xl = __ldg(xlo[nt] + kk);
+                const uint4 xl = xcol[nt] ? __ldg(xlo[nt] + kk) : zero;
                 mma_bf16(p, a0, xv.x, xv.y, p);
                 mma_bf16(p, a1, xv.z, xv.w, p);
                 mma_bf16(p, a0, xl.x, xl.y, p);

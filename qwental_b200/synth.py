@@ -22,25 +22,34 @@ def row_bytes(qtype: int, K: int) -> int:
     raise ValueError("unsupported ggml type %d" % qtype)
 
 
-def _scales_fp16(rng, n):
-    """d as fp16 drawn uniform in [1e-3, 2e-2]."""
-    return rng.uniform(1e-3, 2e-2, size=n).astype(np.float16)
+def _scales_fp16(rng, n, d_scale=1.0):
+    """d as fp16 drawn uniform in [1e-3, 2e-2], optionally times a power-of-two d_scale.
+
+    A stack of random matrices at the stated range overflows fp16 after two contractions (a SwiGLU expert's
+    output has rms ~1.5e5), so the layer- and model-level configs scale d per tensor to keep every block
+    output O(1); the single-matvec configs use d_scale = 1."""
+    return (rng.uniform(1e-3, 2e-2, size=n) * d_scale).astype(np.float16)
 
 
-def iq3s_rows(rng: np.random.Generator, nrows: int, K: int) -> np.ndarray:
-    """uint8 [nrows][K/256*110]: every byte uniform in [0,255] except the fp16 scale d."""
+def d_scale_for(K: int) -> float:
+    """Power of two that brings the output rms of a random IQ3_S [N][K] matvec on unit-rms input near 1."""
+    return {256: 2.0 ** -5, 512: 2.0 ** -5, 2048: 2.0 ** -6, 4096: 2.0 ** -7}.get(K, 2.0 ** -6)
+
+
+def iq3s_rows(rng: np.random.Generator, nrows: int, K: int, d_scale: float = 1.0) -> np.ndarray:
+    """uint8 [nrows][K/256*110]: every byte uniform in [0,255] except the fp16 scale d (times d_scale)."""
     nb = K // 256
     blk = rng.integers(0, 256, size=(nrows, nb, 110), dtype=np.uint8)
-    blk[:, :, 0:2] = _scales_fp16(rng, nrows * nb).view(np.uint8).reshape(nrows, nb, 2)
+    blk[:, :, 0:2] = _scales_fp16(rng, nrows * nb, d_scale).view(np.uint8).reshape(nrows, nb, 2)
     return blk.reshape(nrows, nb * 110)
 
 
-def q8_0_rows(rng: np.random.Generator, nrows: int, K: int) -> np.ndarray:
+def q8_0_rows(rng: np.random.Generator, nrows: int, K: int, d_scale: float = 1.0) -> np.ndarray:
     """uint8 [nrows][K/32*34]: fp16 scale d as above, int8 uniform in [-127, 127]."""
     nb = K // 32
     blk = np.empty((nrows, nb, 34), np.uint8)
     blk[:, :, 2:] = rng.integers(-127, 128, size=(nrows, nb, 32), dtype=np.int8).view(np.uint8)
-    blk[:, :, 0:2] = _scales_fp16(rng, nrows * nb).view(np.uint8).reshape(nrows, nb, 2)
+    blk[:, :, 0:2] = _scales_fp16(rng, nrows * nb, d_scale).view(np.uint8).reshape(nrows, nb, 2)
     return blk.reshape(nrows, nb * 34)
 
 
@@ -85,14 +94,14 @@ def hash_u64(seed: int, idx: np.ndarray) -> np.ndarray:
         return mix64(np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + idx.astype(np.uint64))
 
 
-def fill_scale_bits(seed: int, blk_idx: np.ndarray) -> np.ndarray:
-    """fp16 bit pattern of d for block blk_idx: 1e-3 + u * 1.9e-2 with u = 24-bit uniform, rounded to fp16."""
+def fill_scale_bits(seed: int, blk_idx: np.ndarray, d_scale: float = 1.0) -> np.ndarray:
+    """fp16 bit pattern of d for block blk_idx: (1e-3 + u * 1.9e-2) * d_scale, u = 24-bit uniform, rounded to fp16."""
     u = (hash_u64(seed ^ 0x5CA1E, blk_idx) >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0)
-    d = (np.float32(1e-3) + u * np.float32(1.9e-2)).astype(np.float32)
+    d = ((np.float32(1e-3) + u * np.float32(1.9e-2)).astype(np.float32) * np.float32(d_scale)).astype(np.float32)
     return d.astype(np.float16).view(np.uint16)
 
 
-def fill_quant_rows(seed: int, qtype: int, nrows: int, K: int, row0: int = 0) -> np.ndarray:
+def fill_quant_rows(seed: int, qtype: int, nrows: int, K: int, row0: int = 0, d_scale: float = 1.0) -> np.ndarray:
     """Rows row0 .. row0+nrows-1 of the tensor the device `synth_fill` kernel writes for (seed, qtype, K)."""
     rb = row_bytes(qtype, K)
     bb = 110 if qtype == IQ3_S else 34
@@ -102,7 +111,7 @@ def fill_quant_rows(seed: int, qtype: int, nrows: int, K: int, row0: int = 0) ->
         by = np.where(by == 0x80, np.uint8(0x81), by)  # keep int8 in [-127, 127]
     blk = i // np.uint64(bb)
     off = (i % np.uint64(bb)).astype(np.int64)
-    sb = fill_scale_bits(seed, blk)
+    sb = fill_scale_bits(seed, blk, d_scale)
     by = np.where(off == 0, (sb & 0xFF).astype(np.uint8), by)
     by = np.where(off == 1, (sb >> 8).astype(np.uint8), by)
     return by.reshape(nrows, rb)

@@ -1,0 +1,122 @@
+"""GPU parity of the MoE decode layer (benchmark config 2), through the C ABI.
+
+Router logits and the chosen expert ids must be bit-exact against the CPU oracle's canonical-order router and
+top-k; the layer output must be within the reference's own tolerance (max error / max |ref| < 1e-2,
+bench/moe_decode.c:181-182 -- we hold 2e-3) of the FP64 layer (tools/moe_ref.py:72-82) and agree on top-1;
+each token's output must be bit-identical whether it runs alone or in a batch."""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from qwental_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from qwental_b200.gpu import Gpu
+    g = Gpu()
+    yield g
+    g.close()
+
+
+def make_layer(gpu, E, D, I, topk, seed, shared=True, e_lo=0, e_hi=None):
+    from qwental_b200.layers import MoeLayer
+    rng = np.random.default_rng(seed)
+    h = {}
+    h["Wr"] = (rng.standard_normal((E, D)) * 0.02).astype(np.float16)
+    h["wsg"] = (rng.standard_normal(D) * 0.02).astype(np.float16)
+    # block scales d are the stated range times a power of two per tensor so that the layer output stays O(1):
+    # at the unscaled range a SwiGLU expert's output has rms ~1.5e5 and the fp16 layer output would be inf
+    sD, sI = synth.d_scale_for(D), synth.d_scale_for(I)
+    h["gate"] = synth.iq3s_rows(rng, E * I, D, sD).reshape(E, I, -1)
+    h["up"] = synth.iq3s_rows(rng, E * I, D, sD).reshape(E, I, -1)
+    h["down"] = synth.iq3s_rows(rng, E * D, I, sI).reshape(E, D, -1)
+    h["sg"] = synth.iq3s_rows(rng, I, D, sD)
+    h["su"] = synth.iq3s_rows(rng, I, D, sD)
+    h["sd"] = synth.iq3s_rows(rng, D, I, sI)
+    b = {k: gpu.buf_from(v) for k, v in h.items()}
+    layer = MoeLayer(gpu, E, D, I, topk, b["Wr"], b["wsg"], b["gate"], b["up"], b["down"],
+                     b["sg"] if shared else None, b["su"] if shared else None, b["sd"] if shared else None, e_lo, e_hi)
+    return layer, h, b
+
+
+def run_layer(gpu, layer, x):
+    nb = x.shape[0]
+    xb, ob = gpu.buf_from(x), gpu.buf(nb * layer.D * 2).zero()
+    bt = gpu.batch()
+    layer.encode(bt, xb, ob, nb)
+    bt.end()
+    return ob.download(np.float16, nb * layer.D).reshape(nb, layer.D)
+
+
+@pytest.mark.parametrize("E,B", [(64, 16), (64, 1), (64, 64), (512, 16)])
+def test_moe_layer_parity(gpu, E, B):
+    D, I, topk = 2048, 512, 10
+    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=10 + E)
+    x = synth.acts_fp16(np.random.default_rng(B), B, D)
+    out = run_layer(gpu, layer, x)
+
+    # 1. router logits bit-exact (canonical order), shared-gate row included
+    lg = layer.read_logits(B)
+    ref_lg = orc.router_canon(np.concatenate([h["Wr"], h["wsg"][None]]), x)
+    assert np.array_equal(lg.view(np.uint32), ref_lg.view(np.uint32))
+    # 2. expert ids bit-exact; weights to 1e-6; grouping consistent
+    U, ids, w, ue, off, ent = layer.read_sel(B)
+    ref_ids, ref_w = orc.topk(ref_lg[:, :E], topk)
+    assert np.array_equal(ids, ref_ids)
+    assert np.allclose(w[:, :topk], ref_w, rtol=2e-6, atol=1e-7)
+    assert np.allclose(w[:, topk], 1 / (1 + np.exp(-ref_lg[:, E].astype(np.float64))), rtol=2e-6)
+    uniq = np.unique(ref_ids)
+    assert U == len(uniq) and np.array_equal(ue, uniq) and off[-1] == B * topk
+    pairs = sorted((int(e >> 8), int(e & 255)) for e in ent)
+    assert pairs == sorted((t, k) for t in range(B) for k in range(topk))
+    for u in range(U):
+        for e in ent[off[u]:off[u + 1]]:
+            assert ref_ids[e >> 8, e & 255] == ue[u]
+    # 3. layer output vs the FP64 layer on the same experts
+    ref, ids64, gap = orc.moe_ref(x, h["Wr"], h["wsg"], h["gate"], h["up"], h["down"], h["sg"], h["su"], h["sd"], D, I, topk, ids=ids)
+    err = np.abs(out.astype(np.float64) - ref).max() / np.abs(ref).max()
+    assert err < 2e-3, err
+    assert np.array_equal(out.astype(np.float64).argmax(1), ref.argmax(1))
+    # the FP64 router picks the same set wherever its 10th/11th gap exceeds the fp32 error bound
+    for t in range(B):
+        if gap[t] > 1e-5:
+            assert set(ids64[t]) == set(ids[t])
+
+
+def test_moe_batched_equals_alone(gpu):
+    D, I, topk, E, B = 2048, 512, 10, 64, 24
+    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=3)
+    x = synth.acts_fp16(np.random.default_rng(9), B, D)
+    out = run_layer(gpu, layer, x)
+    for t in (0, 7, 23):
+        alone = run_layer(gpu, layer, x[t:t + 1])
+        assert np.array_equal(alone[0].view(np.uint16), out[t].view(np.uint16))
+    # identical tokens in one batch give identical rows (more than 8 tokens on one expert -> several column tiles)
+    xs = np.repeat(x[:1], 20, axis=0)
+    outs = run_layer(gpu, layer, xs)
+    assert all(np.array_equal(outs[i].view(np.uint16), out[0].view(np.uint16)) for i in range(20))
+
+
+def test_moe_expert_range_partitions_the_work(gpu):
+    """Expert-parallel building block: with experts restricted to [lo, hi) each part writes only its own
+    (token, rank) rows; the union over a partition equals the full layer's rows bit for bit."""
+    D, I, topk, E, B = 2048, 512, 10, 64, 16
+    full, h, b = make_layer(gpu, E, D, I, topk, seed=5)
+    x = synth.acts_fp16(np.random.default_rng(2), B, D)
+    run_layer(gpu, full, x)
+    pg_full = full.Pg.download(np.float32, B * (topk + 1) * D).reshape(B, topk + 1, D)
+    _, ids, _, _, _, _ = full.read_sel(B)
+    from qwental_b200.layers import MoeLayer
+    acc = np.zeros_like(pg_full)
+    for lo, hi in ((0, 32), (32, 64)):
+        part = MoeLayer(gpu, E, D, I, topk, b["Wr"], b["wsg"], b["gate"], b["up"], b["down"], b["sg"], b["su"], b["sd"], lo, hi)
+        run_layer(gpu, part, x)
+        pg = part.Pg.download(np.float32, B * (topk + 1) * D).reshape(B, topk + 1, D)
+        mine = (ids >= lo) & (ids < hi)
+        assert np.all(pg[:, :topk][~mine] == 0)
+        acc[:, :topk] += pg[:, :topk]
+        acc[:, topk] = pg[:, topk]
+    assert np.array_equal(acc.view(np.uint32), pg_full.view(np.uint32))
