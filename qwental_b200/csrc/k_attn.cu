@@ -194,20 +194,37 @@ QW_FAMILY(qsa_attn, launch_qsa_attn, 256)
 
 // ------------------------------------------------------------------------------------------------ merge + output gate
 // binds: 0 = part, 1 = qkv fp16 (gate = qkv[t][qh*2*HD + HD + d]), 2 = y fp16 [nb][QH*HD], 3 = pos, 4 = qsa_args.
-// grid (QH, nb) x 256: thread d merges dim d over the slot's chunks in chunk order.
+// grid (QH, nb) x 256.  The chunk weights exp(m_c - M) are computed once per chunk (thread c), then thread d sums
+// dim d over the slot's chunks in chunk order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.
+#define QSA_MAXCH 1024
 __global__ void __launch_bounds__(256) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
     constexpr uint32_t HD = 256;
-    const uint32_t qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
+    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[8];
+    const uint32_t qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
     const uint32_t ntok = (uint32_t)posv[t] + 1, nch = (ntok + QSA_PAGE - 1) / QSA_PAGE;
-    float m = -INFINITY, l = 0.f, acc = 0.f;
+    const float *base = part + ((size_t)t * a.max_chunks * QH + qh) * (HD + 2);
+    const size_t cstride = (size_t)QH * (HD + 2);
+    float mx = -INFINITY;
+    for (uint32_t c = d; c < nch; c += 256) {
+        const float pm = base[c * cstride + HD], pl = base[c * cstride + HD + 1];
+        wc[c] = pm;
+        lc[c] = pl;
+        if (pl > 0.f) mx = fmaxf(mx, pm);
+    }
+    mx = warp_max(mx);
+    if (lane == 0) tmp[warp] = mx;
+    __syncthreads();
+    float M = tmp[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) M = fmaxf(M, tmp[i]);
+    for (uint32_t c = d; c < nch; c += 256) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
+    __syncthreads();
+    float l = 0.f, acc = 0.f;
+#pragma unroll 4
     for (uint32_t c = 0; c < nch; c++) {
-        const float *p = part + (((size_t)t * a.max_chunks + c) * QH + qh) * (HD + 2);
-        const float pm = p[HD], pl = p[HD + 1];
-        if (pl == 0.f) continue;
-        const float mn = fmaxf(m, pm), a0 = expf(m - mn), a1 = expf(pm - mn);
-        l = l * a0 + pl * a1;
-        acc = acc * a0 + p[d] * a1;
-        m = mn;
+        const float w = wc[c];
+        l = fmaf(lc[c], w, l);
+        acc = fmaf(base[c * cstride + d], w, acc);
     }
     const float g = __half2float(qkv[(size_t)t * a.qkv_stride + qh * 2 * HD + HD + d]);
     const float o = __half2float(__float2half_rn(acc / l));
@@ -218,7 +235,7 @@ static cudaError_t launch_qsa_merge(const QwLaunch &L) {
     uint32_t QH, KVH, HD;
     QW_CHECK_ARG(qsa_dims(L, QH, KVH, HD));
     qsa_args a = L.bytes<qsa_args>(4);
-    QW_CHECK_ARG(L.has_bytes(4, 24) && a.nb >= 1 && a.nb <= 64 && a.max_chunks >= 1);
+    QW_CHECK_ARG(L.has_bytes(4, 24) && a.nb >= 1 && a.nb <= 64 && a.max_chunks >= 1 && a.max_chunks <= QSA_MAXCH);
     for (int i = 0; i <= 3; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * a.max_chunks * QH * (HD + 2) * 4 && L.avail(2) >= (size_t)a.nb * QH * HD * 2 &&
                  L.avail(1) >= ((size_t)(a.nb - 1) * a.qkv_stride + QH * 2 * HD) * 2 && L.tx == 256);

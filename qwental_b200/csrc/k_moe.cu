@@ -204,239 +204,244 @@ struct MoeP {
     uint32_t ebase;             // id of the first expert stored in Wa / Wb (expert-parallel slice)
 };
 
-constexpr int MOE_STAGES = 3;
+constexpr int MOE_STG = 2;
 constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
+constexpr int MOE_RED_BYTES = 2 * 16 * 32 * 16;
 
-// gate/up: tile = 16 rows of gate + the same 16 rows of up (28 KB at D = 2048); warps 0-3 take gate, 4-7 up,
-// each a quarter of the units.
-__global__ void __launch_bounds__(256, 1) moe_gu_k(const MoeP p) {
+__device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 256;" ::"r"(team + 1) : "memory"); }
+
+// One kernel for both halves of the expert FFN.  A block is two independent teams of 8 warps; each team walks a
+// contiguous range of items (so consecutive items mostly belong to the same expert) through its own two-stage
+// pipeline of bulk (TMA) copies.  The 64 KB codebook table (16 interleaved copies: conflict-free lookups) is
+// shared by the teams.
+//   gate/up (DOWN = false): item = 16 rows of the gate matrix + the same 16 rows of the up matrix; warp =
+//       (matrix, K-slice of KS = min(4, units)); a warp's UPW units accumulate into one 16 x 8 tile; the KS
+//       partial tiles are summed in slice order, H = silu(g) * u is written as a bf16 high + low pair.
+//   down (DOWN = true): item = 128 rows; warp = (m-tile mt and mt + 4, K-slice of KS = min(2, units)); the B
+//       operand is the H pair (two MMAs per codebook word); the KS partial tiles are summed in slice order.
+// The B fragments of a warp's units (the token columns of the current expert) stay in registers while
+// consecutive items belong to the same expert.
+template <bool DOWN, int UPW>
+__global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = (uint64_t *)smem;                    // [0..2] stages, [3] table
+    uint64_t *bars = (uint64_t *)smem;  // [team * 2 + stage], [4] = table
     uint2 *tab = (uint2 *)(smem + 128);
-    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES); // [8 warps][32]
-    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 8 * 32 * 16;
-    const uint32_t half_bytes = 16 * p.rbD, tile_bytes = 2 * half_bytes;
+    const int tid = threadIdx.x, team = tid >> 8, tt = tid & 255, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES) + team * 16 * 32;
+    const uint32_t rb = DOWN ? p.rbI : p.rbD, K = DOWN ? p.I : p.D, units = K / 256;
+    const uint32_t tile_bytes = DOWN ? 128 * rb : 2 * 16 * rb, half_bytes = 16 * rb;
     const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int mat = warp >> 2, ks = warp & 3;
+    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)team * MOE_STG * stage_stride;
+    const uint32_t KS = DOWN ? (units < 2 ? units : 2) : (units < 4 ? units : 4);
+    const uint32_t ks = DOWN ? (warp & 1) : (warp & 3), grp = DOWN ? (warp >> 1) : (warp >> 2);  // grp: m-tile (down) or matrix (gate/up)
+    const bool active = ks < KS;
     const moe_sel *ms = p.ms;
     const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
     const uint32_t groups = U + (p.Sa ? 1u : 0u), items = groups * p.tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < MOE_STAGES + 1; s++) mbar_init(&bars[s], 1);
+        for (int s = 0; s < 5; s++) mbar_init(&bars[s], 1);
         mbar_init_fence();
     }
-    __syncthreads();
-    const uint32_t first = blockIdx.x, step = gridDim.x;
-    auto issue = [&](uint32_t j) {
-        const uint32_t item = first + j * step;
-        if (item >= items) return;
-        const uint32_t u = item / p.tiles, tile = item % p.tiles;
-        const int s = j % MOE_STAGES;
-        const uint8_t *ga, *ua;
-        if (u < U) {
-            const size_t o = ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * p.rbD;
-            ga = p.Wa + o;
-            ua = p.Wb + o;
-        } else {
-            const size_t o = (size_t)tile * 16 * p.rbD;
-            ga = p.Sa + o;
-            ua = p.Sb + o;
-        }
-        mbar_expect_tx(&bars[s], tile_bytes);
-        bulk_g2s(stage0 + (size_t)s * stage_stride, ga, half_bytes, &bars[s]);
-        bulk_g2s(stage0 + (size_t)s * stage_stride + half_bytes, ua, half_bytes, &bars[s]);
-    };
-    if (tid == 0) {
-        mbar_expect_tx(&bars[MOE_STAGES], MOE_TAB_BYTES);
-        bulk_g2s(tab, p.tab->grid_h4, MOE_TAB_BYTES, &bars[MOE_STAGES]);
-        for (uint32_t j = 0; j < MOE_STAGES - 1; j++) issue(j);
+    // Work units = (group, pass of 8 token columns, row tile), enumerated group-major, then pass, then tile, so that
+    // a team's contiguous range keeps one set of B fragments for many consecutive units and every team gets the
+    // same number of units whatever the group sizes.  pre[g] = passes of all groups before g.
+    __shared__ uint32_t pre[MOE_MAXE + 2];
+    for (uint32_t gi = tid; gi < groups; gi += 512) {
+        const uint32_t c = gi < U ? ms->off[gi + 1] - ms->off[gi] : nb;
+        pre[gi + 1] = (c + 7) / 8;
     }
-    bool ok = mbar_wait(&bars[MOE_STAGES], 0);
-    const GridTab<16> gt{tab, (uint32_t)(lane & 15)};
-    const int units = p.D / 256;
-
-    for (uint32_t j = 0; ok; j++) {
-        const uint32_t item = first + j * step;
-        if (item >= items) break;
-        if (tid == 0) issue(j + MOE_STAGES - 1);
-        const int s = j % MOE_STAGES;
-        if (!mbar_wait(&bars[s], (j / MOE_STAGES) & 1)) {
-            ok = false;
-            break;
-        }
-        const uint32_t u = item / p.tiles, tile = item % p.tiles;
-        const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
-        const uint8_t *rows = stage0 + (size_t)s * stage_stride + (size_t)mat * half_bytes;
-        for (uint32_t c0 = 0; c0 < cnt; c0 += 8) {
-            // this lane's column: entry c0 + g
-            uint32_t tok = 0, rank = 0;
-            const bool have = c0 + g < cnt;
-            if (have) {
-                if (u < U) {
-                    const uint32_t en = ms->ent[e0 + c0 + g];
-                    tok = en >> 8;
-                    rank = en & 255;
-                } else {
-                    tok = c0 + g;
-                    rank = topk;
-                }
-            }
-            const uint4 *xcol[1] = {have ? (const uint4 *)(p.x + (size_t)tok * p.D) : nullptr};
-            const uint4 *xlo[1] = {nullptr};
-            const uint32_t tile_on = tiles_on<1>(xcol);
-            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-            for (int un = ks; un < units; un += 4)
-                unit_mma<21, 1, 16, false>(rows + (size_t)g * p.rbD + (size_t)un * 110, rows + (size_t)(g + 8) * p.rbD + (size_t)un * 110, gt, t,
-                                           xcol, xlo, tile_on, un * 32, acc);
-            red[warp * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-            __syncthreads();
-            if (tid < 128) {
-                // element (row, col) of the 16 x 8 tile: gate and up sums over the 4 K-slices in slice order
-                const int jj = tid & 3, ln = tid >> 2;
-                float gs = 0.f, us = 0.f;
+    if (tid == 0) pre[0] = 0;
+    __syncthreads();
+    if (warp == 0 && team == 0) {  // inclusive scan of pre[1..groups] in chunks of 32
+        uint32_t carry = 0;
+        for (uint32_t b0 = 1; b0 <= groups; b0 += 32) {
+            const uint32_t idx = b0 + lane;
+            uint32_t v = idx <= groups ? pre[idx] : 0;
 #pragma unroll
-                for (int k2 = 0; k2 < 4; k2++) {
-                    gs += ((const float *)&red[k2 * 32 + ln])[jj];
-                    us += ((const float *)&red[(4 + k2) * 32 + ln])[jj];
-                }
-                const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
-                if (c0 + col < cnt) {
-                    uint32_t tk, rk;
-                    if (u < U) {
-                        const uint32_t en = ms->ent[e0 + c0 + col];
-                        tk = en >> 8;
-                        rk = en & 255;
-                    } else {
-                        tk = c0 + col;
-                        rk = topk;
-                    }
-                    const float h = gs / (1.0f + expf(-gs)) * us;
-                    const __nv_bfloat16 hi = __float2bfloat16_rn(h);
-                    const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
-                    const size_t o = ((size_t)tk * (topk + 1) + rk) * p.I + row;
-                    p.Hhi[o] = __bfloat16_as_ushort(hi);
-                    p.Hlo[o] = __bfloat16_as_ushort(lo);
-                }
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += n;
             }
-            __syncthreads();
+            if (idx <= groups) pre[idx] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
         }
     }
-    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 2);
-}
-
-// down: tile = 64 rows (4 m-tiles) of the [D][I] matrix; warp = (m-tile, K-slice of 2).  B operand = H planes.
-__global__ void __launch_bounds__(256, 1) moe_dn_k(const MoeP p) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = (uint64_t *)smem;
-    uint2 *tab = (uint2 *)(smem + 128);
-    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES);
-    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 8 * 32 * 16;
-    const uint32_t tile_bytes = 64 * p.rbI;
-    const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int mt = warp >> 1, ks = warp & 1;
-    const moe_sel *ms = p.ms;
-    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
-    const uint32_t groups = U + (p.Sa ? 1u : 0u), items = groups * p.tiles;
-
-    if (tid == 0) {
-        for (int s = 0; s < MOE_STAGES + 1; s++) mbar_init(&bars[s], 1);
-        mbar_init_fence();
-    }
     __syncthreads();
-    const uint32_t first = blockIdx.x, step = gridDim.x;
-    auto issue = [&](uint32_t j) {
-        const uint32_t item = first + j * step;
-        if (item >= items) return;
-        const uint32_t u = item / p.tiles, tile = item % p.tiles;
-        const int s = j % MOE_STAGES;
-        const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * 64) * p.rbI : p.Sa + (size_t)tile * 64 * p.rbI;
-        mbar_expect_tx(&bars[s], tile_bytes);
-        bulk_g2s(stage0 + (size_t)s * stage_stride, src, tile_bytes, &bars[s]);
+    const uint32_t total = pre[groups] * p.tiles;
+    const uint32_t T = gridDim.x * 2, tg = blockIdx.x * 2 + team;
+    const uint32_t i0 = (uint32_t)((uint64_t)total * tg / T), i1 = (uint32_t)((uint64_t)total * (tg + 1) / T);
+    auto locate = [&](uint32_t w, uint32_t &u, uint32_t &pass, uint32_t &tile) {  // unit index -> (group, pass, tile)
+        const uint32_t q = w / p.tiles;
+        tile = w % p.tiles;
+        uint32_t lo = 0, hi = groups;  // largest u with pre[u] <= q
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (pre[mid] <= q) lo = mid;
+            else hi = mid;
+        }
+        u = lo;
+        pass = q - pre[lo];
+    };
+    uint64_t *full = bars + team * 2;
+    auto issue = [&](uint32_t i) {  // team leader only
+        if (i0 + i >= i1) return;
+        uint32_t u, pass, tile;
+        locate(i0 + i, u, pass, tile);
+        uint8_t *dst = stage0 + (size_t)(i % MOE_STG) * stage_stride;
+        mbar_expect_tx(&full[i % MOE_STG], tile_bytes);
+        if (DOWN) {
+            const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * 128) * rb : p.Sa + (size_t)tile * 128 * rb;
+            bulk_g2s(dst, src, tile_bytes, &full[i % MOE_STG]);
+        } else {
+            const size_t o = u < U ? ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * rb : (size_t)tile * 16 * rb;
+            bulk_g2s(dst, (u < U ? p.Wa : p.Sa) + o, half_bytes, &full[i % MOE_STG]);
+            bulk_g2s(dst + half_bytes, (u < U ? p.Wb : p.Sb) + o, half_bytes, &full[i % MOE_STG]);
+        }
     };
     if (tid == 0) {
-        mbar_expect_tx(&bars[MOE_STAGES], MOE_TAB_BYTES);
-        bulk_g2s(tab, p.tab->grid_b4, MOE_TAB_BYTES, &bars[MOE_STAGES]);
-        for (uint32_t j = 0; j < MOE_STAGES - 1; j++) issue(j);
+        mbar_expect_tx(&bars[4], MOE_TAB_BYTES);
+        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, &bars[4]);
     }
-    bool ok = mbar_wait(&bars[MOE_STAGES], 0);
+    if (tt == 0) issue(0);
+    bool ok = mbar_wait(&bars[4], 0);
     const GridTab<16> gt{tab, (uint32_t)(lane & 15)};
-    const int units = p.I / 256;
 
-    for (uint32_t j = 0; ok; j++) {
-        const uint32_t item = first + j * step;
-        if (item >= items) break;
-        if (tid == 0) issue(j + MOE_STAGES - 1);
-        const int s = j % MOE_STAGES;
-        if (!mbar_wait(&bars[s], (j / MOE_STAGES) & 1)) {
+    uint4 xf[2][8];  // gate/up: [unit job][sub-block]; down: [0] = high plane, [1] = low plane of the warp's unit
+    uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
+
+    for (uint32_t i = 0; ok && i0 + i < i1; i++) {
+        if (tt == 0) issue(i + 1);
+        if (!mbar_wait(&full[i % MOE_STG], (i / MOE_STG) & 1)) {
             ok = false;
             break;
         }
-        const uint32_t u = item / p.tiles, tile = item % p.tiles;
+        uint32_t u, pass, tile;
+        locate(i0 + i, u, pass, tile);
         const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
-        const uint8_t *rows = stage0 + (size_t)s * stage_stride + (size_t)(16 * mt) * p.rbI;
-        for (uint32_t c0 = 0; c0 < cnt; c0 += 8) {
-            uint32_t tok = 0, rank = 0;
-            const bool have = c0 + g < cnt;
-            if (have) {
-                if (u < U) {
-                    const uint32_t en = ms->ent[e0 + c0 + g];
-                    tok = en >> 8;
-                    rank = en & 255;
-                } else {
-                    tok = c0 + g;
-                    rank = topk;
-                }
-            }
-            const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
-            const uint4 *xcol[1] = {have ? (const uint4 *)(p.Hhi + ho) : nullptr};
-            const uint4 *xlo[1] = {have ? (const uint4 *)(p.Hlo + ho) : nullptr};
-            const uint32_t tile_on = tiles_on<1>(xcol);
-            float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
-            for (int un = ks; un < units; un += 2)
-                unit_mma<21, 1, 16, true>(rows + (size_t)g * p.rbI + (size_t)un * 110, rows + (size_t)(g + 8) * p.rbI + (size_t)un * 110, gt, t,
-                                          xcol, xlo, tile_on, un * 32, acc);
-            red[warp * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-            __syncthreads();
-            for (int e = tid; e < 4 * 128; e += 256) {
-                const int jj = e & 3, ln = (e >> 2) & 31, m = e >> 7;
-                float sum = ((const float *)&red[(2 * m) * 32 + ln])[jj];
-                if (units > 1) sum += ((const float *)&red[(2 * m + 1) * 32 + ln])[jj];
-                const uint32_t row = tile * 64 + m * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
-                if (c0 + col < cnt) {
-                    uint32_t tk, rk;
+        const uint8_t *st = stage0 + (size_t)(i % MOE_STG) * stage_stride;
+        const uint32_t c0 = pass * 8;
+        {
+            if (active && (u != cur_u || c0 != cur_c0)) {  // (re)load this warp's B fragments: column g = entry c0 + g
+                cur_u = u;
+                cur_c0 = c0;
+                const bool have = c0 + g < cnt;
+                uint32_t tok = 0, rank = topk;
+                if (have) {
                     if (u < U) {
-                        const uint32_t en = ms->ent[e0 + c0 + col];
-                        tk = en >> 8;
-                        rk = en & 255;
-                    } else {
-                        tk = c0 + col;
-                        rk = topk;
+                        const uint32_t en = ms->ent[e0 + c0 + g];
+                        tok = en >> 8;
+                        rank = en & 255;
+                    } else tok = c0 + g;
+                }
+                const uint4 zero = make_uint4(0, 0, 0, 0);
+                if (DOWN) {
+                    const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
+                    const uint4 *hi = (const uint4 *)(p.Hhi + ho) + ks * 32 + t, *lo = (const uint4 *)(p.Hlo + ho) + ks * 32 + t;
+#pragma unroll
+                    for (int ib = 0; ib < 8; ib++) {
+                        xf[0][ib] = have ? __ldg(hi + 4 * ib) : zero;
+                        xf[1][ib] = have ? __ldg(lo + 4 * ib) : zero;
                     }
-                    p.Pg[((size_t)tk * (topk + 1) + rk) * p.D + row] = sum;
+                } else {
+                    const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + t;
+#pragma unroll
+                    for (int j = 0; j < UPW; j++)
+#pragma unroll
+                        for (int ib = 0; ib < 8; ib++) xf[j][ib] = have ? __ldg(xr + (ks + KS * j) * 32 + 4 * ib) : zero;
                 }
             }
-            __syncthreads();
+            if (DOWN) {
+                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                if (active) {
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const uint8_t *rows = st + (size_t)(16 * (grp + 4 * j)) * rb + (size_t)ks * 110;
+                        unit_mma1<true>(rows + (size_t)g * rb, rows + (size_t)(g + 8) * rb, gt, t, xf[0], xf[1], acc[j]);
+                    }
+                }
+                red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+                red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+                team_sync(team);
+                for (int e = tt; e < 8 * 128; e += 256) {
+                    const int jj = e & 3, ln = (e >> 2) & 31, m = e >> 7, mt = m & 3, j = m >> 2;
+                    float sum = ((const float *)&red[((mt * 2 + 0) * 2 + j) * 32 + ln])[jj];
+                    if (KS > 1) sum += ((const float *)&red[((mt * 2 + 1) * 2 + j) * 32 + ln])[jj];
+                    const uint32_t row = tile * 128 + m * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
+                    if (c0 + col < cnt) {
+                        uint32_t tk, rk;
+                        if (u < U) {
+                            const uint32_t en = ms->ent[e0 + c0 + col];
+                            tk = en >> 8;
+                            rk = en & 255;
+                        } else {
+                            tk = c0 + col;
+                            rk = topk;
+                        }
+                        p.Pg[((size_t)tk * (topk + 1) + rk) * p.D + row] = sum;
+                    }
+                }
+                team_sync(team);
+            } else {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                if (active) {
+#pragma unroll
+                    for (int j = 0; j < UPW; j++) {
+                        const uint32_t un = ks + KS * j;
+                        if (un < units) {
+                            const uint8_t *rows = st + (size_t)grp * half_bytes + (size_t)un * 110;
+                            unit_mma1<false>(rows + (size_t)g * rb, rows + (size_t)(g + 8) * rb, gt, t, xf[j], xf[j], acc);
+                        }
+                    }
+                }
+                red[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                team_sync(team);
+                if (tt < 128) {
+                    const int jj = tt & 3, ln = tt >> 2;
+                    float gs = 0.f, us = 0.f;
+                    for (uint32_t k2 = 0; k2 < KS; k2++) {
+                        gs += ((const float *)&red[k2 * 32 + ln])[jj];
+                        us += ((const float *)&red[(4 + k2) * 32 + ln])[jj];
+                    }
+                    const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
+                    if (c0 + col < cnt) {
+                        uint32_t tk, rk;
+                        if (u < U) {
+                            const uint32_t en = ms->ent[e0 + c0 + col];
+                            tk = en >> 8;
+                            rk = en & 255;
+                        } else {
+                            tk = c0 + col;
+                            rk = topk;
+                        }
+                        const float h = gs / (1.0f + expf(-gs)) * us;
+                        const __nv_bfloat16 hi = __float2bfloat16_rn(h);
+                        const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
+                        const size_t o = ((size_t)tk * (topk + 1) + rk) * p.I + row;
+                        p.Hhi[o] = __bfloat16_as_ushort(hi);
+                        p.Hlo[o] = __bfloat16_as_ushort(lo);
+                    }
+                }
+                team_sync(team);
+            }
         }
     }
-    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 3);
+    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | (DOWN ? 3 : 2));
 }
 
 // binds (gate/up): 0 = Wg, 1 = Wu, 2 = shared gate, 3 = shared up (used unless SHARED is defined 0), 4 = x, 5 = moe_sel,
 //                  6 = Hhi, 7 = Hlo.   (down): 0 = Wd, 2 = shared down, 5 = moe_sel, 6 = Hhi, 7 = Hlo, 9 = Pg.
 //                  both: 10 = id of the first expert held in the weight buffers (optional, default 0).
-// defines: E, D, I, TOPK, EL (experts held locally, default E).  The host's grid is ignored (persistent, one block per SM); block 256.
+// defines: E, D, I, TOPK, EL (experts held locally, default E).  The host's grid and block are ignored (persistent: one block of 512 per SM).
 static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &topk, bool down) {
     E = (uint32_t)L.def("E", 512);
     topk = (uint32_t)L.def("TOPK", 10);
     p.D = (uint32_t)L.def("D", 2048);
     p.I = (uint32_t)L.def("I", 512);
-    QW_CHECK_ARG(p.D % 256 == 0 && p.I % 256 == 0 && p.I % 16 == 0 && p.D % 64 == 0 && L.tx == 256);
+    QW_CHECK_ARG(p.D % 256 == 0 && p.I % 256 == 0 && p.I % 16 == 0 && p.D % 128 == 0 && (L.tx == 256 || L.tx == 512));
     p.rbD = p.D / 256 * 110;
     p.rbI = p.I / 256 * 110;
-    QW_CHECK_ARG((16 * p.rbD) % 16 == 0 && (64 * p.rbI) % 16 == 0);
+    QW_CHECK_ARG((16 * p.rbD) % 16 == 0 && (128 * p.rbI) % 16 == 0);
     p.Wa = L.buf<uint8_t>(0);
     p.Wb = L.buf<uint8_t>(1);
     const bool shared = L.def("SHARED", 1) != 0;  // bind slots persist across dispatches: optional inputs are opted into by a define
@@ -468,9 +473,21 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
         p.tiles = p.I / 16;
     } else {
         QW_CHECK_ARG(p.Pg && L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
-        p.tiles = p.D / 64;
+        p.tiles = p.D / 128;
     }
     return cudaSuccess;
+}
+
+template <bool DOWN, int UPW>
+static cudaError_t moe_ffn_go(const MoeP &p, int sm_count, cudaStream_t st) {
+    const uint32_t tile_bytes = DOWN ? 128 * p.rbI : 2 * 16 * p.rbD;
+    const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * MOE_STG * ((tile_bytes + 127) & ~127u);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    auto k = moe_ffn_k<DOWN, UPW>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k<<<sm_count, 512, smem, st>>>(p);
+    return cudaGetLastError();
 }
 
 static cudaError_t launch_moe_gu(const QwLaunch &L) {
@@ -478,28 +495,21 @@ static cudaError_t launch_moe_gu(const QwLaunch &L) {
     uint32_t E, topk;
     cudaError_t e = moe_fill(L, p, E, topk, false);
     if (e != cudaSuccess) return e;
-    const size_t smem = 128 + MOE_TAB_BYTES + 8 * 32 * 16 + (size_t)MOE_STAGES * ((2 * 16 * p.rbD + 127) & ~127u);
-    QW_CHECK_ARG(smem <= 227 * 1024);
-    e = cudaFuncSetAttribute(moe_gu_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    moe_gu_k<<<L.sm_count, 256, smem, L.stream>>>(p);
-    return cudaGetLastError();
+    const uint32_t units = p.D / 256;
+    QW_CHECK_ARG(units == 1 || units == 2 || units == 4 || units == 8);
+    return units == 8 ? moe_ffn_go<false, 2>(p, L.sm_count, L.stream) : moe_ffn_go<false, 1>(p, L.sm_count, L.stream);
 }
-QW_FAMILY(moe_gu, launch_moe_gu, 256)
+QW_FAMILY(moe_gu, launch_moe_gu, 512)
 
 static cudaError_t launch_moe_dn(const QwLaunch &L) {
     MoeP p;
     uint32_t E, topk;
     cudaError_t e = moe_fill(L, p, E, topk, true);
     if (e != cudaSuccess) return e;
-    const size_t smem = 128 + MOE_TAB_BYTES + 8 * 32 * 16 + (size_t)MOE_STAGES * ((64 * p.rbI + 127) & ~127u);
-    QW_CHECK_ARG(smem <= 227 * 1024);
-    e = cudaFuncSetAttribute(moe_dn_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    moe_dn_k<<<L.sm_count, 256, smem, L.stream>>>(p);
-    return cudaGetLastError();
+    QW_CHECK_ARG(p.I / 256 <= 2);
+    return moe_ffn_go<true, 1>(p, L.sm_count, L.stream);
 }
-QW_FAMILY(moe_dn, launch_moe_dn, 256)
+QW_FAMILY(moe_dn, launch_moe_dn, 512)
 
 // ------------------------------------------------------------------------------------------------ combine
 // out[t][r] = fp16( sum_{s < topk, rank order} w[t][s] * Pg[t][s][r]  +  w[t][topk] * Pg[t][topk][r] )

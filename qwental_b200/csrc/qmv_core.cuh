@@ -129,6 +129,77 @@ __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, c
     }
 }
 
+// ---- variant for the MoE kernels: one 8-token column tile whose B fragments for the whole unit are already in
+// registers (xf[ib], and xl[ib] for the low bf16 plane), per-unit header fields hoisted, sub-block loop fully
+// unrolled so every shift is an immediate, the two MMAs of a sub-block on independent accumulators.
+struct Iq3sHdr {
+    float d;
+    uint32_t q0, q1;  // qh[0..3], qh[4..7] shifted right by 2t: bits 0 / 1 of byte ib = this thread's two codebook high bits
+    uint32_t sc;      // the eight 4-bit scales
+};
+__device__ __forceinline__ Iq3sHdr iq3s_hdr(const uint8_t *blk, int t) {
+    Iq3sHdr h;
+    h.d = h2f(ldu16(blk));
+    h.q0 = (ldu16(blk + 66) | ((uint32_t)ldu16(blk + 68) << 16)) >> (2 * t);
+    h.q1 = (ldu16(blk + 70) | ((uint32_t)ldu16(blk + 72) << 16)) >> (2 * t);
+    h.sc = ldu16(blk + 106) | ((uint32_t)ldu16(blk + 108) << 16);
+    return h;
+}
+template <int IB>
+__device__ __forceinline__ float iq3s_sub_h(const uint8_t *blk, const Iq3sHdr &h, int t, const GridTab<16> &gt, uint32_t (&w)[4]) {
+    const uint32_t qs = ldu16(blk + 2 + 8 * IB + 2 * t);
+    const uint32_t sg = blk[74 + 4 * IB + t];
+    const uint32_t q = (IB < 4 ? h.q0 : h.q1) >> (8 * (IB & 3));
+    const uint32_t i0 = (qs & 255) | ((q << 8) & 256);
+    const uint32_t i1 = (qs >> 8) | ((q << 7) & 256);
+    const uint2 g0 = gt.get(i0), g1 = gt.get(i1);
+    w[0] = g0.x ^ ((sg * 0x40008000u) & 0x80008000u);
+    w[1] = g0.y ^ ((sg * 0x10002000u) & 0x80008000u);
+    w[2] = g1.x ^ ((sg * 0x04000800u) & 0x80008000u);
+    w[3] = g1.y ^ ((sg * 0x01000200u) & 0x80008000u);
+    return __fmul_rn(h.d, (float)(1 + 2 * (int)((h.sc >> (4 * IB)) & 15)));
+}
+
+template <bool BF16, int IB>
+__device__ __forceinline__ void sub_mma1(const uint8_t *u0, const uint8_t *u1, const Iq3sHdr &h0, const Iq3sHdr &h1, int t, const GridTab<16> &gt,
+                                         const uint4 &xv, const uint4 &xl, float (&acc)[4]) {
+    uint32_t wa[4], wb[4];
+    const float dba = iq3s_sub_h<IB>(u0, h0, t, gt, wa);
+    const float dbb = iq3s_sub_h<IB>(u1, h1, t, gt, wb);
+    const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+    const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+    const float z[4] = {0.f, 0.f, 0.f, 0.f};
+    float p[4], r[4];
+    if (BF16) {
+        mma_bf16(p, a0, xv.x, xv.y, z);
+        mma_bf16(r, a1, xv.z, xv.w, z);
+        mma_bf16(p, a0, xl.x, xl.y, p);
+        mma_bf16(r, a1, xl.z, xl.w, r);
+    } else {
+        mma_f16(p, a0, xv.x, xv.y, z);
+        mma_f16(r, a1, xv.z, xv.w, z);
+    }
+    acc[0] = fmaf(dba, p[0] + r[0], acc[0]);
+    acc[1] = fmaf(dba, p[1] + r[1], acc[1]);
+    acc[2] = fmaf(dbb, p[2] + r[2], acc[2]);
+    acc[3] = fmaf(dbb, p[3] + r[3], acc[3]);
+}
+
+// One IQ3_S unit (rows g and g+8 at u0 / u1) against the cached B fragments of one column tile.
+template <bool BF16>
+__device__ __forceinline__ void unit_mma1(const uint8_t *u0, const uint8_t *u1, const GridTab<16> &gt, int t, const uint4 (&xf)[8],
+                                          const uint4 (&xl)[8], float (&acc)[4]) {
+    const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
+    sub_mma1<BF16, 0>(u0, u1, h0, h1, t, gt, xf[0], xl[0], acc);
+    sub_mma1<BF16, 1>(u0, u1, h0, h1, t, gt, xf[1], xl[1], acc);
+    sub_mma1<BF16, 2>(u0, u1, h0, h1, t, gt, xf[2], xl[2], acc);
+    sub_mma1<BF16, 3>(u0, u1, h0, h1, t, gt, xf[3], xl[3], acc);
+    sub_mma1<BF16, 4>(u0, u1, h0, h1, t, gt, xf[4], xl[4], acc);
+    sub_mma1<BF16, 5>(u0, u1, h0, h1, t, gt, xf[5], xl[5], acc);
+    sub_mma1<BF16, 6>(u0, u1, h0, h1, t, gt, xf[6], xl[6], acc);
+    sub_mma1<BF16, 7>(u0, u1, h0, h1, t, gt, xf[7], xl[7], acc);
+}
+
 __host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }
 
 }  // namespace qw

@@ -1,0 +1,95 @@
+"""CPU test of the expert-parallel exchange (world size 2, gloo): each rank computes the (token, rank) rows of the
+experts it owns with the FP oracle, zeros elsewhere; an all-reduce (sum) must reproduce the single-rank buffer bit
+for bit, and the combine on top of it must equal the single-rank layer output."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from qwental_b200 import ep, synth
+
+E, D, I, TOPK, B = 16, 256, 256, 4, 6
+
+
+def rows_for(x, ids, gate, up, down, lo, hi, orc):
+    """fp32 rows [B][TOPK][D] of the experts in [lo, hi), zeros elsewhere (what moe_dn writes on one rank)."""
+    out = np.zeros((B, TOPK, D), np.float32)
+    xf = x.astype(np.float32)
+    for t in range(B):
+        for k in range(TOPK):
+            e = int(ids[t, k])
+            if lo <= e < hi:
+                g = orc.qmv_cpu(21, gate[e], D, xf[t:t + 1], 1)[0][0]
+                u = orc.qmv_cpu(21, up[e], D, xf[t:t + 1], 1)[0][0]
+                h = (g / (1 + np.exp(-g)) * u).astype(np.float32)
+                out[t, k] = orc.qmv_cpu(21, down[e], I, h[None], 1)[0][0]
+    return out
+
+
+def make_inputs():
+    from oracle import oracle as orc
+    rng = np.random.default_rng(0)
+    x = synth.acts_fp16(rng, B, D)
+    Wr = (rng.standard_normal((E, D)) * 0.02).astype(np.float16)
+    gate = synth.iq3s_rows(rng, E * I, D, 2.0 ** -5).reshape(E, I, -1)
+    up = synth.iq3s_rows(rng, E * I, D, 2.0 ** -5).reshape(E, I, -1)
+    down = synth.iq3s_rows(rng, E * D, I, 2.0 ** -5).reshape(E, D, -1)
+    ids, w = orc.topk(orc.router_canon(Wr, x), TOPK)
+    return orc, x, ids, w, gate, up, down
+
+
+def worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc, x, ids, w, gate, up, down = make_inputs()  # replicated, deterministic: the router needs no exchange
+        lo, hi = ep.expert_range(E, rank, world)
+        mine = rows_for(x, ids, gate, up, down, lo, hi, orc)
+        assert np.all(mine[~((ids >= lo) & (ids < hi))] == 0)
+        t = torch.from_numpy(mine.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        full = rows_for(x, ids, gate, up, down, 0, E, orc)
+        ok = np.array_equal(t.numpy().view(np.uint32), full.view(np.uint32))
+        comb = (t.numpy() * w[:, :, None]).sum(1)
+        ok2 = np.array_equal(comb, (full * w[:, :, None]).sum(1))
+        q.put((rank, ok, ok2, int(((ids >= lo) & (ids < hi)).sum())))
+    finally:
+        dist.destroy_process_group()
+
+
+def free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_expert_ranges_partition():
+    for n in (1, 2, 4, 8):
+        r = [ep.expert_range(512, k, n) for k in range(n)]
+        assert r[0][0] == 0 and r[-1][1] == 512 and all(r[i][1] == r[i + 1][0] for i in range(n - 1))
+    assert ep.owner_of(512, 4, np.array([0, 127, 128, 511])).tolist() == [0, 0, 1, 3]
+    with pytest.raises(ValueError):
+        ep.expert_range(10, 0, 3)
+    assert ep.scaling_bound(17.4, 9.1, 8) == pytest.approx(17.4 / (8.3 + 9.1 / 8))
+
+
+@pytest.mark.timeout(180)
+def test_allreduce_of_owned_rows_is_bit_identical_world2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=150) for _ in procs]
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    assert all(ok and ok2 for _, ok, ok2, _ in res)
+    assert sum(n for _, _, _, n in res) == B * TOPK
