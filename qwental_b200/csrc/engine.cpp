@@ -304,7 +304,8 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          new_buf(e, &e->msel, (size_t)e->L * e->sel_bytes) && new_buf(e, &e->Hhi, B * (e->TOPK + 1) * e->I * 2) &&
          new_buf(e, &e->Hlo, B * (e->TOPK + 1) * e->I * 2) && new_buf(e, &e->Pg, B * (e->TOPK + 1) * e->D * 4);
     if (ok) ok = qw_buf_zero(g, &e->msel, 0, e->msel.size) && qw_buf_zero(g, &e->Pg, 0, e->Pg.size) && qw_buf_zero(g, &e->Hhi, 0, e->Hhi.size) &&
-                 qw_buf_zero(g, &e->Hlo, 0, e->Hlo.size) && qw_buf_zero(g, &e->ptab, 0, e->ptab.size);
+                 qw_buf_zero(g, &e->Hlo, 0, e->Hlo.size) && qw_buf_zero(g, &e->ptab, 0, e->ptab.size) &&
+                 qw_buf_zero(g, &e->kvpool, 0, e->kvpool.size);  // rows past a slot's length are multiplied by probability 0: keep them finite
     if (ok) ok = init_weights(e);
     if (!ok) {
         g_open_error = e->err.empty() ? "engine open failed" : e->err;
@@ -472,7 +473,7 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             qw_batch_buf(b, 4, &e->ctl_d, 64 * 4);
             qw_batch_buf(b, 5, &e->part, 0);
             qw_batch_bytes(b, 6, &qa, sizeof qa);
-            qw_batch_dispatch(b, max_chunks, e->KVH, nb, 256, 1, 1);
+            qw_batch_dispatch(b, max_chunks, e->KVH, nb, 128, 1, 1);
             qw_batch_kernel(b, e->k_merge);
             qw_batch_buf(b, 0, &e->part, 0);
             qw_batch_buf(b, 1, &e->proj, 0);

@@ -19,6 +19,9 @@
 // length, so a slot's result is bit-identical alone or in any batch.
 #include "common.cuh"
 #include "qw_kern.h"
+#include <cuda.h>
+#include <map>
+#include <mutex>
 
 using namespace qw;
 
@@ -190,7 +193,232 @@ static cudaError_t launch_qsa_attn(const QwLaunch &L) {
                                                                    L.buf<int32_t>(4), L.buf<float>(5), a, QH, KVH);
     return cudaGetLastError();
 }
-QW_FAMILY(qsa_attn, launch_qsa_attn, 256)
+QW_FAMILY(qsa_attn_simt, launch_qsa_attn, 256)
+
+// ------------------------------------------------------------------------------------------------ attention core, tensor cores
+// Same contract and partial format as qsa_attn_simt above, computed with warp MMAs on K / V tiles staged by 2-D
+// tiled TMA copies (cp.async.bulk.tensor, 128-byte swizzle) -- this is the family the engine uses ("qsa_attn").
+// Block = 4 warps = the four 64-token quarters of one 256-token page for one kv head; a warp walks its quarter in
+// steps of 16 tokens with its own two mbarriers (K buffer, V buffer), so no block-wide synchronisation happens
+// until the final merge of the four quarters.
+//   scores   S^T[16 tokens][8 heads] = K[16][256] . Q^T            16 MMAs m16n8k16, A = K rows via ldmatrix
+//   softmax  online, per head, over the token rows (lanes that share t = lane % 4 hold the same two heads)
+//   output   O^T[256 dims][8 heads] += V^T[256][16 tokens] . P^T   16 MMAs, A = V via ldmatrix.trans,
+//            B = the probabilities moved from accumulator layout to operand layout with four shuffles
+// The 8 query heads of the kv head fill the MMA's N dimension exactly: nothing is padded.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
+                 "l"(tm), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+constexpr int AT_WARP_BYTES = 16384;  // per warp: K tile 8 KB + V tile 8 KB (4 swizzled boxes of 16 rows x 128 B each)
+
+__global__ void __launch_bounds__(128) qsa_attn_mma_k(const __grid_constant__ CUtensorMap tm, const __half *q, const int32_t *pt, const int32_t *posv,
+                                                      const int32_t *sids, float *part, qsa_args a, uint32_t QH, uint32_t KVH, unsigned *status) {
+    constexpr uint32_t HD = 256;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t ch = blockIdx.x, kvh = blockIdx.y, ts = blockIdx.z;
+    const uint32_t ntok = (uint32_t)posv[ts] + 1;
+    if (ch * QSA_PAGE >= ntok) return;
+    const uint32_t n = min((uint32_t)QSA_PAGE, ntok - ch * QSA_PAGE);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);  // swizzled boxes need 1024-byte alignment
+    uint8_t *Kb = smem + warp * AT_WARP_BYTES, *Vb = Kb + 8192;
+    uint64_t *bars = (uint64_t *)(smem + 4 * AT_WARP_BYTES) + warp * 2;
+    const uint32_t tok0 = warp * 64;
+    const uint32_t wn = n > tok0 ? min(64u, n - tok0) : 0, steps = (wn + 15) / 16;
+    if (lane == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    const uint32_t page = (uint32_t)pt[(size_t)sids[ts] * a.max_pages + ch];
+    const int rowK = (int)(((page * a.nlayers + a.layer) * 2) * KVH * QSA_PAGE + kvh * QSA_PAGE + tok0), rowV = rowK + (int)(KVH * QSA_PAGE);
+    auto load = [&](uint8_t *dst, uint64_t *bar, int row) {
+        if (lane == 0) {
+            fence_proxy_async();  // the warp's reads of this buffer (ordered by __syncwarp) before the async-proxy writes
+            mbar_expect_tx(bar, 8192);
+#pragma unroll
+            for (int db = 0; db < 4; db++) tma_load_2d(dst + db * 2048, &tm, db * 64, row, bar);
+        }
+    };
+    if (steps) {
+        load(Kb, &bars[0], rowK);
+        load(Vb, &bars[1], rowV);
+    }
+    // Q as B fragments (k = dim, n = head g), pre-scaled by HD^-1/2 = 1/16 (exact in fp16)
+    uint32_t qf[16][2];
+    {
+        const __half *qp = q + ((size_t)ts * QH + kvh * 8 + g) * HD + 2 * t;
+        const __half2 sc = __floats2half2_rn(0.0625f, 0.0625f);
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            const __half2 v0 = __hmul2(*(const __half2 *)(qp + 16 * ks), sc), v1 = __hmul2(*(const __half2 *)(qp + 16 * ks + 8), sc);
+            qf[ks][0] = *(const uint32_t *)&v0;
+            qf[ks][1] = *(const uint32_t *)&v1;
+        }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int dt = 0; dt < 16; dt++) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    // ldmatrix lane roles: matrix mi = lane / 8, row r8 = lane % 8 (the swizzle key of that row)
+    const uint32_t mi = lane >> 3, r8 = lane & 7;
+    const uint32_t kbase = smem_u32(Kb) + ((mi & 1) * 8 + r8) * 128, vbase = smem_u32(Vb) + ((mi >> 1) * 8 + r8) * 128;
+    bool ok = true;
+    for (uint32_t step = 0; step < steps; step++) {
+        if (!mbar_wait(&bars[0], step & 1)) { ok = false; break; }
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            uint32_t af[4];
+            ldsm_x4(af, kbase + (ks >> 2) * 2048 + ((((ks & 3) * 2 + (mi >> 1)) ^ r8) << 4));
+            mma_f16(s, af, qf[ks][0], qf[ks][1], s);
+        }
+        __syncwarp();
+        if (step + 1 < steps) load(Kb, &bars[0], rowK + (int)(step + 1) * 16);
+        const uint32_t ta = step * 16 + g;
+        if (ta >= wn) s[0] = s[1] = -INFINITY;
+        if (ta + 8 >= wn) s[2] = s[3] = -INFINITY;
+        float x0 = fmaxf(s[0], s[2]), x1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
+            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
+        }
+        const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+        const float a0 = expf(m0 - n0), a1 = expf(m1 - n1);
+        const float p0 = expf(s[0] - n0), p1 = expf(s[1] - n1), p2 = expf(s[2] - n0), p3 = expf(s[3] - n1);
+        l0 = l0 * a0 + (p0 + p2);
+        l1 = l1 * a1 + (p1 + p3);
+        m0 = n0;
+        m1 = n1;
+#pragma unroll
+        for (int dt = 0; dt < 16; dt++) {
+            o[dt][0] *= a0;
+            o[dt][1] *= a1;
+            o[dt][2] *= a0;
+            o[dt][3] *= a1;
+        }
+        // probabilities: accumulator layout (token g / g+8, heads 2t, 2t+1) -> B operand layout (tokens 2t, 2t+1 / +8,
+        // head g).  Each probability travels as an fp16 high part plus an fp16 remainder (two MMAs per dim tile), so the
+        // weighted sum keeps ~22 bits of p instead of 11.
+        const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+        const __half2 r01 = __floats2half2_rn(p0 - f01.x, p1 - f01.y), r23 = __floats2half2_rn(p2 - f23.x, p3 - f23.y);
+        const int srcA = (2 * t) * 4 + (g >> 1), srcB = srcA + 4;
+        const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+        auto to_b = [&](const __half2 &h) {
+            const uint32_t u = *(const uint32_t *)&h;
+            return __byte_perm(__shfl_sync(0xffffffffu, u, srcA), __shfl_sync(0xffffffffu, u, srcB), sel);
+        };
+        const uint32_t b0 = to_b(h01), b1 = to_b(h23), c0 = to_b(r01), c1 = to_b(r23);
+        if (!mbar_wait(&bars[1], step & 1)) { ok = false; break; }
+#pragma unroll
+        for (int dt = 0; dt < 16; dt++) {
+            uint32_t af[4];
+            ldsm_x4_t(af, vbase + (dt >> 2) * 2048 + ((((dt & 3) * 2 + (mi & 1)) ^ r8) << 4));
+            mma_f16(o[dt], af, b0, b1, o[dt]);
+            mma_f16(o[dt], af, c0, c1, o[dt]);
+        }
+        __syncwarp();
+        if (step + 1 < steps) load(Vb, &bars[1], rowV + (int)(step + 1) * 16);
+    }
+    if (!ok && lane == 0) set_status(status, ST_MBAR_TIMEOUT | 4);
+    // this quarter's totals, then the merge of the four quarters in quarter order
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    float *osm = (float *)(smem + warp * AT_WARP_BYTES);  // [8 heads][256 dims], then m[8], l[8]; the warp's own, fully consumed tiles
+    __syncwarp();
+#pragma unroll
+    for (int dt = 0; dt < 16; dt++) {
+        osm[(2 * t) * HD + 16 * dt + g] = o[dt][0];
+        osm[(2 * t + 1) * HD + 16 * dt + g] = o[dt][1];
+        osm[(2 * t) * HD + 16 * dt + g + 8] = o[dt][2];
+        osm[(2 * t + 1) * HD + 16 * dt + g + 8] = o[dt][3];
+    }
+    if (g == 0) {
+        osm[8 * HD + 2 * t] = m0;
+        osm[8 * HD + 2 * t + 1] = m1;
+        osm[8 * HD + 8 + 2 * t] = l0;
+        osm[8 * HD + 8 + 2 * t + 1] = l1;
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < 8 * HD; e += 128) {
+        const uint32_t h = e >> 8, d = e & 255;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float *ow = (const float *)(smem + w * AT_WARP_BYTES);
+            if (ow[8 * HD + 8 + h] > 0.f) M = fmaxf(M, ow[8 * HD + h]);
+        }
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float *ow = (const float *)(smem + w * AT_WARP_BYTES);
+            const float lw = ow[8 * HD + 8 + h];
+            if (lw > 0.f) {
+                const float wt = expf(ow[8 * HD + h] - M);
+                L = fmaf(lw, wt, L);
+                acc = fmaf(ow[h * HD + d], wt, acc);
+            }
+        }
+        float *po = part + (((size_t)ts * a.max_chunks + ch) * QH + kvh * 8 + h) * (HD + 2);
+        po[d] = acc;
+        if (d == 0) {
+            po[HD] = M;
+            po[HD + 1] = L;
+        }
+    }
+}
+
+// One tensor map per KV pool: the pool seen as [rows of one token of one kv head][256 halves]
+static const CUtensorMap *attn_tensor_map(void *pool, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<void *, size_t>, CUtensorMap> cache;
+    std::lock_guard<std::mutex> lk(mu);
+    auto key = std::make_pair(pool, bytes);
+    auto it = cache.find(key);
+    if (it != cache.end()) return &it->second;
+    CUtensorMap tm;
+    const cuuint64_t gdim[2] = {256, (cuuint64_t)(bytes / 512)};
+    const cuuint64_t gstride[1] = {512};
+    const cuuint32_t box[2] = {64, 16}, estr[2] = {1, 1};
+    const CUresult r = cuTensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pool, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return nullptr;
+    return &(cache[key] = tm);
+}
+
+static cudaError_t launch_qsa_attn_mma(const QwLaunch &L) {
+    uint32_t QH, KVH, HD;
+    QW_CHECK_ARG(qsa_dims(L, QH, KVH, HD));
+    qsa_args a = L.bytes<qsa_args>(6);
+    QW_CHECK_ARG(L.has_bytes(6, 24) && a.nb >= 1 && a.nb <= 64 && a.layer < a.nlayers && a.max_chunks >= 1 && a.max_chunks <= a.max_pages);
+    for (int i = 0; i <= 5; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
+    QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * QH * HD * 2 && L.avail(5) >= (size_t)a.nb * a.max_chunks * QH * (HD + 2) * 4);
+    QW_CHECK_ARG(((uintptr_t)L.buf<void>(1) & 15) == 0 && L.avail(1) >= 512 && L.avail(1) / 512 < 0x7fffffffull);
+    const CUtensorMap *tm = attn_tensor_map(L.buf<void>(1), L.avail(1) / 512 * 512);
+    QW_CHECK_ARG(tm != nullptr);
+    const size_t smem = 4 * AT_WARP_BYTES + 64 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(qsa_attn_mma_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    qsa_attn_mma_k<<<dim3(a.max_chunks, KVH, a.nb), 128, smem, L.stream>>>(*tm, L.buf<__half>(0), L.buf<int32_t>(2), L.buf<int32_t>(3),
+                                                                          L.buf<int32_t>(4), L.buf<float>(5), a, QH, KVH, L.status);
+    return cudaGetLastError();
+}
+QW_FAMILY(qsa_attn, launch_qsa_attn_mma, 128)
 
 // ------------------------------------------------------------------------------------------------ merge + output gate
 // binds: 0 = part, 1 = qkv fp16 (gate = qkv[t][qh*2*HD + HD + d]), 2 = y fp16 [nb][QH*HD], 3 = pos, 4 = qsa_args.

@@ -87,18 +87,20 @@ struct sel_args {
 };
 
 __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
-    __shared__ uint32_t cnt[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];
+    __shared__ uint32_t mlo[MOE_MAXE], mhi[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];  // token bit masks per expert
     __shared__ uint16_t sid[MOE_MAXB * MOE_MAXK];
     __shared__ uint32_t wsum[2][32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t PER = E / 32;
-    for (uint32_t e = tid; e < MOE_MAXE; e += 1024) cnt[e] = 0;
-    // 1. top-k per token (one warp per token; lane owns experts lane*PER .. lane*PER+PER-1)
+    for (uint32_t e = tid; e < MOE_MAXE; e += 1024) mlo[e] = mhi[e] = 0;
+    // 1. top-k per token: one warp per token, lane owns experts lane, lane + 32, ... (coalesced reads).  Equal
+    //    logits -> lowest expert id: within a lane the strict '>' keeps the lowest id, across lanes the smallest id
+    //    among the lanes holding the maximum wins.
     for (uint32_t t = warp; t < a.nb; t += 32) {
         const float *lg = logits + (size_t)t * (E + 1);
         float v[32];
 #pragma unroll
-        for (uint32_t j = 0; j < 32; j++) v[j] = j < PER ? lg[lane * PER + j] : -INFINITY;
+        for (uint32_t j = 0; j < 32; j++) v[j] = j < PER ? lg[lane + 32 * j] : -INFINITY;
         float pk = 0.f;
         for (uint32_t k = 0; k < topk; k++) {
             float b0 = v[0];
@@ -107,15 +109,17 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
             for (uint32_t j = 1; j < 32; j++)
                 if (j < PER && v[j] > b0) { b0 = v[j]; j0 = j; }
             const float m = warp_max(b0);
-            const uint32_t Lw = __ffs(__ballot_sync(0xffffffffu, b0 == m)) - 1;  // equal values: lowest lane = lowest id
-            const uint32_t bj = __shfl_sync(0xffffffffu, j0, Lw);
+            uint32_t id = b0 == m ? lane + 32 * j0 : 0xffffffffu;
+#pragma unroll
+            for (int off = 16; off; off >>= 1) id = min(id, __shfl_xor_sync(0xffffffffu, id, off));
             if (lane == 0) {
-                ms->ids[t][k] = (int32_t)(Lw * PER + bj);
-                sid[t * MOE_MAXK + k] = (uint16_t)(Lw * PER + bj);
+                ms->ids[t][k] = (int32_t)id;
+                sid[t * MOE_MAXK + k] = (uint16_t)id;
             }
             if (lane == k) pk = m;
+            const uint32_t bl = id & 31, bj = id >> 5;
 #pragma unroll
-            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == Lw && j == bj) ? -INFINITY : v[j];
+            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == bl && j == bj) ? -INFINITY : v[j];
         }
         const float mx = __shfl_sync(0xffffffffu, pk, 0), ex = expf(pk - mx);
         float sm = 0.f;
@@ -124,14 +128,16 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
         if (lane == topk) ms->w[t][topk] = 1.0f / (1.0f + expf(-lg[E]));
     }
     __syncthreads();
-    // 2. group by expert: count, number the non-empty experts of [e_lo, e_hi) in id order, fill in token order
-    for (uint32_t i = tid; i < a.nb * topk; i += 1024) {
-        const uint32_t e = sid[(i / topk) * MOE_MAXK + i % topk];
-        if (e >= a.e_lo && e < a.e_hi) atomicAdd(&cnt[e], 1u);
+    // 2. group by expert.  mask[e] = tokens that chose e; an entry's place inside its group is the number of
+    //    earlier tokens in the mask, so groups are filled in token order without any serial scan.
+    const uint32_t nent = a.nb * topk;
+    for (uint32_t i = tid; i < nent; i += 1024) {
+        const uint32_t t = i / topk, e = sid[t * MOE_MAXK + (i - t * topk)];
+        if (e >= a.e_lo && e < a.e_hi) atomicOr(t < 32 ? &mlo[e] : &mhi[e], 1u << (t & 31));
     }
     __syncthreads();
     {   // exclusive scans over experts (thread e = expert e): entries and non-empty flags
-        const uint32_t c = tid < E ? cnt[tid] : 0, f = c ? 1u : 0u;
+        const uint32_t c = tid < E ? __popc(mlo[tid]) + __popc(mhi[tid]) : 0, f = c ? 1u : 0u;
         uint32_t sc = c, sf = f;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -152,9 +158,11 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
         }
         __syncthreads();
         const uint32_t bc = warp ? wsum[0][warp - 1] : 0, bf = warp ? wsum[1][warp - 1] : 0;
-        if (tid < MOE_MAXE) {
-            pos[tid] = bc + sc - c;   // first entry of expert tid
-            grp[tid] = bf + sf - f;   // group number of expert tid (if non-empty)
+        pos[tid] = bc + sc - c;   // first entry of expert tid
+        grp[tid] = bf + sf - f;   // group number of expert tid (if non-empty)
+        if (c) {
+            ms->ue[bf + sf - f] = tid;
+            ms->off[bf + sf - f] = bc + sc - c;
         }
         if (tid == 1023) {
             ms->U = bf + sf;
@@ -164,14 +172,11 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
         }
     }
     __syncthreads();
-    if (tid < E && cnt[tid]) {
-        const uint32_t u = grp[tid];
-        ms->ue[u] = tid;
-        ms->off[u] = pos[tid];
-        uint32_t o = pos[tid];
-        for (uint32_t i = 0; i < a.nb * topk; i++) {
-            const uint32_t t = i / topk, k = i % topk;
-            if (sid[t * MOE_MAXK + k] == tid) ms->ent[o++] = (uint16_t)((t << 8) | k);
+    for (uint32_t i = tid; i < nent; i += 1024) {
+        const uint32_t t = i / topk, k = i - t * topk, e = sid[t * MOE_MAXK + k];
+        if (e >= a.e_lo && e < a.e_hi) {
+            const uint32_t before = t < 32 ? __popc(mlo[e] & ((1u << t) - 1)) : __popc(mlo[e]) + __popc(mhi[e] & ((1u << (t - 32)) - 1));
+            ms->ent[pos[e] + before] = (uint16_t)((t << 8) | k);
         }
     }
 }
@@ -305,7 +310,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     }
     if (tt == 0) issue(0);
     bool ok = mbar_wait(&bars[4], 0);
-    const GridTab<16> gt{tab, (uint32_t)(lane & 15)};
+    const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
 
     uint4 xf[2][8];  // gate/up: [unit job][sub-block]; down: [0] = high plane, [1] = low plane of the warp's unit
     uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
@@ -319,7 +324,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         uint32_t u, pass, tile;
         locate(i0 + i, u, pass, tile);
         const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
-        const uint8_t *st = stage0 + (size_t)(i % MOE_STG) * stage_stride;
+        const uint32_t st = smem_u32(stage0) + (i % MOE_STG) * stage_stride;  // shared-space address of the staged tile
         const uint32_t c0 = pass * 8;
         {
             if (active && (u != cur_u || c0 != cur_c0)) {  // (re)load this warp's B fragments: column g = entry c0 + g
@@ -356,8 +361,8 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                 if (active) {
 #pragma unroll
                     for (int j = 0; j < 2; j++) {
-                        const uint8_t *rows = st + (size_t)(16 * (grp + 4 * j)) * rb + (size_t)ks * 110;
-                        unit_mma1<true>(rows + (size_t)g * rb, rows + (size_t)(g + 8) * rb, gt, t, xf[0], xf[1], acc[j]);
+                        const uint32_t rows = st + (16 * (grp + 4 * j) + g) * rb + ks * 110;
+                        unit_mma1<true>(rows, rows + 8 * rb, tabc, t, xf[0], xf[1], acc[j]);
                     }
                 }
                 red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
@@ -389,8 +394,8 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                     for (int j = 0; j < UPW; j++) {
                         const uint32_t un = ks + KS * j;
                         if (un < units) {
-                            const uint8_t *rows = st + (size_t)grp * half_bytes + (size_t)un * 110;
-                            unit_mma1<false>(rows + (size_t)g * rb, rows + (size_t)(g + 8) * rb, gt, t, xf[j], xf[j], acc);
+                            const uint32_t rows = st + grp * half_bytes + g * rb + un * 110;
+                            unit_mma1<false>(rows, rows + 8 * rb, tabc, t, xf[j], xf[j], acc);
                         }
                     }
                 }

@@ -131,41 +131,71 @@ __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, c
 
 // ---- variant for the MoE kernels: one 8-token column tile whose B fragments for the whole unit are already in
 // registers (xf[ib], and xl[ib] for the low bf16 plane), per-unit header fields hoisted, sub-block loop fully
-// unrolled so every shift is an immediate, the two MMAs of a sub-block on independent accumulators.
+// unrolled so every shift and byte selector is an immediate, the two MMAs of a sub-block on independent
+// accumulators.  Shared memory is addressed with 32-bit shared-space addresses and immediate offsets.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+
 struct Iq3sHdr {
-    float d;
-    uint32_t q0, q1;  // qh[0..3], qh[4..7] shifted right by 2t: bits 0 / 1 of byte ib = this thread's two codebook high bits
-    uint32_t sc;      // the eight 4-bit scales
+    float d, d2;        // block scale and twice it: sub-block scale = d + d2 * s
+    uint32_t qa0, qa1;  // bytes = this thread's codebook high bit for word 0 of sub-blocks 0..3 / 4..7 (0 or 1)
+    uint32_t qb0, qb1;  // the same for word 1
+    uint32_t sc;        // the eight 4-bit scales
 };
-__device__ __forceinline__ Iq3sHdr iq3s_hdr(const uint8_t *blk, int t) {
+// blk_t = shared address of the block + 2*t (the thread's qs pair); blk_s = shared address of the block + t (its sign byte)
+__device__ __forceinline__ Iq3sHdr iq3s_hdr(uint32_t blk, int t) {
     Iq3sHdr h;
-    h.d = h2f(ldu16(blk));
-    h.q0 = (ldu16(blk + 66) | ((uint32_t)ldu16(blk + 68) << 16)) >> (2 * t);
-    h.q1 = (ldu16(blk + 70) | ((uint32_t)ldu16(blk + 72) << 16)) >> (2 * t);
-    h.sc = ldu16(blk + 106) | ((uint32_t)ldu16(blk + 108) << 16);
+    h.d = h2f((uint16_t)lds_u16<0>(blk));
+    h.d2 = h.d + h.d;
+    const uint32_t q0 = (lds_u16<66>(blk) | (lds_u16<68>(blk) << 16)) >> (2 * t);
+    const uint32_t q1 = (lds_u16<70>(blk) | (lds_u16<72>(blk) << 16)) >> (2 * t);
+    h.qa0 = q0 & 0x01010101u;
+    h.qb0 = (q0 >> 1) & 0x01010101u;
+    h.qa1 = q1 & 0x01010101u;
+    h.qb1 = (q1 >> 1) & 0x01010101u;
+    h.sc = lds_u16<106>(blk) | (lds_u16<108>(blk) << 16);
     return h;
 }
+// Codebook index = qs byte | high bit << 8, assembled by one byte permute: byte 0 from qs, byte 1 = the 0/1 byte of
+// the header word, bytes 2-3 = the upper bytes of the zero-extended 16-bit qs load (always zero).
 template <int IB>
-__device__ __forceinline__ float iq3s_sub_h(const uint8_t *blk, const Iq3sHdr &h, int t, const GridTab<16> &gt, uint32_t (&w)[4]) {
-    const uint32_t qs = ldu16(blk + 2 + 8 * IB + 2 * t);
-    const uint32_t sg = blk[74 + 4 * IB + t];
-    const uint32_t q = (IB < 4 ? h.q0 : h.q1) >> (8 * (IB & 3));
-    const uint32_t i0 = (qs & 255) | ((q << 8) & 256);
-    const uint32_t i1 = (qs >> 8) | ((q << 7) & 256);
-    const uint2 g0 = gt.get(i0), g1 = gt.get(i1);
+__device__ __forceinline__ float iq3s_sub_h(uint32_t blk_t, uint32_t blk_s, const Iq3sHdr &h, uint32_t tabc, uint32_t (&w)[4]) {
+    constexpr uint32_t k = IB & 3;
+    constexpr uint32_t selA = (3u << 12) | (2u << 8) | ((4 + k) << 4) | 0;
+    constexpr uint32_t selB = (3u << 12) | (2u << 8) | ((4 + k) << 4) | 1;
+    const uint32_t qs = lds_u16<2 + 8 * IB>(blk_t);
+    const uint32_t sg = lds_u8<74 + 4 * IB>(blk_s);
+    const uint32_t i0 = __byte_perm(qs, IB < 4 ? h.qa0 : h.qa1, selA);
+    const uint32_t i1 = __byte_perm(qs, IB < 4 ? h.qb0 : h.qb1, selB);
+    const uint2 g0 = lds_v2(tabc + i0 * 128), g1 = lds_v2(tabc + i1 * 128);
     w[0] = g0.x ^ ((sg * 0x40008000u) & 0x80008000u);
     w[1] = g0.y ^ ((sg * 0x10002000u) & 0x80008000u);
     w[2] = g1.x ^ ((sg * 0x04000800u) & 0x80008000u);
     w[3] = g1.y ^ ((sg * 0x01000200u) & 0x80008000u);
-    return __fmul_rn(h.d, (float)(1 + 2 * (int)((h.sc >> (4 * IB)) & 15)));
+    return fmaf(h.d2, (float)((h.sc >> (4 * IB)) & 15), h.d);
 }
 
 template <bool BF16, int IB>
-__device__ __forceinline__ void sub_mma1(const uint8_t *u0, const uint8_t *u1, const Iq3sHdr &h0, const Iq3sHdr &h1, int t, const GridTab<16> &gt,
-                                         const uint4 &xv, const uint4 &xl, float (&acc)[4]) {
+__device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const uint4 &xv,
+                                         const uint4 &xl, float (&acc)[4]) {
     uint32_t wa[4], wb[4];
-    const float dba = iq3s_sub_h<IB>(u0, h0, t, gt, wa);
-    const float dbb = iq3s_sub_h<IB>(u1, h1, t, gt, wb);
+    const float dba = iq3s_sub_h<IB>(u0 + 2 * t, u0 + t, h0, tabc, wa);
+    const float dbb = iq3s_sub_h<IB>(u1 + 2 * t, u1 + t, h1, tabc, wb);
     const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
     const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
     const float z[4] = {0.f, 0.f, 0.f, 0.f};
@@ -185,19 +215,20 @@ __device__ __forceinline__ void sub_mma1(const uint8_t *u0, const uint8_t *u1, c
     acc[3] = fmaf(dbb, p[3] + r[3], acc[3]);
 }
 
-// One IQ3_S unit (rows g and g+8 at u0 / u1) against the cached B fragments of one column tile.
+// One IQ3_S unit (rows g and g+8 at shared addresses u0 / u1) against the cached B fragments of one column tile.
+// d*(1+2s) is evaluated as fma(2d, s, d): both forms are exact products of a half-precision d and an odd integer
+// below 32, so they give the same fp32 value.
 template <bool BF16>
-__device__ __forceinline__ void unit_mma1(const uint8_t *u0, const uint8_t *u1, const GridTab<16> &gt, int t, const uint4 (&xf)[8],
-                                          const uint4 (&xl)[8], float (&acc)[4]) {
+__device__ __forceinline__ void unit_mma1(uint32_t u0, uint32_t u1, uint32_t tabc, int t, const uint4 (&xf)[8], const uint4 (&xl)[8], float (&acc)[4]) {
     const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
-    sub_mma1<BF16, 0>(u0, u1, h0, h1, t, gt, xf[0], xl[0], acc);
-    sub_mma1<BF16, 1>(u0, u1, h0, h1, t, gt, xf[1], xl[1], acc);
-    sub_mma1<BF16, 2>(u0, u1, h0, h1, t, gt, xf[2], xl[2], acc);
-    sub_mma1<BF16, 3>(u0, u1, h0, h1, t, gt, xf[3], xl[3], acc);
-    sub_mma1<BF16, 4>(u0, u1, h0, h1, t, gt, xf[4], xl[4], acc);
-    sub_mma1<BF16, 5>(u0, u1, h0, h1, t, gt, xf[5], xl[5], acc);
-    sub_mma1<BF16, 6>(u0, u1, h0, h1, t, gt, xf[6], xl[6], acc);
-    sub_mma1<BF16, 7>(u0, u1, h0, h1, t, gt, xf[7], xl[7], acc);
+    sub_mma1<BF16, 0>(u0, u1, t, h0, h1, tabc, xf[0], xl[0], acc);
+    sub_mma1<BF16, 1>(u0, u1, t, h0, h1, tabc, xf[1], xl[1], acc);
+    sub_mma1<BF16, 2>(u0, u1, t, h0, h1, tabc, xf[2], xl[2], acc);
+    sub_mma1<BF16, 3>(u0, u1, t, h0, h1, tabc, xf[3], xl[3], acc);
+    sub_mma1<BF16, 4>(u0, u1, t, h0, h1, tabc, xf[4], xl[4], acc);
+    sub_mma1<BF16, 5>(u0, u1, t, h0, h1, tabc, xf[5], xl[5], acc);
+    sub_mma1<BF16, 6>(u0, u1, t, h0, h1, tabc, xf[6], xl[6], acc);
+    sub_mma1<BF16, 7>(u0, u1, t, h0, h1, tabc, xf[7], xl[7], acc);
 }
 
 __host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }

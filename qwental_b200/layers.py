@@ -103,14 +103,16 @@ class MoeLayer:
 class AttnCore:
     """qsa_prep + qsa_attn + qsa_merge over a paged KV pool (one attention layer's slice of the pages)."""
 
-    def __init__(self, gpu: Gpu, QH: int, KVH: int, HD: int, max_slots: int, max_pages: int, n_pages: int, nlayers: int = 1):
+    def __init__(self, gpu: Gpu, QH: int, KVH: int, HD: int, max_slots: int, max_pages: int, n_pages: int, nlayers: int = 1,
+                 attn_family: str = "qsa_attn"):
         self.gpu, self.QH, self.KVH, self.HD, self.max_pages, self.nlayers = gpu, QH, KVH, HD, max_pages, nlayers
         d = dict(QH=QH, KVH=KVH, HD=HD)
         self.k_prep = gpu.compile("qsa_prep", "qsa_prep_t", **d)
-        self.k_attn = gpu.compile("qsa_attn", "qsa_attn_t", **d)
+        self.k_attn = gpu.compile(attn_family, attn_family + "_t", **d)
+        self.attn_threads = 256 if attn_family == "qsa_attn_simt" else 128
         self.k_merge = gpu.compile("qsa_merge", "qsa_merge_t", **d)
         self.page_halves = nlayers * 2 * KVH * 256 * HD
-        self.pool = gpu.buf(n_pages * self.page_halves * 2)
+        self.pool = gpu.buf(n_pages * self.page_halves * 2).zero()
         self.ptab = gpu.buf(max_slots * max_pages * 4).zero()
         self.part = gpu.buf(MOE_MAXB * max_pages * QH * (HD + 2) * 4)
         self.q = gpu.buf(MOE_MAXB * QH * HD * 2)
@@ -123,7 +125,7 @@ class AttnCore:
         b.kernel(self.k_prep).buf(0, qkv).buf(1, qn).buf(2, kn).buf(3, self.q).buf(4, self.pool).buf(5, self.ptab).buf(6, pos).buf(7, sids) \
             .bytes(8, a).dispatch((self.QH + self.KVH, nb), (256,))
         b.kernel(self.k_attn).buf(0, self.q).buf(1, self.pool).buf(2, self.ptab).buf(3, pos).buf(4, sids).buf(5, self.part).bytes(6, a) \
-            .dispatch((max_chunks, self.KVH, nb), (256,))
+            .dispatch((max_chunks, self.KVH, nb), (self.attn_threads,))
         b.kernel(self.k_merge).buf(0, self.part).buf(1, qkv).buf(2, y).buf(3, pos).bytes(4, a).dispatch((self.QH, nb), (256,))
 
 

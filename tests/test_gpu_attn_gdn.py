@@ -22,14 +22,14 @@ def gpu():
     g.close()
 
 
-def attn_setup(gpu, lens, seed, nlayers=2, layer=1):
+def attn_setup(gpu, lens, seed, nlayers=2, layer=1, family="qsa_attn"):
     """Slots with the given context lengths (tokens already cached); pages handed out in a shuffled order."""
     from qwental_b200.layers import AttnCore
     rng = np.random.default_rng(seed)
     B = len(lens)
     max_pages = max((int(l) + 1 + 255) // 256 for l in lens) + 1
     n_pages = sum((int(l) + 1 + 255) // 256 for l in lens) + 3
-    core = AttnCore(gpu, QH, KVH, HD, max_slots=B + 2, max_pages=max_pages, n_pages=n_pages, nlayers=nlayers)
+    core = AttnCore(gpu, QH, KVH, HD, max_slots=B + 2, max_pages=max_pages, n_pages=n_pages, nlayers=nlayers, attn_family=family)
     order = rng.permutation(n_pages)
     pool = np.zeros((n_pages, nlayers, 2, KVH, 256, HD), np.float16)
     ptab = np.zeros((B + 2, max_pages), np.int32)
@@ -84,9 +84,10 @@ def attn_oracle(d, r):
     return orc.attn_ref(qn, K, V, gate), kk
 
 
-@pytest.mark.parametrize("lens", [[0, 1, 3, 255, 256, 257, 1500, 2049], [1024, 3001, 8195, 20000, 48000]])
-def test_attention_parity_ragged(gpu, lens):
-    core, d = attn_setup(gpu, lens, seed=len(lens))
+@pytest.mark.parametrize("family", ["qsa_attn", "qsa_attn_simt"])
+@pytest.mark.parametrize("lens", [[0, 1, 3, 15, 16, 17, 63, 64, 65, 255, 256, 257, 1500, 2049], [1024, 3001, 8195, 20000, 48000]])
+def test_attention_parity_ragged(gpu, lens, family):
+    core, d = attn_setup(gpu, lens, seed=len(lens), family=family)
     y = attn_run(gpu, core, d, range(len(lens)))
     for r in range(len(lens)):
         ref, kk = attn_oracle(d, r)
