@@ -211,7 +211,7 @@ struct MoeP {
 
 constexpr int MOE_STG = 2;
 constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
-constexpr int MOE_RED_BYTES = 2 * 16 * 32 * 16;
+constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // per team two buffers (alternating by unit) of 16 x 32 float4
 
 __device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 256;" ::"r"(team + 1) : "memory"); }
 
@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     uint64_t *bars = (uint64_t *)smem;  // [team * 2 + stage], [4] = table
     uint2 *tab = (uint2 *)(smem + 128);
     const int tid = threadIdx.x, team = tid >> 8, tt = tid & 255, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    float4 *red = (float4 *)(smem + 128 + MOE_TAB_BYTES) + team * 16 * 32;
+    float4 *red0 = (float4 *)(smem + 128 + MOE_TAB_BYTES) + team * 2 * 16 * 32;
     const uint32_t rb = DOWN ? p.rbI : p.rbD, K = DOWN ? p.I : p.D, units = K / 256;
     const uint32_t tile_bytes = DOWN ? 128 * rb : 2 * 16 * rb, half_bytes = 16 * rb;
     const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
@@ -289,10 +289,17 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         pass = q - pre[lo];
     };
     uint64_t *full = bars + team * 2;
-    auto issue = [&](uint32_t i) {  // team leader only
+    __shared__ uint4 meta[2][MOE_STG];   // per team and stage: {group, tile, first entry of the group, entries in the group}
+    __shared__ uint32_t meta_c0[2][MOE_STG];
+    auto issue = [&](uint32_t i) {  // team leader only: locate the unit, publish its description, start the copies
         if (i0 + i >= i1) return;
         uint32_t u, pass, tile;
         locate(i0 + i, u, pass, tile);
+        {
+            const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+            meta[team][i % MOE_STG] = make_uint4(u, tile, e0, cnt);
+            meta_c0[team][i % MOE_STG] = pass * 8;
+        }
         uint8_t *dst = stage0 + (size_t)(i % MOE_STG) * stage_stride;
         mbar_expect_tx(&full[i % MOE_STG], tile_bytes);
         if (DOWN) {
@@ -312,6 +319,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     bool ok = mbar_wait(&bars[4], 0);
     const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
 
+    const ZeroRegs zr = zero_regs();
     uint4 xf[2][8];  // gate/up: [unit job][sub-block]; down: [0] = high plane, [1] = low plane of the warp's unit
     uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
 
@@ -321,11 +329,14 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
             ok = false;
             break;
         }
-        uint32_t u, pass, tile;
-        locate(i0 + i, u, pass, tile);
-        const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+        // the leader wrote the unit's description before its mbarrier arrive (release); the wait above acquires it
+        const uint4 md = meta[team][i % MOE_STG];
+        const uint32_t u = md.x, tile = md.y, e0 = md.z, cnt = md.w, c0 = meta_c0[team][i % MOE_STG];
         const uint32_t st = smem_u32(stage0) + (i % MOE_STG) * stage_stride;  // shared-space address of the staged tile
-        const uint32_t c0 = pass * 8;
+        // partial tiles alternate between two buffers, so one team barrier per unit is enough: a buffer is rewritten two
+        // units later, after every thread has passed the next unit's barrier; the same barrier frees the stage for the
+        // copy that the leader starts at the top of the next iteration
+        float4 *red = red0 + (i & 1) * 16 * 32;
         {
             if (active && (u != cur_u || c0 != cur_c0)) {  // (re)load this warp's B fragments: column g = entry c0 + g
                 cur_u = u;
@@ -362,7 +373,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
 #pragma unroll
                     for (int j = 0; j < 2; j++) {
                         const uint32_t rows = st + (16 * (grp + 4 * j) + g) * rb + ks * 110;
-                        unit_mma1<true>(rows, rows + 8 * rb, tabc, t, xf[0], xf[1], acc[j]);
+                        unit_mma1<true>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[1], acc[j]);
                     }
                 }
                 red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
@@ -386,7 +397,6 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                         p.Pg[((size_t)tk * (topk + 1) + rk) * p.D + row] = sum;
                     }
                 }
-                team_sync(team);
             } else {
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 if (active) {
@@ -395,7 +405,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                         const uint32_t un = ks + KS * j;
                         if (un < units) {
                             const uint32_t rows = st + grp * half_bytes + g * rb + un * 110;
-                            unit_mma1<false>(rows, rows + 8 * rb, tabc, t, xf[j], xf[j], acc);
+                            unit_mma1<false>(rows, rows + 8 * rb, tabc, t, zr, xf[j], xf[j], acc);
                         }
                     }
                 }
@@ -427,7 +437,6 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                         p.Hlo[o] = __bfloat16_as_ushort(lo);
                     }
                 }
-                team_sync(team);
             }
         }
     }

@@ -135,8 +135,8 @@ __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, c
 // accumulators.  Shared memory is addressed with 32-bit shared-space addresses and immediate offsets.
 template <int OFF>
 __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=h"(v) : "r"(a), "n"(OFF));
+    uint32_t v;  // zero-extended into a 32-bit register
+    asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
     return v;
 }
 template <int OFF>
@@ -190,45 +190,57 @@ __device__ __forceinline__ float iq3s_sub_h(uint32_t blk_t, uint32_t blk_s, cons
     return fmaf(h.d2, (float)((h.sc >> (4 * IB)) & 15), h.d);
 }
 
+// Four registers that hold 0.0f and that the compiler cannot fold away: the C operand of each sub-block's first MMA
+// (a literal zero would be re-materialised with moves in front of every MMA).
+struct ZeroRegs {
+    float z[4];
+};
+__device__ __forceinline__ ZeroRegs zero_regs() {
+    ZeroRegs r;
+    asm volatile("mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\tmov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;"
+                 : "=f"(r.z[0]), "=f"(r.z[1]), "=f"(r.z[2]), "=f"(r.z[3]));
+    return r;
+}
+
 template <bool BF16, int IB>
-__device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const uint4 &xv,
-                                         const uint4 &xl, float (&acc)[4]) {
+__device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr,
+                                         const uint4 &xv, const uint4 &xl, float (&acc)[4]) {
     uint32_t wa[4], wb[4];
     const float dba = iq3s_sub_h<IB>(u0 + 2 * t, u0 + t, h0, tabc, wa);
     const float dbb = iq3s_sub_h<IB>(u1 + 2 * t, u1 + t, h1, tabc, wb);
     const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
     const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
-    const float z[4] = {0.f, 0.f, 0.f, 0.f};
-    float p[4], r[4];
+    float p[4];
     if (BF16) {
-        mma_bf16(p, a0, xv.x, xv.y, z);
-        mma_bf16(r, a1, xv.z, xv.w, z);
+        mma_bf16(p, a0, xv.x, xv.y, zr.z);
+        mma_bf16(p, a1, xv.z, xv.w, p);
         mma_bf16(p, a0, xl.x, xl.y, p);
-        mma_bf16(r, a1, xl.z, xl.w, r);
+        mma_bf16(p, a1, xl.z, xl.w, p);
     } else {
-        mma_f16(p, a0, xv.x, xv.y, z);
-        mma_f16(r, a1, xv.z, xv.w, z);
+        mma_f16(p, a0, xv.x, xv.y, zr.z);
+        mma_f16(p, a1, xv.z, xv.w, p);
     }
-    acc[0] = fmaf(dba, p[0] + r[0], acc[0]);
-    acc[1] = fmaf(dba, p[1] + r[1], acc[1]);
-    acc[2] = fmaf(dbb, p[2] + r[2], acc[2]);
-    acc[3] = fmaf(dbb, p[3] + r[3], acc[3]);
+    acc[0] = fmaf(dba, p[0], acc[0]);
+    acc[1] = fmaf(dba, p[1], acc[1]);
+    acc[2] = fmaf(dbb, p[2], acc[2]);
+    acc[3] = fmaf(dbb, p[3], acc[3]);
 }
 
 // One IQ3_S unit (rows g and g+8 at shared addresses u0 / u1) against the cached B fragments of one column tile.
 // d*(1+2s) is evaluated as fma(2d, s, d): both forms are exact products of a half-precision d and an odd integer
 // below 32, so they give the same fp32 value.
 template <bool BF16>
-__device__ __forceinline__ void unit_mma1(uint32_t u0, uint32_t u1, uint32_t tabc, int t, const uint4 (&xf)[8], const uint4 (&xl)[8], float (&acc)[4]) {
+__device__ __forceinline__ void unit_mma1(uint32_t u0, uint32_t u1, uint32_t tabc, int t, const ZeroRegs &zr, const uint4 (&xf)[8], const uint4 (&xl)[8],
+                                          float (&acc)[4]) {
     const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
-    sub_mma1<BF16, 0>(u0, u1, t, h0, h1, tabc, xf[0], xl[0], acc);
-    sub_mma1<BF16, 1>(u0, u1, t, h0, h1, tabc, xf[1], xl[1], acc);
-    sub_mma1<BF16, 2>(u0, u1, t, h0, h1, tabc, xf[2], xl[2], acc);
-    sub_mma1<BF16, 3>(u0, u1, t, h0, h1, tabc, xf[3], xl[3], acc);
-    sub_mma1<BF16, 4>(u0, u1, t, h0, h1, tabc, xf[4], xl[4], acc);
-    sub_mma1<BF16, 5>(u0, u1, t, h0, h1, tabc, xf[5], xl[5], acc);
-    sub_mma1<BF16, 6>(u0, u1, t, h0, h1, tabc, xf[6], xl[6], acc);
-    sub_mma1<BF16, 7>(u0, u1, t, h0, h1, tabc, xf[7], xl[7], acc);
+    sub_mma1<BF16, 0>(u0, u1, t, h0, h1, tabc, zr, xf[0], xl[0], acc);
+    sub_mma1<BF16, 1>(u0, u1, t, h0, h1, tabc, zr, xf[1], xl[1], acc);
+    sub_mma1<BF16, 2>(u0, u1, t, h0, h1, tabc, zr, xf[2], xl[2], acc);
+    sub_mma1<BF16, 3>(u0, u1, t, h0, h1, tabc, zr, xf[3], xl[3], acc);
+    sub_mma1<BF16, 4>(u0, u1, t, h0, h1, tabc, zr, xf[4], xl[4], acc);
+    sub_mma1<BF16, 5>(u0, u1, t, h0, h1, tabc, zr, xf[5], xl[5], acc);
+    sub_mma1<BF16, 6>(u0, u1, t, h0, h1, tabc, zr, xf[6], xl[6], acc);
+    sub_mma1<BF16, 7>(u0, u1, t, h0, h1, tabc, zr, xf[7], xl[7], acc);
 }
 
 __host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }
