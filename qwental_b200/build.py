@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if r.returncode != 0:
                     raise RuntimeError("nvcc failed on %s:\n%s" % (f, r.stderr[-4000:]))
     if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart", "-lcuda"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-ccbin", "/usr/bin/g++", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stderr[-4000:])

@@ -20,6 +20,7 @@
 #include "common.cuh"
 #include "qw_kern.h"
 #include <cuda.h>
+#include <cstdio>
 #include <map>
 #include <mutex>
 
@@ -383,6 +384,26 @@ __global__ void __launch_bounds__(128) qsa_attn_mma_k(const __grid_constant__ CU
     }
 }
 
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the library has no link
+// dependency on libcuda (it must load, without running anything, on machines that have no driver).
+typedef CUresult (*qw_encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                       const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                       CUtensorMapFloatOOBfill);
+static bool attn_encode_map(CUtensorMap *tm, const void *pool, size_t bytes) {
+    static qw_encode_tiled_fn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess || !p) return false;
+        fn = (qw_encode_tiled_fn)p;
+    }
+    const cuuint64_t gdim[2] = {256, (cuuint64_t)(bytes / 512)};
+    const cuuint64_t gstride[1] = {512};
+    const cuuint32_t box[2] = {64, 16}, estr[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)pool, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // One tensor map per KV pool: the pool seen as [rows of one token of one kv head][256 halves]
 static const CUtensorMap *attn_tensor_map(void *pool, size_t bytes) {
     static std::mutex mu;
@@ -392,12 +413,7 @@ static const CUtensorMap *attn_tensor_map(void *pool, size_t bytes) {
     auto it = cache.find(key);
     if (it != cache.end()) return &it->second;
     CUtensorMap tm;
-    const cuuint64_t gdim[2] = {256, (cuuint64_t)(bytes / 512)};
-    const cuuint64_t gstride[1] = {512};
-    const cuuint32_t box[2] = {64, 16}, estr[2] = {1, 1};
-    const CUresult r = cuTensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, pool, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return nullptr;
+    if (!attn_encode_map(&tm, pool, bytes)) return nullptr;
     return &(cache[key] = tm);
 }
 
@@ -471,3 +487,4 @@ static cudaError_t launch_qsa_merge(const QwLaunch &L) {
     return cudaGetLastError();
 }
 QW_FAMILY(qsa_merge, launch_qsa_merge, 256)
+
