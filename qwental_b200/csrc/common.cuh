@@ -17,6 +17,16 @@ __device__ __forceinline__ void set_status(unsigned *status, unsigned code) {
     if (status) *(volatile unsigned *)status = code;  // plain store: the word lives in host memory
 }
 
+// ---- programmatic dependent launch: pdl_launch() lets the next kernel of the stream begin launching, pdl_wait() blocks
+// until the previous kernel has completed and its writes are visible (a no-op when the launch carried no such
+// attribute).  Rule of this library: nothing that another kernel reads or writes is touched before pdl_wait().
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() {
+    pdl_launch();
+    pdl_wait();
+}
+
 // ---- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

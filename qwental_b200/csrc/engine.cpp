@@ -87,10 +87,10 @@ struct qw_engine {
     unsigned long long clock = 0;
     // scratch
     qw_buf ctl_h{}, ctl_d{}, h{}, x{}, proj{}, cv{}, la{}, be{}, gy{}, qb{}, part{}, ya{}, ob{}, mo{}, logits{}, ids{}, ids_h{}, logits_h{};
-    qw_buf mlog{}, msel{}, Hhi{}, Hlo{}, Pg{};
+    qw_buf mlog{}, msel{}, Hhi{}, Hlo{}, Pg{}, rcnt{};
     size_t sel_bytes = 0;
     // kernels
-    qw_kernel *k_begin, *k_embed, *k_norm, *k_norm0, *k_adv_feed, *k_qmv_in_a, *k_qmv_in_g, *k_qmv_o_a, *k_qmv_o_g, *k_lm, *k_prep, *k_attn, *k_merge, *k_epi, *k_gdn, *k_router, *k_select,
+    qw_kernel *k_begin, *k_embed, *k_norm, *k_norm0, *k_norm_cmb, *k_route, *k_adv_feed, *k_qmv_in_a, *k_qmv_in_g, *k_qmv_o_a, *k_qmv_o_g, *k_lm, *k_prep, *k_attn, *k_merge, *k_epi, *k_gdn, *k_router, *k_select,
         *k_gu, *k_dn, *k_cmb, *k_argmax, *k_adv, *k_fill, *k_ar;
     bool ep_ready = false;
     // bookkeeping
@@ -195,7 +195,7 @@ extern "C" void qw_engine_close(qw_engine *e) {
     if (!e) return;
     qw_buf *all[] = {&e->emb, &e->lm_head, &e->dense, &e->small, &e->router, &e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd, &e->kvpool,
                      &e->ptab, &e->sstate, &e->cstate, &e->ctl_h, &e->ctl_d, &e->h, &e->x, &e->proj, &e->cv, &e->la, &e->be, &e->gy, &e->qb,
-                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg};
+                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt};
     for (qw_buf *b : all) qw_buf_free(b);
     delete e;
 }
@@ -272,7 +272,9 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     std::vector<std::pair<const char *, long>> md = {{"E", e->E}, {"EL", e->EL}, {"D", D}, {"I", e->I}, {"TOPK", e->TOPK},
                                                       {"SHARED", c.ep_rank == 0 ? 1 : 0}, {"RESID", 0}};
     ok = ok && compile(e, "moe_router", "moe_router", md, &e->k_router) && compile(e, "moe_select", "moe_select", md, &e->k_select) &&
-         compile(e, "moe_gu", "moe_gu", md, &e->k_gu) && compile(e, "moe_dn", "moe_dn", md, &e->k_dn) && compile(e, "moe_cmb", "moe_cmb", md, &e->k_cmb);
+         compile(e, "moe_gu", "moe_gu", md, &e->k_gu) && compile(e, "moe_dn", "moe_dn", md, &e->k_dn) && compile(e, "moe_cmb", "moe_cmb", md, &e->k_cmb) &&
+         compile(e, "moe_route", "moe_route", md, &e->k_route) &&
+         compile(e, "add_rmsnorm", "cmb_add_rmsnorm", {{"CMB", 1}, {"TOPK", e->TOPK}}, &e->k_norm_cmb);
     e->k_ar = nullptr;
     if (ok && c.ep_size > 1) ok = compile(e, "ep_allreduce", "ep_allreduce", {}, &e->k_ar);
     if (!ok) {
@@ -302,10 +304,10 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          new_buf(e, &e->logits, B * (size_t)e->V * 4) && new_buf(e, &e->ids, B * 4) && new_buf(e, &e->ids_h, B * 4, QW_BUF_HOSTIO) &&
          new_buf(e, &e->logits_h, B * (size_t)e->V * 4, QW_BUF_HOSTIO) && new_buf(e, &e->mlog, B * (e->E + 1) * 4) &&
          new_buf(e, &e->msel, (size_t)e->L * e->sel_bytes) && new_buf(e, &e->Hhi, B * (e->TOPK + 1) * e->I * 2) &&
-         new_buf(e, &e->Hlo, B * (e->TOPK + 1) * e->I * 2) && new_buf(e, &e->Pg, B * (e->TOPK + 1) * e->D * 4);
+         new_buf(e, &e->Hlo, B * (e->TOPK + 1) * e->I * 2) && new_buf(e, &e->Pg, B * (e->TOPK + 1) * e->D * 4) && new_buf(e, &e->rcnt, 256);
     if (ok) ok = qw_buf_zero(g, &e->msel, 0, e->msel.size) && qw_buf_zero(g, &e->Pg, 0, e->Pg.size) && qw_buf_zero(g, &e->Hhi, 0, e->Hhi.size) &&
                  qw_buf_zero(g, &e->Hlo, 0, e->Hlo.size) && qw_buf_zero(g, &e->ptab, 0, e->ptab.size) &&
-                 qw_buf_zero(g, &e->kvpool, 0, e->kvpool.size);  // rows past a slot's length are multiplied by probability 0: keep them finite
+                 qw_buf_zero(g, &e->kvpool, 0, e->kvpool.size) && qw_buf_zero(g, &e->rcnt, 0, e->rcnt.size);  // rows past a slot's length are multiplied by probability 0: keep them finite
     if (ok) ok = init_weights(e);
     if (!ok) {
         g_open_error = e->err.empty() ? "engine open failed" : e->err;
@@ -415,11 +417,17 @@ void enc_qmv(qw_batch *b, qw_kernel *k, const qw_buf *W, size_t woff, uint32_t N
     qw_batch_dispatch(b, (N + 7) / 8, 1, 1, 256, 1, 1);
 }
 
-void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_floats, uint32_t nb) {
+// h (+)= the previous block's output, x = rmsnorm(h) * w.  delta == &e->Pg means "the MoE combine of layer cmb_layer",
+// computed inside the norm kernel from Pg and that layer's selection record.
+void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_floats, uint32_t nb, int cmb_layer = -1) {
     const uint32_t a[2] = {nb, (uint32_t)e->D};
-    qw_batch_kernel(b, delta ? e->k_norm : e->k_norm0);
+    const bool cmb = delta == &e->Pg;
+    qw_batch_kernel(b, cmb ? e->k_norm_cmb : delta ? e->k_norm : e->k_norm0);
     qw_batch_buf(b, 0, &e->h, 0);
-    qw_batch_buf(b, 1, delta, 0);
+    if (cmb) {
+        qw_batch_buf(b, 5, &e->msel, (size_t)cmb_layer * e->sel_bytes);
+        qw_batch_buf(b, 6, &e->Pg, 0);
+    } else qw_batch_buf(b, 1, delta, 0);
     qw_batch_buf(b, 2, &e->small, w_off_floats * 4);
     qw_batch_buf(b, 3, &e->x, 0);
     qw_batch_bytes(b, 4, a, sizeof a);
@@ -450,7 +458,7 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
     const qw_buf *pending = none;  // block output not yet added to the residual stream
     for (int l = 0; l < e->L; l++) {
         const LayerW &w = e->layers[l];
-        enc_norm(e, b, pending, w.small, nb);  // h += previous block; x = rmsnorm(h) * w1
+        enc_norm(e, b, pending, w.small, nb, l - 1);  // h += previous block (the MoE combine of layer l-1); x = rmsnorm(h) * w1
         if (w.attn) {
             enc_qmv(b, e->k_qmv_in_a, &e->dense, w.w_in, e->qkv_rows, D, &e->x, &e->proj, nb, e->qkv_rows);
             const qsa_args qa = {nb, (uint32_t)w.idx, (uint32_t)e->n_attn, e->qkv_rows, (uint32_t)e->max_pages, max_chunks, 0, 0};
@@ -515,19 +523,16 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
         enc_norm(e, b, &e->ob, w.small + D, nb);  // h += mixer output; x = rmsnorm(h) * w2
         // ---- MoE (gg_moe, src/engine.c:568-646)
         const size_t gu_bytes = (size_t)e->I * e->rbD, ex_bytes = (size_t)e->EL * gu_bytes, selo = (size_t)l * e->sel_bytes;
-        qw_batch_kernel(b, e->k_router);
+        const sel_args sa = {nb, (uint32_t)e->e_lo, (uint32_t)(e->e_lo + e->EL)};
+        qw_batch_kernel(b, e->k_route);  // router logits + top-k + grouping in one launch
         qw_batch_buf(b, 0, &e->router, (size_t)l * (e->E + 1) * D * 2);
         qw_batch_buf(b, 1, &e->router, ((size_t)l * (e->E + 1) + e->E) * D * 2);
         qw_batch_buf(b, 2, &e->x, 0);
         qw_batch_buf(b, 3, &e->mlog, 0);
-        qw_batch_bytes(b, 14, &nb, 4);
-        qw_batch_dispatch(b, (e->E + 1 + 7) / 8, 1, 1, 256, 1, 1);
-        const sel_args sa = {nb, (uint32_t)e->e_lo, (uint32_t)(e->e_lo + e->EL)};
-        qw_batch_kernel(b, e->k_select);
-        qw_batch_buf(b, 0, &e->mlog, 0);
-        qw_batch_buf(b, 1, &e->msel, selo);
-        qw_batch_bytes(b, 2, &sa, sizeof sa);
-        qw_batch_dispatch(b, 1, 1, 1, 1024, 1, 1);
+        qw_batch_buf(b, 4, &e->rcnt, 0);
+        qw_batch_buf(b, 5, &e->msel, selo);
+        qw_batch_bytes(b, 14, &sa, sizeof sa);
+        qw_batch_dispatch(b, (e->E + 1 + 7) / 8, 1, 1, 1024, 1, 1);
         const uint32_t ebase = (uint32_t)e->e_lo;
         qw_batch_kernel(b, e->k_gu);
         qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
@@ -562,15 +567,9 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             qw_batch_bytes(b, 1, &cnt, sizeof cnt);
             qw_batch_dispatch(b, 1, 1, 1, 1, 1, 1);
         }
-        qw_batch_kernel(b, e->k_cmb);
-        qw_batch_buf(b, 3, &e->msel, selo);
-        qw_batch_buf(b, 4, &e->mo, 0);
-        qw_batch_buf(b, 9, &e->Pg, 0);
-        qw_batch_bytes(b, 8, &nb, 4);
-        qw_batch_dispatch(b, D / 256, nb, 1, 256, 1, 1);
-        pending = &e->mo;
+        pending = &e->Pg;  // combined, rounded to fp16 and added to the residual stream inside the next norm kernel
     }
-    enc_norm(e, b, pending, e->final_norm, nb);
+    enc_norm(e, b, pending, e->final_norm, nb, e->L - 1);
     enc_qmv(b, e->k_lm, &e->lm_head, 0, (uint32_t)e->V, D, &e->x, &e->logits, nb, (uint32_t)e->V);
     if (sample) {
         const uint32_t a[2] = {nb, (uint32_t)e->V};

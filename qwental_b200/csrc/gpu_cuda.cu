@@ -14,6 +14,18 @@
 #include <unordered_map>
 #include <vector>
 
+// ------------------------------------------------------------------------------------------------ launch mode
+static int g_pdl = -1;
+bool qw_pdl_enabled() {
+    if (g_pdl < 0) {
+        const char *e = getenv("QW_PDL");
+        g_pdl = e ? (atoi(e) != 0) : 0;
+    }
+    return g_pdl != 0;
+}
+void qw_set_pdl(bool on) { g_pdl = on ? 1 : 0; }
+extern "C" void qw_gpu_set_pdl(qw_gpu *, bool on) { qw_set_pdl(on); }
+
 // ------------------------------------------------------------------------------------------------ registry
 static QwFamily *g_families = nullptr;
 void qw_register_family(QwFamily *f) {
@@ -182,15 +194,8 @@ static bool is_ident(const std::string &s) {
     return true;
 }
 
-extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err, size_t errlen) {
-    auto fail = [&](const std::string &m) {
-        if (err && errlen) snprintf(err, errlen, "%s", m.c_str());
-        if (g) g->err = m;
-        return false;
-    };
-    if (!g || !src) return fail("qw_gpu_compile: null argument");
-    std::string family, entry;
-    QwDefs defs;
+// Parses the `#define` prelude of a kernel source (see qw_gpu_compile in qw_gpu.h).  Pure host logic: no device needed.
+static bool parse_prelude(const char *src, size_t len, std::string &family, std::string &entry, QwDefs &defs, std::string &msg) {
     std::vector<std::pair<std::string, std::string>> idents;
     size_t i = 0;
     while (i < len) {
@@ -204,7 +209,10 @@ extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err
         if (line.compare(a, 7, "#define") != 0) break;  // end of the prelude
         char nm[128] = {0}, val[256] = {0};
         int got = sscanf(line.c_str() + a + 7, " %127s %255[^\n\r]", nm, val);
-        if (got < 1) return fail("qw_gpu_compile: malformed #define: " + line);
+        if (got < 1) {
+            msg = "qw_gpu_compile: malformed #define: " + line;
+            return false;
+        }
         std::string v(val);
         size_t c = v.find("//");
         if (c != std::string::npos) v = v.substr(0, c);
@@ -215,7 +223,8 @@ extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err
         else if (got == 2 && !v.empty()) {
             char *endp = nullptr;
             long num = strtol(v.c_str(), &endp, 0);
-            if (endp && (*endp == 0 || *endp == 'u' || *endp == 'U' || *endp == 'l' || *endp == 'L')) defs.v[name] = num;
+            if (endp && endp != v.c_str() && (*endp == 0 || *endp == 'u' || *endp == 'U' || *endp == 'l' || *endp == 'L')) defs.v[name] = num;
+            else if (name == "YT") defs.v["YT_F32"] = v == "float";  // the reference's output-type define of qmv_gg (kernels/qmv_gg.metal:4-6)
             else if (is_ident(v)) idents.push_back({name, v});
         } else defs.v[name] = 1;
     }
@@ -225,11 +234,45 @@ extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err
             family = p.first;
             if (entry.empty()) entry = p.second;
         }
-    if (family.empty()) return fail("qw_gpu_compile: the prelude names no kernel family (#define QW_KERNEL <family>)");
-    QwFamily *f = find_family(family);
-    if (!f) return fail("qw_gpu_compile: unknown kernel family '" + family + "'");
+    if (family.empty()) {
+        msg = "qw_gpu_compile: the prelude names no kernel family (#define QW_KERNEL <family>)";
+        return false;
+    }
+    if (!find_family(family)) {
+        msg = "qw_gpu_compile: unknown kernel family '" + family + "'";
+        return false;
+    }
     if (entry.empty()) entry = family;
-    if (!is_ident(entry)) return fail("qw_gpu_compile: bad entry name '" + entry + "'");
+    if (!is_ident(entry)) {
+        msg = "qw_gpu_compile: bad entry name '" + entry + "'";
+        return false;
+    }
+    return true;
+}
+
+// Host-logic probe of the prelude parser (no device): writes "family entry NAME=VALUE ..." into out.
+extern "C" bool qw_gpu_prelude_describe(const char *src, size_t len, char *out, size_t outlen) {
+    std::string family, entry, msg;
+    QwDefs defs;
+    const bool ok = src && parse_prelude(src, len, family, entry, defs, msg);
+    std::string r = ok ? family + " " + entry : msg;
+    if (ok)
+        for (auto &kv : defs.v) r += " " + kv.first + "=" + std::to_string(kv.second);
+    if (out && outlen) snprintf(out, outlen, "%s", r.c_str());
+    return ok;
+}
+
+extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err, size_t errlen) {
+    auto fail = [&](const std::string &m) {
+        if (err && errlen) snprintf(err, errlen, "%s", m.c_str());
+        if (g) g->err = m;
+        return false;
+    };
+    if (!g || !src) return fail("qw_gpu_compile: null argument");
+    std::string family, entry, msg;
+    QwDefs defs;
+    if (!parse_prelude(src, len, family, entry, defs, msg)) return fail(msg);
+    QwFamily *f = find_family(family);
     qw_kernel *k = new qw_kernel();
     k->name = entry;
     k->fam = f;

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(256) qsa_prep_k(const __half *qkv, const float
                                                   const int32_t *posv, const int32_t *sids, qsa_args a, uint32_t QH, uint32_t KVH) {
     constexpr uint32_t HD = 256, RD = 64;
     __shared__ float tmp[8], v[HD];
+    pdl_sync();
     const uint32_t hh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t pos = (uint32_t)posv[t];
     const bool isq = hh < QH;
@@ -94,7 +95,7 @@ static cudaError_t launch_qsa_prep(const QwLaunch &L) {
     for (int i = 0; i <= 7; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
     QW_CHECK_ARG(L.avail(0) >= ((size_t)(a.nb - 1) * a.qkv_stride + QH * 2 * HD + 2 * KVH * HD) * 2 && L.avail(3) >= (size_t)a.nb * QH * HD * 2 &&
                  L.avail(6) >= (size_t)a.nb * 4 && L.avail(7) >= (size_t)a.nb * 4 && L.tx == 256);
-    qsa_prep_k<<<dim3(QH + KVH, a.nb), 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<__half>(3), L.buf<__half>(4),
+    qw_launch(qsa_prep_k, dim3(QH + KVH, a.nb), 256, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<__half>(3), L.buf<__half>(4),
                                                           L.buf<int32_t>(5), L.buf<int32_t>(6), L.buf<int32_t>(7), a, QH, KVH);
     return cudaGetLastError();
 }
@@ -110,6 +111,7 @@ QW_FAMILY(qsa_prep, launch_qsa_prep, 256)
 __global__ void __launch_bounds__(256) qsa_attn_k(const __half *q, const __half *pool, const int32_t *pt, const int32_t *posv, const int32_t *sids,
                                                   float *part, qsa_args a, uint32_t QH, uint32_t KVH) {
     constexpr uint32_t HD = 256, PL = 8, U4 = 4;
+    pdl_sync();
     const uint32_t ch = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const uint32_t ntok = (uint32_t)posv[t] + 1;
     if (ch * QSA_PAGE >= ntok) return;
@@ -190,7 +192,7 @@ static cudaError_t launch_qsa_attn(const QwLaunch &L) {
     QW_CHECK_ARG(L.has_bytes(6, 24) && a.nb >= 1 && a.nb <= 64 && a.layer < a.nlayers && a.max_chunks >= 1 && a.max_chunks <= a.max_pages);
     for (int i = 0; i <= 5; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * QH * HD * 2 && L.avail(5) >= (size_t)a.nb * a.max_chunks * QH * (HD + 2) * 4 && L.tx == 256);
-    qsa_attn_k<<<dim3(a.max_chunks, KVH, a.nb), 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<__half>(1), L.buf<int32_t>(2), L.buf<int32_t>(3),
+    qw_launch(qsa_attn_k, dim3(a.max_chunks, KVH, a.nb), 256, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<int32_t>(2), L.buf<int32_t>(3),
                                                                    L.buf<int32_t>(4), L.buf<float>(5), a, QH, KVH);
     return cudaGetLastError();
 }
@@ -225,6 +227,7 @@ __global__ void __launch_bounds__(128) qsa_attn_mma_k(const __grid_constant__ CU
                                                       const int32_t *sids, float *part, qsa_args a, uint32_t QH, uint32_t KVH, unsigned *status) {
     constexpr uint32_t HD = 256;
     extern __shared__ uint8_t smem_raw[];
+    pdl_sync();
     const uint32_t ch = blockIdx.x, kvh = blockIdx.y, ts = blockIdx.z;
     const uint32_t ntok = (uint32_t)posv[ts] + 1;
     if (ch * QSA_PAGE >= ntok) return;
@@ -430,7 +433,7 @@ static cudaError_t launch_qsa_attn_mma(const QwLaunch &L) {
     const size_t smem = 4 * AT_WARP_BYTES + 64 + 1024;
     cudaError_t e = cudaFuncSetAttribute(qsa_attn_mma_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    qsa_attn_mma_k<<<dim3(a.max_chunks, KVH, a.nb), 128, smem, L.stream>>>(*tm, L.buf<__half>(0), L.buf<int32_t>(2), L.buf<int32_t>(3),
+    qw_launch(qsa_attn_mma_k, dim3(a.max_chunks, KVH, a.nb), 128, smem, L.stream, *tm, L.buf<__half>(0), L.buf<int32_t>(2), L.buf<int32_t>(3),
                                                                           L.buf<int32_t>(4), L.buf<float>(5), a, QH, KVH, L.status);
     return cudaGetLastError();
 }
@@ -441,15 +444,16 @@ QW_FAMILY(qsa_attn, launch_qsa_attn_mma, 128)
 // grid (QH, nb) x 256.  The chunk weights exp(m_c - M) are computed once per chunk (thread c), then thread d sums
 // dim d over the slot's chunks in chunk order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.
 #define QSA_MAXCH 1024
-__global__ void __launch_bounds__(256) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
+__global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
     constexpr uint32_t HD = 256;
-    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[8];
-    const uint32_t qh = blockIdx.x, t = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[32], accs[4][HD], ls[4];
+    pdl_sync();
+    const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, d = tid & 255, grp = tid >> 8, lane = tid & 31, warp = tid >> 5;
     const uint32_t ntok = (uint32_t)posv[t] + 1, nch = (ntok + QSA_PAGE - 1) / QSA_PAGE;
     const float *base = part + ((size_t)t * a.max_chunks * QH + qh) * (HD + 2);
     const size_t cstride = (size_t)QH * (HD + 2);
     float mx = -INFINITY;
-    for (uint32_t c = d; c < nch; c += 256) {
+    for (uint32_t c = tid; c < nch; c += 1024) {
         const float pm = base[c * cstride + HD], pl = base[c * cstride + HD + 1];
         wc[c] = pm;
         lc[c] = pl;
@@ -460,19 +464,28 @@ __global__ void __launch_bounds__(256) qsa_merge_k(const float *part, const __ha
     __syncthreads();
     float M = tmp[0];
 #pragma unroll
-    for (int i = 1; i < 8; i++) M = fmaxf(M, tmp[i]);
-    for (uint32_t c = d; c < nch; c += 256) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
+    for (int i = 1; i < 32; i++) M = fmaxf(M, tmp[i]);
+    for (uint32_t c = tid; c < nch; c += 1024) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
     __syncthreads();
+    // four thread groups take the chunks c = grp, grp + 4, ... (each in increasing order); the four partial sums are
+    // then added in group order, so the result depends only on the slot's own chunk count
     float l = 0.f, acc = 0.f;
-#pragma unroll 4
-    for (uint32_t c = 0; c < nch; c++) {
+#pragma unroll 8
+    for (uint32_t c = grp; c < nch; c += 4) {
         const float w = wc[c];
         l = fmaf(lc[c], w, l);
         acc = fmaf(base[c * cstride + d], w, acc);
     }
-    const float g = __half2float(qkv[(size_t)t * a.qkv_stride + qh * 2 * HD + HD + d]);
-    const float o = __half2float(__float2half_rn(acc / l));
-    y[((size_t)t * QH + qh) * HD + d] = __float2half_rn(o * (1.0f / (1.0f + expf(-g))));
+    accs[grp][d] = acc;
+    if (d == 0) ls[grp] = l;
+    __syncthreads();
+    if (tid < HD) {
+        const float at = ((accs[0][d] + accs[1][d]) + accs[2][d]) + accs[3][d];
+        const float lt = ((ls[0] + ls[1]) + ls[2]) + ls[3];
+        const float g = __half2float(qkv[(size_t)t * a.qkv_stride + qh * 2 * HD + HD + d]);
+        const float o = __half2float(__float2half_rn(at / lt));
+        y[((size_t)t * QH + qh) * HD + d] = __float2half_rn(o * (1.0f / (1.0f + expf(-g))));
+    }
 }
 
 static cudaError_t launch_qsa_merge(const QwLaunch &L) {
@@ -482,8 +495,8 @@ static cudaError_t launch_qsa_merge(const QwLaunch &L) {
     QW_CHECK_ARG(L.has_bytes(4, 24) && a.nb >= 1 && a.nb <= 64 && a.max_chunks >= 1 && a.max_chunks <= QSA_MAXCH);
     for (int i = 0; i <= 3; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * a.max_chunks * QH * (HD + 2) * 4 && L.avail(2) >= (size_t)a.nb * QH * HD * 2 &&
-                 L.avail(1) >= ((size_t)(a.nb - 1) * a.qkv_stride + QH * 2 * HD) * 2 && L.tx == 256);
-    qsa_merge_k<<<dim3(QH, a.nb), 256, 0, L.stream>>>(L.buf<float>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<int32_t>(3), a, QH);
+                 L.avail(1) >= ((size_t)(a.nb - 1) * a.qkv_stride + QH * 2 * HD) * 2);
+    qw_launch(qsa_merge_k, dim3(QH, a.nb), 1024, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<int32_t>(3), a, QH);
     return cudaGetLastError();
 }
 QW_FAMILY(qsa_merge, launch_qsa_merge, 256)

@@ -29,6 +29,7 @@ struct dn_epi_args {
 // grid (ceil((C + 2 HV)/256), nb) x 256
 __global__ void __launch_bounds__(256) dn_epi_k(const __half *proj, const float *cw, float *pool, const float *An, const float *dtb, __half *cv,
                                                float *la, float *be, const int32_t *sids, dn_epi_args a, uint32_t C, uint32_t HV) {
+    pdl_sync();
     const uint32_t g = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     const __half *pr = proj + (size_t)t * a.proj_stride;
     if (g < C) {
@@ -61,7 +62,7 @@ static cudaError_t launch_dn_epi(const QwLaunch &L) {
     QW_CHECK_ARG(L.avail(0) >= ((size_t)(a.nb - 1) * a.proj_stride + C + HV * DV + 2 * HV) * 2 && L.avail(1) >= (size_t)C * 16 &&
                  L.avail(5) >= (size_t)a.nb * C * 2 && L.avail(6) >= (size_t)a.nb * HV * 4 && L.avail(7) >= (size_t)a.nb * HV * 4 &&
                  L.avail(8) >= (size_t)a.nb * 4);
-    dn_epi_k<<<dim3((C + 2 * HV + 255) / 256, a.nb), 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3),
+    qw_launch(dn_epi_k, dim3((C + 2 * HV + 255) / 256, a.nb), 256, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3),
                                                                         L.buf<float>(4), L.buf<__half>(5), L.buf<float>(6), L.buf<float>(7),
                                                                         L.buf<int32_t>(8), a, C, HV);
     return cudaGetLastError();
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(512) gdn_fstep_k(const __half *cv, const float
                                                   const float *nw, __half *gy, const int32_t *sids, __half *oo, gdn_args a, uint32_t HK, uint32_t HV) {
     constexpr int DK = 128, DV = 128;
     __shared__ float ks[DK], qs[DK], part[4][DV], red[8];
+    pdl_sync();
     const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c = tid & 127, qr = tid >> 7, lane = tid & 31, warp = tid >> 5;
     const uint32_t hk = TILED ? hv % HK : hv / (HV / HK);
     const uint32_t C = 2 * HK * DK + HV * DV;
@@ -164,10 +166,10 @@ static cudaError_t launch_gdn_fstep(const QwLaunch &L) {
     __half *oo = L.def("O_OUT", 0) ? L.buf<__half>(9) : nullptr;
     if (L.def("O_OUT", 0)) QW_CHECK_ARG(oo && L.avail(9) >= (size_t)a.nb * HV * DV * 2);
     if (tiled)
-        gdn_fstep_k<true><<<grid, 512, 0, L.stream>>>(L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
+        qw_launch(gdn_fstep_k<true>, grid, 512, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
                                                      L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV);
     else
-        gdn_fstep_k<false><<<grid, 512, 0, L.stream>>>(L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
+        qw_launch(gdn_fstep_k<false>, grid, 512, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
                                                       L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV);
     return cudaGetLastError();
 }

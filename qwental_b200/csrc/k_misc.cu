@@ -10,12 +10,14 @@
 //                need no host round trip
 //   qw_fill      zero / counter-based synthetic fill of a buffer (weights of the synthetic model)
 #include "common.cuh"
+#include "moe_sel.h"
 #include "qw_kern.h"
 
 using namespace qw;
 
 // binds: 0 = emb fp16 [V][D], 1 = tok int32 [nb], 2 = h fp32 [nb][D], 3 = {nb, D, V}.  grid (ceil(D/256), nb) x 256
 __global__ void kb_embed_k(const __half *emb, const int32_t *tok, float *h, uint32_t D, uint32_t V) {
+    pdl_sync();
     const uint32_t d = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     if (d >= D) return;
     uint32_t id = (uint32_t)tok[t];
@@ -26,22 +28,42 @@ static cudaError_t launch_kb_embed(const QwLaunch &L) {
     struct { uint32_t nb, D, V; } a = L.bytes<decltype(a)>(3);
     QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && L.buf<void>(2) && L.has_bytes(3, 12) && a.nb >= 1 && a.nb <= 64);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.V * a.D * 2 && L.avail(1) >= a.nb * 4 && L.avail(2) >= (size_t)a.nb * a.D * 4);
-    kb_embed_k<<<dim3((a.D + 255) / 256, a.nb), 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<int32_t>(1), L.buf<float>(2), a.D, a.V);
+    qw_launch(kb_embed_k, dim3((a.D + 255) / 256, a.nb), 256, 0, L.stream, L.buf<__half>(0), L.buf<int32_t>(1), L.buf<float>(2), a.D, a.V);
     return cudaGetLastError();
 }
 QW_FAMILY(kb_embed, launch_kb_embed, 256)
 
 // binds: 0 = h fp32 [nb][D], 1 = delta fp16 [nb][D] (only with ADD defined 1: h is then updated in place),
-// 2 = w fp32 [D], 3 = x out fp16 [nb][D], 4 = {nb, D}.  grid nb x 256
-__global__ void __launch_bounds__(256) add_rmsnorm_k(float *h, const __half *delta, const float *w, __half *x, uint32_t D) {
-    __shared__ float tmp[8];
-    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// 2 = w fp32 [D], 3 = x out fp16 [nb][D], 4 = {nb, D}.  With CMB defined 1 the delta is not read from memory but is
+// the MoE combine of moe_cmb (rank-ordered weighted sum of Pg plus the shared expert, rounded to fp16) computed on
+// the fly: 5 = moe_sel, 6 = Pg fp32 [nb][TOPK+1][D], define TOPK.  grid nb x 256
+template <int MODE>  // 0: norm only, 1: h += delta, 2: h += fp16(combine)
+__global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *delta, const float *w, __half *x, uint32_t D, const moe_sel *ms,
+                                                     const float *Pg, uint32_t topk) {
+    __shared__ float tmp[32];
+    pdl_sync();
+    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
     float *hr = h + (size_t)t * D;
+    float wk[MOE_MAXK];
+    if (MODE == 2) {
+#pragma unroll
+        for (uint32_t s = 0; s < MOE_MAXK; s++) wk[s] = s <= topk ? ms->w[t][s] : 0.f;
+    }
     float ss = 0.f;
-    for (uint32_t d = tid; d < D; d += 256) {
+    for (uint32_t d = tid; d < D; d += nth) {
         float v = hr[d];
-        if (delta) {
+        if (MODE == 1) {
             v += __half2float(delta[(size_t)t * D + d]);
+            hr[d] = v;
+        } else if (MODE == 2) {
+            float pv[MOE_MAXK];  // all loads first (independent), then the rank-ordered chain
+#pragma unroll
+            for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? Pg[((size_t)t * (topk + 1) + s) * D + d] : 0.f;
+            float o = 0.f;
+#pragma unroll
+            for (uint32_t s = 0; s < MOE_MAXK; s++)
+                if (s <= topk) o = fmaf(wk[s], pv[s], o);
+            v += __half2float(__float2half_rn(o));
             hr[d] = v;
         }
         ss = fmaf(v, v, ss);
@@ -50,18 +72,24 @@ __global__ void __launch_bounds__(256) add_rmsnorm_k(float *h, const __half *del
     if (lane == 0) tmp[warp] = ss;
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) tot += tmp[i];
+    for (uint32_t i = 0; i < nth / 32; i++) tot += tmp[i];
     const float r = rsqrtf(tot / D + 1e-6f);
-    for (uint32_t d = tid; d < D; d += 256) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
+    for (uint32_t d = tid; d < D; d += nth) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
 }
 static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
     struct { uint32_t nb, D; } a = L.bytes<decltype(a)>(4);
     QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(2) && L.buf<void>(3) && L.has_bytes(4, 8) && a.nb >= 1 && a.nb <= 64);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * a.D * 4 && L.avail(2) >= (size_t)a.D * 4 && L.avail(3) >= (size_t)a.nb * a.D * 2);
-    const __half *delta = L.def("ADD", 0) ? L.buf<__half>(1) : nullptr;
-    if (L.def("ADD", 0)) QW_CHECK_ARG(delta && L.avail(1) >= (size_t)a.nb * a.D * 2);
-    add_rmsnorm_k<<<a.nb, 256, 0, L.stream>>>(L.buf<float>(0), delta, L.buf<float>(2), L.buf<__half>(3), a.D);
+    if (L.def("CMB", 0)) {
+        const uint32_t topk = (uint32_t)L.def("TOPK", 10);
+        QW_CHECK_ARG(L.buf<void>(5) && L.buf<void>(6) && L.avail(5) >= sizeof(moe_sel) && L.avail(6) >= (size_t)a.nb * (topk + 1) * a.D * 4 && topk < MOE_MAXK);
+        qw_launch(add_rmsnorm_k<2>, a.nb, 1024, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, L.buf<moe_sel>(5), L.buf<float>(6), topk);
+    } else if (L.def("ADD", 0)) {
+        QW_CHECK_ARG(L.buf<void>(1) && L.avail(1) >= (size_t)a.nb * a.D * 2);
+        qw_launch(add_rmsnorm_k<1>, a.nb, 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0);
+    } else {
+        qw_launch(add_rmsnorm_k<0>, a.nb, 512, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0);
+    }
     return cudaGetLastError();
 }
 QW_FAMILY(add_rmsnorm, launch_add_rmsnorm, 256)
@@ -71,6 +99,7 @@ QW_FAMILY(add_rmsnorm, launch_add_rmsnorm, 256)
 __global__ void __launch_bounds__(1024) k_argmax_k(const float *lg, int32_t *ids, int32_t *ids2, uint32_t V) {
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
+    pdl_sync();
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float *r = lg + (size_t)t * V;
     float best = -INFINITY;
@@ -109,13 +138,14 @@ static cudaError_t launch_k_argmax(const QwLaunch &L) {
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * a.V * 4 && L.avail(1) >= a.nb * 4);
     int32_t *ids2 = L.def("IDS2", 0) ? L.buf<int32_t>(3) : nullptr;
     if (L.def("IDS2", 0)) QW_CHECK_ARG(ids2 && L.avail(3) >= a.nb * 4);
-    k_argmax_k<<<a.nb, 1024, 0, L.stream>>>(L.buf<float>(0), L.buf<int32_t>(1), ids2, a.V);
+    qw_launch(k_argmax_k, a.nb, 1024, 0, L.stream, L.buf<float>(0), L.buf<int32_t>(1), ids2, a.V);
     return cudaGetLastError();
 }
 QW_FAMILY(k_argmax, launch_k_argmax, 1024)
 
 // binds: 0 = pos int32 [nb], 3 = {nb}; with FEED defined 1 also 1 = tok int32 [nb], 2 = sampled ids int32 [nb]
 __global__ void par_advance_k(int32_t *pos, int32_t *tok, const int32_t *ids, uint32_t nb) {
+    pdl_sync();
     const uint32_t t = threadIdx.x;
     if (t >= nb) return;
     pos[t] += 1;
@@ -126,7 +156,7 @@ static cudaError_t launch_par_advance(const QwLaunch &L) {
     QW_CHECK_ARG(L.buf<void>(0) && nb >= 1 && nb <= 64 && L.avail(0) >= nb * 4);
     const bool feed = L.def("FEED", 0) != 0;
     if (feed) QW_CHECK_ARG(L.buf<void>(1) && L.buf<void>(2) && L.avail(1) >= nb * 4 && L.avail(2) >= nb * 4);
-    par_advance_k<<<1, 64, 0, L.stream>>>(L.buf<int32_t>(0), feed ? L.buf<int32_t>(1) : nullptr, feed ? L.buf<int32_t>(2) : nullptr, nb);
+    qw_launch(par_advance_k, 1, 64, 0, L.stream, L.buf<int32_t>(0), feed ? L.buf<int32_t>(1) : nullptr, feed ? L.buf<int32_t>(2) : nullptr, nb);
     return cudaGetLastError();
 }
 QW_FAMILY(par_advance, launch_par_advance, 64)
@@ -135,12 +165,13 @@ QW_FAMILY(par_advance, launch_par_advance, 64)
 // copies it into device memory once so that no other kernel reads across PCIe.
 // binds: 0 = source int32, 1 = destination int32, 2 = {count}
 __global__ void par_begin_k(const int32_t *src, int32_t *dst, uint32_t n) {
+    pdl_sync();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
 }
 static cudaError_t launch_par_begin(const QwLaunch &L) {
     const uint32_t n = L.bytes<uint32_t>(2);
     QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && n >= 1 && L.avail(0) >= n * 4 && L.avail(1) >= n * 4);
-    par_begin_k<<<1, 256, 0, L.stream>>>(L.buf<int32_t>(0), L.buf<int32_t>(1), n);
+    qw_launch(par_begin_k, 1, 256, 0, L.stream, L.buf<int32_t>(0), L.buf<int32_t>(1), n);
     return cudaGetLastError();
 }
 QW_FAMILY(par_begin, launch_par_begin, 256)
@@ -171,6 +202,7 @@ __device__ __forceinline__ float hash_normal(uint64_t seed, uint64_t i) {
 }
 
 __global__ void qw_fill_k(uint8_t *dst, fill_args a) {
+    pdl_sync();
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t li = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; li < a.count; li += stride) {
         const uint64_t i = a.base + li;
@@ -201,7 +233,7 @@ static cudaError_t launch_qw_fill(const QwLaunch &L) {
     QW_CHECK_ARG(L.avail(0) >= a.count * esz);
     const uint64_t blocks = (a.count + 255) / 256;
     const unsigned grid = (unsigned)(blocks < (uint64_t)L.sm_count * 32 ? blocks : (uint64_t)L.sm_count * 32);
-    qw_fill_k<<<grid, 256, 0, L.stream>>>(L.buf<uint8_t>(0), a);
+    qw_launch(qw_fill_k, grid, 256, 0, L.stream, L.buf<uint8_t>(0), a);
     return cudaGetLastError();
 }
 QW_FAMILY(qw_fill, launch_qw_fill, 256)

@@ -18,21 +18,7 @@
 
 using namespace qw;
 
-#define MOE_MAXB 64
-#define MOE_MAXK 16
-#define MOE_MAXE 1024
-
-// Result of the selection, read by the gate/up, down and combine kernels (role of struct gg_sel,
-// kernels/moe_gg.metal:110-116).  Groups are in expert-id order; a group's entries are in token order.
-struct moe_sel {
-    uint32_t U;                               // groups (distinct experts in [e_lo, e_hi) that were chosen)
-    uint32_t nb, topk, pad;
-    int32_t ids[MOE_MAXB][MOE_MAXK];          // chosen experts per token, rank order
-    float w[MOE_MAXB][MOE_MAXK + 1];          // routed weights, then the shared gate at [topk]
-    uint32_t ue[MOE_MAXE];                    // expert of group u
-    uint32_t off[MOE_MAXE + 1];               // entries of group u: ent[off[u] .. off[u+1])
-    uint16_t ent[MOE_MAXB * MOE_MAXK];        // token << 8 | rank
-};
+#include "moe_sel.h"
 
 // ------------------------------------------------------------------------------------------------ router
 // logits [nb][E+1] fp32; row E is the shared-expert gate.  One warp per row, lane owns the 8-value chunks
@@ -47,6 +33,7 @@ __global__ void __launch_bounds__(256) moe_router_k(const __half *Wr, const __ha
     uint4 wr[CH];
 #pragma unroll
     for (int c = 0; c < CH; c++) wr[c] = __ldg(w + lane + 32 * c);
+    pdl_sync();  // the router row is static; the tokens are the previous kernel's output
     for (uint32_t t = 0; t < nb; t++) {
         const uint4 *xt = (const uint4 *)(x + (size_t)t * D);
         float acc = 0.f;
@@ -73,8 +60,8 @@ static cudaError_t launch_moe_router(const QwLaunch &L) {
     QW_CHECK_ARG(L.avail(0) >= (size_t)E * D * 2 && L.avail(1) >= (size_t)D * 2 && L.avail(2) >= (size_t)nb * D * 2 &&
                  L.avail(3) >= (size_t)nb * (E + 1) * 4);
     QW_CHECK_ARG(L.tx == 256 && L.gx == (E + 1 + 7) / 8);
-    if (D == 2048) moe_router_k<2048><<<L.gx, 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
-    else if (D == 256) moe_router_k<256><<<L.gx, 256, 0, L.stream>>>(L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
+    if (D == 2048) qw_launch(moe_router_k<2048>, L.gx, 256, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
+    else if (D == 256) qw_launch(moe_router_k<256>, L.gx, 256, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), E, nb);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }
@@ -86,7 +73,9 @@ struct sel_args {
     uint32_t nb, e_lo, e_hi;
 };
 
-__global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
+// Body of the selection for one block of 1024 threads.  Logits are read with .cg loads: in the fused router + select
+// kernel they were written by other blocks of the same launch.
+__device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
     __shared__ uint32_t mlo[MOE_MAXE], mhi[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];  // token bit masks per expert
     __shared__ uint16_t sid[MOE_MAXB * MOE_MAXK];
     __shared__ uint32_t wsum[2][32];
@@ -98,34 +87,37 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
     //    among the lanes holding the maximum wins.
     for (uint32_t t = warp; t < a.nb; t += 32) {
         const float *lg = logits + (size_t)t * (E + 1);
-        float v[32];
+        // Logits as order-preserving unsigned keys (a float's bits with the sign folded), so a maximum is one hardware
+        // warp reduction.  Equal floats give equal keys (a logit is never -0: every dot product starts from +0).
+        uint32_t v[32];
 #pragma unroll
-        for (uint32_t j = 0; j < 32; j++) v[j] = j < PER ? lg[lane + 32 * j] : -INFINITY;
-        float pk = 0.f;
+        for (uint32_t j = 0; j < 32; j++) {
+            const uint32_t u = j < PER ? __float_as_uint(__ldcg(lg + lane + 32 * j)) : 0xff800000u;  // -inf
+            v[j] = u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
+        }
+        uint32_t pkey = 0;
         for (uint32_t k = 0; k < topk; k++) {
-            float b0 = v[0];
-            uint32_t j0 = 0;
+            uint32_t b0 = v[0], j0 = 0;
 #pragma unroll
             for (uint32_t j = 1; j < 32; j++)
                 if (j < PER && v[j] > b0) { b0 = v[j]; j0 = j; }
-            const float m = warp_max(b0);
-            uint32_t id = b0 == m ? lane + 32 * j0 : 0xffffffffu;
-#pragma unroll
-            for (int off = 16; off; off >>= 1) id = min(id, __shfl_xor_sync(0xffffffffu, id, off));
+            const uint32_t m = __reduce_max_sync(0xffffffffu, b0);
+            const uint32_t id = __reduce_min_sync(0xffffffffu, b0 == m ? lane + 32 * j0 : 0xffffffffu);
             if (lane == 0) {
                 ms->ids[t][k] = (int32_t)id;
                 sid[t * MOE_MAXK + k] = (uint16_t)id;
             }
-            if (lane == k) pk = m;
+            if (lane == k) pkey = m;
             const uint32_t bl = id & 31, bj = id >> 5;
 #pragma unroll
-            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == bl && j == bj) ? -INFINITY : v[j];
+            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == bl && j == bj) ? 0u : v[j];  // below every real key
         }
+        const float pk = __uint_as_float(pkey ^ ((pkey >> 31) ? 0x80000000u : 0xffffffffu));
         const float mx = __shfl_sync(0xffffffffu, pk, 0), ex = expf(pk - mx);
         float sm = 0.f;
         for (uint32_t k = 0; k < topk; k++) sm = __fadd_rn(sm, __shfl_sync(0xffffffffu, ex, k));  // rank order
         if (lane < topk) ms->w[t][lane] = ex / sm;
-        if (lane == topk) ms->w[t][topk] = 1.0f / (1.0f + expf(-lg[E]));
+        if (lane == topk) ms->w[t][topk] = 1.0f / (1.0f + expf(-__ldcg(lg + E)));
     }
     __syncthreads();
     // 2. group by expert.  mask[e] = tokens that chose e; an entry's place inside its group is the number of
@@ -181,6 +173,11 @@ __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_se
     }
 }
 
+__global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
+    pdl_sync();
+    moe_select_body(logits, ms, E, topk, a);
+}
+
 static cudaError_t launch_moe_select(const QwLaunch &L) {
     const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
     sel_args a = L.bytes<sel_args>(2);
@@ -188,10 +185,79 @@ static cudaError_t launch_moe_select(const QwLaunch &L) {
     QW_CHECK_ARG(E % 32 == 0 && E <= MOE_MAXE && topk >= 1 && topk < MOE_MAXK && topk <= E && a.nb >= 1 && a.nb <= MOE_MAXB);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * (E + 1) * 4 && L.avail(1) >= sizeof(moe_sel));
     if (a.e_hi > E) a.e_hi = E;
-    moe_select_k<<<1, 1024, 0, L.stream>>>(L.buf<float>(0), L.buf<moe_sel>(1), E, topk, a);
+    qw_launch(moe_select_k, 1, 1024, 0, L.stream, L.buf<float>(0), L.buf<moe_sel>(1), E, topk, a);
     return cudaGetLastError();
 }
 QW_FAMILY(moe_select, launch_moe_select, 1024)
+
+// ------------------------------------------------------------------------------------------------ router + select in one launch
+// The role of moe_pre_gg's hand-over (kernels/moe_gg.metal:574-589): the block that finishes the router last (device
+// counter + fences) runs the selection.  Blocks of 1024 threads: warp = (row blockIdx*8 + warp%8, token group warp/8),
+// each (row, token) dot product is the same single-lane-chain expression as moe_router, so logits are bit-identical.
+// binds: 0 = Wr, 1 = Wsg, 2 = x, 3 = logits, 4 = counter (uint32, zero before the first launch; left zero), 5 = moe_sel,
+// 14 = {nb, e_lo, e_hi}.  grid ceil((E+1)/8) x 1024
+template <int D>
+__global__ void __launch_bounds__(1024) moe_route_k(const __half *Wr, const __half *Wsg, const __half *x, float *logits, unsigned *counter, moe_sel *ms,
+                                                    uint32_t E, uint32_t topk, sel_args a) {
+    constexpr int CH = D / 8 / 32;
+    __shared__ bool last;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = blockIdx.x * 8 + (warp & 7), tg = warp >> 3;
+    pdl_launch();
+    if (r <= E) {
+        const uint4 *w = (const uint4 *)(r < E ? Wr + (size_t)r * D : Wsg);
+        uint4 wr[CH];
+#pragma unroll
+        for (int c = 0; c < CH; c++) wr[c] = __ldg(w + lane + 32 * c);
+        pdl_wait();  // the router row is static; the tokens are the previous kernel's output
+        for (uint32_t t = tg; t < a.nb; t += 4) {
+            const uint4 *xt = (const uint4 *)(x + (size_t)t * D);
+            float acc = 0.f;
+#pragma unroll
+            for (int c = 0; c < CH; c++) {
+                const uint4 xv = __ldg(xt + lane + 32 * c);
+                const uint32_t a4[4] = {wr[c].x, wr[c].y, wr[c].z, wr[c].w}, b4[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 fa = __half22float2(*(const __half2 *)&a4[j]), fb = __half22float2(*(const __half2 *)&b4[j]);
+                    acc = __fmaf_rn(fa.x, fb.x, acc);
+                    acc = __fmaf_rn(fa.y, fb.y, acc);
+                }
+            }
+            const float v = warp_sum_canon(acc);
+            if (lane == 0) logits[(size_t)t * (E + 1) + r] = v;
+        }
+    }
+    pdl_wait();  // (blocks without a row have not waited yet; the selection below reads and writes shared buffers)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last = atomicAdd(counter, 1u) == gridDim.x - 1;
+        __threadfence();
+    }
+    __syncthreads();
+    if (!last) return;
+    moe_select_body(logits, ms, E, topk, a);
+    if (threadIdx.x == 0) *counter = 0;
+}
+
+static cudaError_t launch_moe_route(const QwLaunch &L) {
+    const uint32_t E = (uint32_t)L.def("E", 512), D = (uint32_t)L.def("D", 2048), topk = (uint32_t)L.def("TOPK", 10);
+    sel_args a = L.bytes<sel_args>(14);
+    QW_CHECK_ARG(L.has_bytes(14, 12) && a.nb >= 1 && a.nb <= MOE_MAXB);
+    for (int i = 0; i <= 5; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
+    QW_CHECK_ARG(E % 32 == 0 && E <= MOE_MAXE && topk >= 1 && topk < MOE_MAXK && topk <= E);
+    QW_CHECK_ARG(L.avail(0) >= (size_t)E * D * 2 && L.avail(1) >= (size_t)D * 2 && L.avail(2) >= (size_t)a.nb * D * 2 &&
+                 L.avail(3) >= (size_t)a.nb * (E + 1) * 4 && L.avail(4) >= 4 && L.avail(5) >= sizeof(moe_sel));
+    if (a.e_hi > E) a.e_hi = E;
+    const unsigned grid = (E + 1 + 7) / 8;
+#define GO(DD) qw_launch(moe_route_k<DD>, grid, 1024, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), L.buf<unsigned>(4), L.buf<moe_sel>(5), E, topk, a)
+    if (D == 2048) GO(2048);
+    else if (D == 256) GO(256);
+    else return cudaErrorInvalidValue;
+#undef GO
+    return cudaGetLastError();
+}
+QW_FAMILY(moe_route, launch_moe_route, 1024)
 
 // ------------------------------------------------------------------------------------------------ gate/up and down
 // Persistent blocks of 8 warps; item = (group u, row tile).  Group U (one past the routed groups) is the
@@ -219,14 +285,15 @@ __device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0,
 // contiguous range of items (so consecutive items mostly belong to the same expert) through its own two-stage
 // pipeline of bulk (TMA) copies.  The 64 KB codebook table (16 interleaved copies: conflict-free lookups) is
 // shared by the teams.
-//   gate/up (DOWN = false): item = 16 rows of the gate matrix + the same 16 rows of the up matrix; warp =
-//       (matrix, K-slice of KS = min(4, units)); a warp's UPW units accumulate into one 16 x 8 tile; the KS
-//       partial tiles are summed in slice order, H = silu(g) * u is written as a bf16 high + low pair.
+//   gate/up (DOWN = false): item = 16 rows of the gate matrix + the same 16 rows of the up matrix; warp = K-slice
+//       (one 256-K unit, KS = min(8, units) slices): it multiplies the gate rows and then the up rows of its unit
+//       with the same B fragments; the KS partial tiles of each matrix are summed in slice order,
+//       H = silu(g) * u is written as a bf16 high + low pair.
 //   down (DOWN = true): item = 128 rows; warp = (m-tile mt and mt + 4, K-slice of KS = min(2, units)); the B
 //       operand is the H pair (two MMAs per codebook word); the KS partial tiles are summed in slice order.
 // The B fragments of a warp's units (the token columns of the current expert) stay in registers while
 // consecutive items belong to the same expert.
-template <bool DOWN, int UPW>
+template <bool DOWN>
 __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;  // [team * 2 + stage], [4] = table
@@ -237,17 +304,24 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     const uint32_t tile_bytes = DOWN ? 128 * rb : 2 * 16 * rb, half_bytes = 16 * rb;
     const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
     uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)team * MOE_STG * stage_stride;
-    const uint32_t KS = DOWN ? (units < 2 ? units : 2) : (units < 4 ? units : 4);
-    const uint32_t ks = DOWN ? (warp & 1) : (warp & 3), grp = DOWN ? (warp >> 1) : (warp >> 2);  // grp: m-tile (down) or matrix (gate/up)
+    // down: warp = (m-tile grp, K-slice ks of 2); gate/up: warp = K-slice ks of 8, the same warp does the gate rows and
+    // then the up rows of its unit, so one set of B fragments (32 registers) serves both
+    const uint32_t KS = DOWN ? (units < 2 ? units : 2) : (units < 8 ? units : 8);
+    const uint32_t ks = DOWN ? (warp & 1) : warp, grp = warp >> 1;
     const bool active = ks < KS;
-    const moe_sel *ms = p.ms;
-    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
-    const uint32_t groups = U + (p.Sa ? 1u : 0u), items = groups * p.tiles;
-
+    // independent of earlier kernels: barriers and the codebook table (thread 0 both initialises and uses bars[4] here;
+    // the other threads see the initialised barriers after the __syncthreads below)
+    pdl_launch();
     if (tid == 0) {
         for (int s = 0; s < 5; s++) mbar_init(&bars[s], 1);
         mbar_init_fence();
+        mbar_expect_tx(&bars[4], MOE_TAB_BYTES);
+        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, &bars[4]);
     }
+    pdl_wait();  // the selection record, the tokens / H planes and the outputs belong to earlier kernels
+    const moe_sel *ms = p.ms;
+    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
+    const uint32_t groups = U + (p.Sa ? 1u : 0u);
     // Work units = (group, pass of 8 token columns, row tile), enumerated group-major, then pass, then tile, so that
     // a team's contiguous range keeps one set of B fragments for many consecutive units and every team gets the
     // same number of units whatever the group sizes.  pre[g] = passes of all groups before g.
@@ -311,16 +385,12 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
             bulk_g2s(dst + half_bytes, (u < U ? p.Wb : p.Sb) + o, half_bytes, &full[i % MOE_STG]);
         }
     };
-    if (tid == 0) {
-        mbar_expect_tx(&bars[4], MOE_TAB_BYTES);
-        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, &bars[4]);
-    }
     if (tt == 0) issue(0);
     bool ok = mbar_wait(&bars[4], 0);
     const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
 
     const ZeroRegs zr = zero_regs();
-    uint4 xf[2][8];  // gate/up: [unit job][sub-block]; down: [0] = high plane, [1] = low plane of the warp's unit
+    uint4 xf[DOWN ? 2 : 1][8];  // gate/up: the warp's unit; down: [0] = high plane, [1] = low plane of the warp's unit
     uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
 
     for (uint32_t i = 0; ok && i0 + i < i1; i++) {
@@ -360,11 +430,9 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                         xf[1][ib] = have ? __ldg(lo + 4 * ib) : zero;
                     }
                 } else {
-                    const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + t;
+                    const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
 #pragma unroll
-                    for (int j = 0; j < UPW; j++)
-#pragma unroll
-                        for (int ib = 0; ib < 8; ib++) xf[j][ib] = have ? __ldg(xr + (ks + KS * j) * 32 + 4 * ib) : zero;
+                    for (int ib = 0; ib < 8; ib++) xf[0][ib] = have ? __ldg(xr + 4 * ib) : zero;
                 }
             }
             if (DOWN) {
@@ -398,25 +466,23 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                     }
                 }
             } else {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 if (active) {
 #pragma unroll
-                    for (int j = 0; j < UPW; j++) {
-                        const uint32_t un = ks + KS * j;
-                        if (un < units) {
-                            const uint32_t rows = st + grp * half_bytes + g * rb + un * 110;
-                            unit_mma1<false>(rows, rows + 8 * rb, tabc, t, zr, xf[j], xf[j], acc);
-                        }
+                    for (int j = 0; j < 2; j++) {  // gate rows, then up rows, of unit ks
+                        const uint32_t rows = st + j * half_bytes + g * rb + ks * 110;
+                        unit_mma1<false>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[0], acc[j]);
                     }
                 }
-                red[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+                red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
                 team_sync(team);
                 if (tt < 128) {
                     const int jj = tt & 3, ln = tt >> 2;
                     float gs = 0.f, us = 0.f;
                     for (uint32_t k2 = 0; k2 < KS; k2++) {
-                        gs += ((const float *)&red[k2 * 32 + ln])[jj];
-                        us += ((const float *)&red[(4 + k2) * 32 + ln])[jj];
+                        gs += ((const float *)&red[(k2 * 2 + 0) * 32 + ln])[jj];
+                        us += ((const float *)&red[(k2 * 2 + 1) * 32 + ln])[jj];
                     }
                     const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
                     if (c0 + col < cnt) {
@@ -492,15 +558,15 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     return cudaSuccess;
 }
 
-template <bool DOWN, int UPW>
+template <bool DOWN>
 static cudaError_t moe_ffn_go(const MoeP &p, int sm_count, cudaStream_t st) {
     const uint32_t tile_bytes = DOWN ? 128 * p.rbI : 2 * 16 * p.rbD;
     const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * MOE_STG * ((tile_bytes + 127) & ~127u);
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    auto k = moe_ffn_k<DOWN, UPW>;
+    auto k = moe_ffn_k<DOWN>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    k<<<sm_count, 512, smem, st>>>(p);
+    qw_launch(k, sm_count, 512, smem, st, p);
     return cudaGetLastError();
 }
 
@@ -511,7 +577,7 @@ static cudaError_t launch_moe_gu(const QwLaunch &L) {
     if (e != cudaSuccess) return e;
     const uint32_t units = p.D / 256;
     QW_CHECK_ARG(units == 1 || units == 2 || units == 4 || units == 8);
-    return units == 8 ? moe_ffn_go<false, 2>(p, L.sm_count, L.stream) : moe_ffn_go<false, 1>(p, L.sm_count, L.stream);
+    return moe_ffn_go<false>(p, L.sm_count, L.stream);
 }
 QW_FAMILY(moe_gu, launch_moe_gu, 512)
 
@@ -521,7 +587,7 @@ static cudaError_t launch_moe_dn(const QwLaunch &L) {
     cudaError_t e = moe_fill(L, p, E, topk, true);
     if (e != cudaSuccess) return e;
     QW_CHECK_ARG(p.I / 256 <= 2);
-    return moe_ffn_go<true, 1>(p, L.sm_count, L.stream);
+    return moe_ffn_go<true>(p, L.sm_count, L.stream);
 }
 QW_FAMILY(moe_dn, launch_moe_dn, 512)
 
@@ -531,6 +597,7 @@ QW_FAMILY(moe_dn, launch_moe_dn, 512)
 // updated in place (h += out, the plain residual that stands in for the reference's hyper-connection mix).
 // grid (D/256, nb) x 256
 __global__ void __launch_bounds__(256) moe_cmb_k(const moe_sel *ms, __half *out, const float *Pg, float *resid, uint32_t D, uint32_t topk, uint32_t nb) {
+    pdl_sync();
     const uint32_t row = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     if (row >= D || t >= nb) return;
     float o = 0.f;
@@ -547,7 +614,7 @@ static cudaError_t launch_moe_cmb(const QwLaunch &L) {
     QW_CHECK_ARG(L.avail(3) >= sizeof(moe_sel) && L.avail(4) >= (size_t)nb * D * 2 && L.avail(9) >= (size_t)nb * (topk + 1) * D * 4);
     float *resid = L.def("RESID", 0) ? L.buf<float>(5) : nullptr;
     if (L.def("RESID", 0)) QW_CHECK_ARG(resid && L.avail(5) >= (size_t)nb * D * 4);
-    moe_cmb_k<<<dim3((D + 255) / 256, nb), 256, 0, L.stream>>>(L.buf<moe_sel>(3), L.buf<__half>(4), L.buf<float>(9), resid, D, topk, nb);
+    qw_launch(moe_cmb_k, dim3((D + 255) / 256, nb), 256, 0, L.stream, L.buf<moe_sel>(3), L.buf<__half>(4), L.buf<float>(9), resid, D, topk, nb);
     return cudaGetLastError();
 }
 QW_FAMILY(moe_cmb, launch_moe_cmb, 256)

@@ -50,6 +50,7 @@ __device__ __forceinline__ void dq32(const uint8_t *row, int sub, float *y, cons
 // grid: rows x 32 threads; bytes(2) = {K, row bytes}
 template <int GF>
 __global__ void dq_test_k(const uint8_t *W, float *y, uint32_t K, uint32_t rb, const uint32_t *grid) {
+    pdl_sync();
     const uint32_t r = blockIdx.x, lane = threadIdx.x;
     float v[32];
     for (uint32_t s = lane; s < K / 32; s += 32) {
@@ -65,8 +66,8 @@ static cudaError_t launch_dq_test(const QwLaunch &L) {
     QW_CHECK_ARG((gf == 21 && a.K % 256 == 0) || gf == 8);
     QW_CHECK_ARG(L.avail(0) >= (size_t)L.gx * a.rb && L.avail(1) >= (size_t)L.gx * a.K * 4);
     const uint32_t *grid = ((const QwTables *)L.tables)->grid_u32;
-    if (gf == 21) dq_test_k<21><<<L.gx, 32, 0, L.stream>>>(L.buf<uint8_t>(0), L.buf<float>(1), a.K, a.rb, grid);
-    else dq_test_k<8><<<L.gx, 32, 0, L.stream>>>(L.buf<uint8_t>(0), L.buf<float>(1), a.K, a.rb, grid);
+    if (gf == 21) qw_launch(dq_test_k<21>, L.gx, 32, 0, L.stream, L.buf<uint8_t>(0), L.buf<float>(1), a.K, a.rb, grid);
+    else qw_launch(dq_test_k<8>, L.gx, 32, 0, L.stream, L.buf<uint8_t>(0), L.buf<float>(1), a.K, a.rb, grid);
     return cudaGetLastError();
 }
 QW_FAMILY(dq_test, launch_dq_test, 32)
@@ -77,6 +78,7 @@ QW_FAMILY(dq_test, launch_dq_test, 32)
 // oracle.  Tokens are processed 8 at a time (the decoded segment is reused for the 8).
 template <int GF, bool F32OUT>
 __global__ void __launch_bounds__(256) qmv_gg_k(const uint8_t *W, const __half *x, void *y, qmv_args a, uint32_t K, uint32_t rb, const uint32_t *grid) {
+    pdl_sync();
     const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= a.N) return;
     const uint8_t *wr = W + (size_t)row * rb;
@@ -146,7 +148,7 @@ static cudaError_t launch_qmv_gg(const QwLaunch &L) {
     const uint8_t *W = L.buf<uint8_t>(0);
     const __half *x = L.buf<__half>(3);
     void *y = L.buf<void>(4);
-#define GO(G, F) qmv_gg_k<G, F><<<L.gx, 256, 0, L.stream>>>(W, x, y, a, K, rb, grid)
+#define GO(G, F) qw_launch(qmv_gg_k<G, F>, L.gx, 256, 0, L.stream, W, x, y, a, K, rb, grid)
     if (gf == 21) { if (f32) GO(21, true); else GO(21, false); }
     else { if (f32) GO(8, true); else GO(8, false); }
 #undef GO
@@ -202,6 +204,7 @@ __global__ void __launch_bounds__(256) qmv_mma_k(const QmvMmaP p) {
     if (tid == 0)
         for (uint32_t j = 0; j < QMV_STAGES - 1; j++) issue(j);
 
+    pdl_sync();  // the weight tiles above do not depend on earlier kernels; the activations and the output do
     // activation rows of this lane's columns
     const uint4 *xcol[NT], *xlo[NT];
 #pragma unroll
@@ -267,7 +270,7 @@ static cudaError_t qmv_mma_go(const QmvMmaP &p, int sm_count, cudaStream_t st) {
     if (occ > 4) occ = 4;
     const uint32_t cap = (uint32_t)(sm_count * occ);
     const uint32_t grid = p.items < cap ? p.items : cap;
-    k<<<grid, 256, smem, st>>>(p);
+    qw_launch(k, grid, 256, smem, st, p);
     return cudaGetLastError();
 }
 
@@ -279,6 +282,108 @@ static cudaError_t qmv_mma_nt(const QmvMmaP &p, int sm, cudaStream_t st) {
     return qmv_mma_go<GF, 8, MT, F32OUT>(p, sm, st);
 }
 
+// ---- IQ3_S variant used for the dense projections: one warp per 256-K unit of the tile (8 warps at K = 2048, 16 at
+// K = 4096), the activations' B fragments of up to 16 tokens held in registers for the whole kernel (they are
+// loaded while the first tile is still in flight), decode through the shared-space path of unit_mma1 with a
+// 4-copy codebook (16 KB).  More than 16 tokens run as passes of 16 over the staged tile.
+template <int GF, int WARPS, bool F32OUT>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) qmv_mma2_k(const QmvMmaP p) {
+    constexpr int NT = 2, TS = 32, STG = GF == 8 ? 2 : QMV_STAGES, UB = GF == 21 ? 110 : 272;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = (uint64_t *)smem;
+    uint2 *tab = (uint2 *)(smem + 64);                             // [512][4]
+    float4 *red = (float4 *)(smem + 64 + 16384);                   // [2][WARPS][NT][32]
+    uint8_t *stage0 = smem + 64 + 16384 + 2 * WARPS * NT * 32 * 16;
+    const uint32_t tile_bytes = 16 * p.rb, stage_stride = (tile_bytes + 127) & ~127u;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    if (tid == 0) {
+        for (int s = 0; s < STG; s++) mbar_init(&bars[s], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    const uint32_t first = blockIdx.x, step = gridDim.x;
+    auto issue = [&](uint32_t j) {
+        const uint32_t item = first + j * step;
+        if (item >= p.items) return;
+        const int s = j % STG;
+        mbar_expect_tx(&bars[s], tile_bytes);
+        bulk_g2s(stage0 + (size_t)s * stage_stride, p.W + (size_t)item * tile_bytes, tile_bytes, &bars[s]);
+    };
+    if (tid == 0)
+        for (uint32_t j = 0; j < STG - 1; j++) issue(j);
+    if (GF == 21)
+        for (int e = tid; e < 512 * 4; e += WARPS * 32) tab[e] = p.tab->grid_h4[(e >> 2) * 16 + (e & 3)];
+    const uint32_t tabc = smem_u32(tab) + (lane & 3) * 8;
+    const ZeroRegs zr = zero_regs();
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 xf[NT][8];
+    auto load_x = [&](uint32_t c0) {  // columns c0 + g and c0 + 8 + g of this warp's unit
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const uint32_t col = c0 + g + 8 * nt;
+            const uint4 *xr = (const uint4 *)(p.x + (size_t)col * p.xstride) + warp * 32 + t;
+#pragma unroll
+            for (int ib = 0; ib < 8; ib++) xf[nt][ib] = col < p.nb ? __ldg(xr + 4 * ib) : zero;
+        }
+    };
+    pdl_sync();  // weight tiles and the codebook are static; the activations (and the output buffer) are not
+    load_x(0);
+    __syncthreads();  // table ready
+    const uint32_t passes = (p.nb + 15) / 16;
+    bool ok = true;
+    uint32_t rb_i = 0;  // alternating reduce buffer
+    for (uint32_t j = 0; ok; j++) {
+        const uint32_t item = first + j * step;
+        if (item >= p.items) break;
+        if (tid == 0) issue(j + STG - 1);
+        const int s = j % STG;
+        if (!mbar_wait(&bars[s], (j / STG) & 1)) {
+            ok = false;
+            break;
+        }
+        const uint32_t rows = smem_u32(stage0) + s * stage_stride + g * p.rb + warp * UB;
+        for (uint32_t ps = 0; ps < passes; ps++) {
+            if (passes > 1) load_x(ps * 16);
+            float acc[NT][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            if (GF == 21) unit_mma2<TS>(rows, rows + 8 * p.rb, tabc, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
+            else unit_mma2_q8(rows, rows + 8 * p.rb, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
+            float4 *rd = red + rb_i * WARPS * NT * 32;
+            rb_i ^= 1;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) rd[(warp * NT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
+            __syncthreads();  // partial tiles visible; on the last pass every warp is also done with stage s
+            for (int e = tid; e < NT * 32 * 4; e += WARPS * 32) {
+                const int jj = e & 3, ln = (e >> 2) & 31, nt = e >> 7;
+                float sum = 0.f;
+#pragma unroll
+                for (int k2 = 0; k2 < WARPS; k2++) sum += ((const float *)&rd[(k2 * NT + nt) * 32 + ln])[jj];
+                const uint32_t row = item * 16 + (ln >> 2) + 8 * (jj >> 1), col = ps * 16 + nt * 8 + 2 * (ln & 3) + (jj & 1);
+                if (col < p.nb && row < p.N) {
+                    if (F32OUT) ((float *)p.y)[(size_t)col * p.ystride + row] = sum;
+                    else ((__half *)p.y)[(size_t)col * p.ystride + row] = __float2half_rn(sum);
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 5);
+}
+
+template <int GF, int WARPS, bool F32OUT>
+static cudaError_t qmv_mma2_go(const QmvMmaP &p, int sm_count, cudaStream_t st) {
+    const uint32_t tile_bytes = 16 * p.rb;
+    const size_t smem = 64 + 16384 + (size_t)2 * WARPS * 2 * 32 * 16 + (size_t)(GF == 8 ? 2 : QMV_STAGES) * ((tile_bytes + 127) & ~127u);
+    auto k = qmv_mma2_k<GF, WARPS, F32OUT>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    int occ = 1;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, WARPS * 32, smem);
+    if (e != cudaSuccess) return e;
+    occ = occ < 1 ? 1 : occ > 4 ? 4 : occ;
+    const uint32_t cap = (uint32_t)(sm_count * occ), grid = p.items < cap ? p.items : cap;
+    qw_launch(k, grid, WARPS * 32, smem, st, p);
+    return cudaGetLastError();
+}
+
 // The grid given by the host is ignored (the kernel is persistent: one block per SM); block size must be 256.
 static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     qmv_args a;
@@ -286,7 +391,7 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     uint32_t K, rb;
     bool f32;
     QW_CHECK_ARG(qmv_common_check(L, a, gf, K, rb, f32));
-    QW_CHECK_ARG(L.tx == 256);
+    QW_CHECK_ARG(L.tx == 256 || L.tx == 512);
     // rows per item: fixed by the matrix shape alone (never by the batch), so results do not depend on nb
     const int mt = 1;
     QW_CHECK_ARG(a.N % (16 * mt) == 0 && ((uintptr_t)L.buf<uint8_t>(0) & 15) == 0 && (16 * rb) % 16 == 0);
@@ -300,6 +405,9 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     p.items = a.N / (16 * mt);
 #define GO(G, M)                                                        \
     return f32 ? qmv_mma_nt<G, M, true>(p, L.sm_count, L.stream) : qmv_mma_nt<G, M, false>(p, L.sm_count, L.stream)
+    if (gf == 21 && K == 2048) return f32 ? qmv_mma2_go<21, 8, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 8, false>(p, L.sm_count, L.stream);
+    if (gf == 21 && K == 4096) return f32 ? qmv_mma2_go<21, 16, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 16, false>(p, L.sm_count, L.stream);
+    if (gf == 8 && K == 2048) return f32 ? qmv_mma2_go<8, 8, true>(p, L.sm_count, L.stream) : qmv_mma2_go<8, 8, false>(p, L.sm_count, L.stream);
     if (gf == 21) GO(21, 1);
     else GO(8, 1);
 #undef GO

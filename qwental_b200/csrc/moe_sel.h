@@ -1,0 +1,20 @@
+// Selection record shared by the MoE kernels and the fused combine + norm kernel.
+#pragma once
+#include <stdint.h>
+
+#define MOE_MAXB 64
+#define MOE_MAXK 16
+#define MOE_MAXE 1024
+
+// Result of the selection, read by the gate/up, down and combine kernels (role of struct gg_sel,
+// kernels/moe_gg.metal:110-116).  Groups are in expert-id order; a group's entries are in token order.
+struct moe_sel {
+    uint32_t U;                               // groups (distinct experts in [e_lo, e_hi) that were chosen)
+    uint32_t nb, topk, pad;
+    int32_t ids[MOE_MAXB][MOE_MAXK];          // chosen experts per token, rank order
+    float w[MOE_MAXB][MOE_MAXK + 1];          // routed weights, then the shared gate at [topk]
+    uint32_t ue[MOE_MAXE];                    // expert of group u
+    uint32_t off[MOE_MAXE + 1];               // entries of group u: ent[off[u] .. off[u+1])
+    uint16_t ent[MOE_MAXB * MOE_MAXK];        // token << 8 | rank
+};
+

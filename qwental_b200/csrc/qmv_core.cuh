@@ -173,7 +173,7 @@ __device__ __forceinline__ Iq3sHdr iq3s_hdr(uint32_t blk, int t) {
 }
 // Codebook index = qs byte | high bit << 8, assembled by one byte permute: byte 0 from qs, byte 1 = the 0/1 byte of
 // the header word, bytes 2-3 = the upper bytes of the zero-extended 16-bit qs load (always zero).
-template <int IB>
+template <int IB, int TS>  // TS = bytes between consecutive codebook entries (8 x copies)
 __device__ __forceinline__ float iq3s_sub_h(uint32_t blk_t, uint32_t blk_s, const Iq3sHdr &h, uint32_t tabc, uint32_t (&w)[4]) {
     constexpr uint32_t k = IB & 3;
     constexpr uint32_t selA = (3u << 12) | (2u << 8) | ((4 + k) << 4) | 0;
@@ -182,7 +182,7 @@ __device__ __forceinline__ float iq3s_sub_h(uint32_t blk_t, uint32_t blk_s, cons
     const uint32_t sg = lds_u8<74 + 4 * IB>(blk_s);
     const uint32_t i0 = __byte_perm(qs, IB < 4 ? h.qa0 : h.qa1, selA);
     const uint32_t i1 = __byte_perm(qs, IB < 4 ? h.qb0 : h.qb1, selB);
-    const uint2 g0 = lds_v2(tabc + i0 * 128), g1 = lds_v2(tabc + i1 * 128);
+    const uint2 g0 = lds_v2(tabc + i0 * TS), g1 = lds_v2(tabc + i1 * TS);
     w[0] = g0.x ^ ((sg * 0x40008000u) & 0x80008000u);
     w[1] = g0.y ^ ((sg * 0x10002000u) & 0x80008000u);
     w[2] = g1.x ^ ((sg * 0x04000800u) & 0x80008000u);
@@ -202,12 +202,12 @@ __device__ __forceinline__ ZeroRegs zero_regs() {
     return r;
 }
 
-template <bool BF16, int IB>
+template <bool BF16, int IB, int TS>
 __device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr,
                                          const uint4 &xv, const uint4 &xl, float (&acc)[4]) {
     uint32_t wa[4], wb[4];
-    const float dba = iq3s_sub_h<IB>(u0 + 2 * t, u0 + t, h0, tabc, wa);
-    const float dbb = iq3s_sub_h<IB>(u1 + 2 * t, u1 + t, h1, tabc, wb);
+    const float dba = iq3s_sub_h<IB, TS>(u0 + 2 * t, u0 + t, h0, tabc, wa);
+    const float dbb = iq3s_sub_h<IB, TS>(u1 + 2 * t, u1 + t, h1, tabc, wb);
     const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
     const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
     float p[4];
@@ -229,18 +229,121 @@ __device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const 
 // One IQ3_S unit (rows g and g+8 at shared addresses u0 / u1) against the cached B fragments of one column tile.
 // d*(1+2s) is evaluated as fma(2d, s, d): both forms are exact products of a half-precision d and an odd integer
 // below 32, so they give the same fp32 value.
-template <bool BF16>
+template <bool BF16, int TS = 128>
 __device__ __forceinline__ void unit_mma1(uint32_t u0, uint32_t u1, uint32_t tabc, int t, const ZeroRegs &zr, const uint4 (&xf)[8], const uint4 (&xl)[8],
                                           float (&acc)[4]) {
     const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
-    sub_mma1<BF16, 0>(u0, u1, t, h0, h1, tabc, zr, xf[0], xl[0], acc);
-    sub_mma1<BF16, 1>(u0, u1, t, h0, h1, tabc, zr, xf[1], xl[1], acc);
-    sub_mma1<BF16, 2>(u0, u1, t, h0, h1, tabc, zr, xf[2], xl[2], acc);
-    sub_mma1<BF16, 3>(u0, u1, t, h0, h1, tabc, zr, xf[3], xl[3], acc);
-    sub_mma1<BF16, 4>(u0, u1, t, h0, h1, tabc, zr, xf[4], xl[4], acc);
-    sub_mma1<BF16, 5>(u0, u1, t, h0, h1, tabc, zr, xf[5], xl[5], acc);
-    sub_mma1<BF16, 6>(u0, u1, t, h0, h1, tabc, zr, xf[6], xl[6], acc);
-    sub_mma1<BF16, 7>(u0, u1, t, h0, h1, tabc, zr, xf[7], xl[7], acc);
+    sub_mma1<BF16, 0, TS>(u0, u1, t, h0, h1, tabc, zr, xf[0], xl[0], acc);
+    sub_mma1<BF16, 1, TS>(u0, u1, t, h0, h1, tabc, zr, xf[1], xl[1], acc);
+    sub_mma1<BF16, 2, TS>(u0, u1, t, h0, h1, tabc, zr, xf[2], xl[2], acc);
+    sub_mma1<BF16, 3, TS>(u0, u1, t, h0, h1, tabc, zr, xf[3], xl[3], acc);
+    sub_mma1<BF16, 4, TS>(u0, u1, t, h0, h1, tabc, zr, xf[4], xl[4], acc);
+    sub_mma1<BF16, 5, TS>(u0, u1, t, h0, h1, tabc, zr, xf[5], xl[5], acc);
+    sub_mma1<BF16, 6, TS>(u0, u1, t, h0, h1, tabc, zr, xf[6], xl[6], acc);
+    sub_mma1<BF16, 7, TS>(u0, u1, t, h0, h1, tabc, zr, xf[7], xl[7], acc);
+}
+
+// Two column tiles (16 tokens) against one decode of the unit (fp16 activations).
+template <int IB, int TS>
+__device__ __forceinline__ void sub_mma2(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr,
+                                         const uint4 &xa, const uint4 &xb, bool second, float (&acc)[2][4]) {
+    uint32_t wa[4], wb[4];
+    const float dba = iq3s_sub_h<IB, TS>(u0 + 2 * t, u0 + t, h0, tabc, wa);
+    const float dbb = iq3s_sub_h<IB, TS>(u1 + 2 * t, u1 + t, h1, tabc, wb);
+    const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+    const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+    float p[4];
+    mma_f16(p, a0, xa.x, xa.y, zr.z);
+    mma_f16(p, a1, xa.z, xa.w, p);
+    acc[0][0] = fmaf(dba, p[0], acc[0][0]);
+    acc[0][1] = fmaf(dba, p[1], acc[0][1]);
+    acc[0][2] = fmaf(dbb, p[2], acc[0][2]);
+    acc[0][3] = fmaf(dbb, p[3], acc[0][3]);
+    if (second) {  // warp-uniform
+        float r[4];
+        mma_f16(r, a0, xb.x, xb.y, zr.z);
+        mma_f16(r, a1, xb.z, xb.w, r);
+        acc[1][0] = fmaf(dba, r[0], acc[1][0]);
+        acc[1][1] = fmaf(dba, r[1], acc[1][1]);
+        acc[1][2] = fmaf(dbb, r[2], acc[1][2]);
+        acc[1][3] = fmaf(dbb, r[3], acc[1][3]);
+    }
+}
+template <int TS>
+__device__ __forceinline__ void unit_mma2(uint32_t u0, uint32_t u1, uint32_t tabc, int t, const ZeroRegs &zr, const uint4 (&xa)[8], const uint4 (&xb)[8],
+                                          bool second, float (&acc)[2][4]) {
+    const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
+    sub_mma2<0, TS>(u0, u1, t, h0, h1, tabc, zr, xa[0], xb[0], second, acc);
+    sub_mma2<1, TS>(u0, u1, t, h0, h1, tabc, zr, xa[1], xb[1], second, acc);
+    sub_mma2<2, TS>(u0, u1, t, h0, h1, tabc, zr, xa[2], xb[2], second, acc);
+    sub_mma2<3, TS>(u0, u1, t, h0, h1, tabc, zr, xa[3], xb[3], second, acc);
+    sub_mma2<4, TS>(u0, u1, t, h0, h1, tabc, zr, xa[4], xb[4], second, acc);
+    sub_mma2<5, TS>(u0, u1, t, h0, h1, tabc, zr, xa[5], xb[5], second, acc);
+    sub_mma2<6, TS>(u0, u1, t, h0, h1, tabc, zr, xa[6], xb[6], second, acc);
+    sub_mma2<7, TS>(u0, u1, t, h0, h1, tabc, zr, xa[7], xb[7], second, acc);
+}
+
+// Q8_0 through the same shared-space path: unit = eight 34-byte blocks of a row (src/ggml_dq.c:34-37).  The thread's
+// eight int8 values of block IB sit at byte 34*IB + 2 + 8t: 4-byte aligned for odd IB (two 32-bit loads), 2-byte aligned
+// for even IB (four 16-bit loads).  (q ^ 0x80) | 0x6400 is the half 1024 + (q + 128); subtracting 1152 is exact.
+template <int IB>
+__device__ __forceinline__ float q8_sub_h(uint32_t row_t, uint32_t row, uint32_t (&w)[4]) {
+    uint32_t lo, hi;
+    if (IB & 1) {
+        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(lo) : "r"(row_t), "n"(34 * IB + 2));
+        asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(hi) : "r"(row_t), "n"(34 * IB + 6));
+    } else {
+        lo = lds_u16<34 * IB + 2>(row_t) | (lds_u16<34 * IB + 4>(row_t) << 16);
+        hi = lds_u16<34 * IB + 6>(row_t) | (lds_u16<34 * IB + 8>(row_t) << 16);
+    }
+    lo ^= 0x80808080u;
+    hi ^= 0x80808080u;
+    const uint32_t bias = 0x64806480u;
+    const __half2 b2 = *(const __half2 *)&bias;
+    const uint32_t v[4] = {__byte_perm(lo, 0x64646464u, 0x4140), __byte_perm(lo, 0x64646464u, 0x4342), __byte_perm(hi, 0x64646464u, 0x4140),
+                           __byte_perm(hi, 0x64646464u, 0x4342)};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const __half2 r = __hsub2(*(const __half2 *)&v[j], b2);
+        w[j] = *(const uint32_t *)&r;
+    }
+    return h2f((uint16_t)lds_u16<34 * IB>(row));
+}
+template <int IB>
+__device__ __forceinline__ void sub_mma2_q8(uint32_t u0, uint32_t u1, int t, const ZeroRegs &zr, const uint4 &xa, const uint4 &xb, bool second,
+                                            float (&acc)[2][4]) {
+    uint32_t wa[4], wb[4];
+    const float dba = q8_sub_h<IB>(u0 + 8 * t, u0, wa);
+    const float dbb = q8_sub_h<IB>(u1 + 8 * t, u1, wb);
+    const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+    const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+    float p[4];
+    mma_f16(p, a0, xa.x, xa.y, zr.z);
+    mma_f16(p, a1, xa.z, xa.w, p);
+    acc[0][0] = fmaf(dba, p[0], acc[0][0]);
+    acc[0][1] = fmaf(dba, p[1], acc[0][1]);
+    acc[0][2] = fmaf(dbb, p[2], acc[0][2]);
+    acc[0][3] = fmaf(dbb, p[3], acc[0][3]);
+    if (second) {
+        float r[4];
+        mma_f16(r, a0, xb.x, xb.y, zr.z);
+        mma_f16(r, a1, xb.z, xb.w, r);
+        acc[1][0] = fmaf(dba, r[0], acc[1][0]);
+        acc[1][1] = fmaf(dba, r[1], acc[1][1]);
+        acc[1][2] = fmaf(dbb, r[2], acc[1][2]);
+        acc[1][3] = fmaf(dbb, r[3], acc[1][3]);
+    }
+}
+__device__ __forceinline__ void unit_mma2_q8(uint32_t u0, uint32_t u1, int t, const ZeroRegs &zr, const uint4 (&xa)[8], const uint4 (&xb)[8], bool second,
+                                             float (&acc)[2][4]) {
+    sub_mma2_q8<0>(u0, u1, t, zr, xa[0], xb[0], second, acc);
+    sub_mma2_q8<1>(u0, u1, t, zr, xa[1], xb[1], second, acc);
+    sub_mma2_q8<2>(u0, u1, t, zr, xa[2], xb[2], second, acc);
+    sub_mma2_q8<3>(u0, u1, t, zr, xa[3], xb[3], second, acc);
+    sub_mma2_q8<4>(u0, u1, t, zr, xa[4], xb[4], second, acc);
+    sub_mma2_q8<5>(u0, u1, t, zr, xa[5], xb[5], second, acc);
+    sub_mma2_q8<6>(u0, u1, t, zr, xa[6], xb[6], second, acc);
+    sub_mma2_q8<7>(u0, u1, t, zr, xa[7], xb[7], second, acc);
 }
 
 __host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }

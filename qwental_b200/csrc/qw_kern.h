@@ -63,6 +63,28 @@ struct QwTables {
 };
 cudaError_t qw_tables_create(void **out, cudaStream_t s);
 
+// Kernel launch used by every family.  With programmatic dependent launch enabled (QW_PDL=1 or qw_set_pdl) the launch
+// carries the programmatic-stream-serialization attribute: the kernel may start while its predecessor in the stream is
+// still finishing, runs its data-independent prologue (barrier set-up, lookup tables, staging of weights) and blocks in
+// pdl_wait() (common.cuh) until the predecessor's results are complete and visible.  Every kernel of this library
+// calls pdl_wait() before it reads or writes anything a predecessor may touch.
+bool qw_pdl_enabled();
+void qw_set_pdl(bool on);
+template <typename... KArgs, typename... Args>
+static inline cudaError_t qw_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = qw_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define QW_CHECK_ARG(cond)                         \
     do {                                           \
         if (!(cond)) return cudaErrorInvalidValue; \

@@ -52,6 +52,8 @@ class MoeLayer:
         d = dict(E=E, D=D, I=I, TOPK=topk, SHARED=int(Sg is not None))
         self.k_router = gpu.compile("moe_router", "moe_router" + tag, **d)
         self.k_select = gpu.compile("moe_select", "moe_select" + tag, **d)
+        self.k_route = gpu.compile("moe_route", "moe_route" + tag, **d)
+        self.route_cnt = gpu.buf(256).zero()
         self.k_gu = gpu.compile("moe_gu", "moe_gu" + tag, **d)
         self.k_dn = gpu.compile("moe_dn", "moe_dn" + tag, **d)
         self.k_cmb = gpu.compile("moe_cmb", "moe_cmb" + tag, RESID=0, **d)
@@ -62,11 +64,19 @@ class MoeLayer:
         self.Hlo = gpu.buf(MOE_MAXB * (topk + 1) * I * 2).zero()
         self.Pg = gpu.buf(MOE_MAXB * (topk + 1) * D * 4).zero()
 
-    def encode(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None = None):
+    def encode(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None = None, fused_route: bool = False):
         E, D, I = self.E, self.D, self.I
+        if fused_route:  # router + selection in one launch (what the engine uses)
+            b.kernel(self.k_route).buf(0, self.Wr).buf(1, self.Wsg).buf(2, x).buf(3, self.logits).buf(4, self.route_cnt).buf(5, self.sel) \
+                .bytes(14, u32(nb, self.e_lo, self.e_hi)).dispatch(((E + 1 + 7) // 8,), (1024,))
+            return self._encode_ffn(b, x, out, nb, resid)
         b.kernel(self.k_router).buf(0, self.Wr).buf(1, self.Wsg).buf(2, x).buf(3, self.logits).bytes(14, u32(nb)) \
             .dispatch(((E + 1 + 7) // 8,), (256,))
         b.kernel(self.k_select).buf(0, self.logits).buf(1, self.sel).bytes(2, u32(nb, self.e_lo, self.e_hi)).dispatch((1,), (1024,))
+        self._encode_ffn(b, x, out, nb, resid)
+
+    def _encode_ffn(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None):
+        D, I = self.D, self.I
         b.kernel(self.k_gu).buf(0, self.Wg).buf(1, self.Wu)
         if self.Sg is not None:
             b.buf(2, self.Sg).buf(3, self.Su)

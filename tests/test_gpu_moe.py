@@ -42,11 +42,11 @@ def make_layer(gpu, E, D, I, topk, seed, shared=True, e_lo=0, e_hi=None):
     return layer, h, b
 
 
-def run_layer(gpu, layer, x):
+def run_layer(gpu, layer, x, fused_route=False):
     nb = x.shape[0]
     xb, ob = gpu.buf_from(x), gpu.buf(nb * layer.D * 2).zero()
     bt = gpu.batch()
-    layer.encode(bt, xb, ob, nb)
+    layer.encode(bt, xb, ob, nb, fused_route=fused_route)
     bt.end()
     return ob.download(np.float16, nb * layer.D).reshape(nb, layer.D)
 
@@ -120,3 +120,27 @@ def test_moe_expert_range_partitions_the_work(gpu):
         acc[:, :topk] += pg[:, :topk]
         acc[:, topk] = pg[:, topk]
     assert np.array_equal(acc.view(np.uint32), pg_full.view(np.uint32))
+
+
+@pytest.mark.parametrize("B", [1, 16, 64])
+def test_fused_router_select_equals_two_launches(gpu, B):
+    """moe_route (router + selection in one launch, last block selects) gives the same logits, selection record and
+    layer output, bit for bit, as moe_router followed by moe_select -- also when launched repeatedly (the hand-over
+    counter must be left at zero)."""
+    D, I, topk, E = 2048, 512, 10, 64
+    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=21)
+    x = synth.acts_fp16(np.random.default_rng(B + 5), B, D)
+    out = run_layer(gpu, layer, x)
+    lg, sel = layer.read_logits(B).copy(), layer.sel.download(np.uint8, layer.sel.size).copy()
+    for _ in range(3):
+        layer.sel.zero()
+        layer.logits.zero()
+        out2 = run_layer(gpu, layer, x, fused_route=True)
+        assert np.array_equal(layer.read_logits(B).view(np.uint32), lg.view(np.uint32))
+        got = layer.sel.download(np.uint8, layer.sel.size)
+        U, ids, w, ue, off, ent = layer.read_sel(B)
+        n = 16 + 64 * 16 * 4 + 64 * 17 * 4
+        ref_ids = sel[16:16 + 64 * 16 * 4].view(np.int32).reshape(64, 16)[:B, :topk]
+        assert np.array_equal(ids, ref_ids)
+        assert np.array_equal(got[n:n + 4 * U], sel[n:n + 4 * U]) and got[:4].view(np.uint32)[0] == sel[:4].view(np.uint32)[0]
+        assert np.array_equal(out2.view(np.uint16), out.view(np.uint16))
