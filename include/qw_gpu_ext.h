@@ -38,6 +38,25 @@ void qw_gpu_set_graphs(qw_gpu *g, bool on);
  * on): each kernel may start while its predecessor drains and waits on the device for the predecessor's results. */
 void qw_gpu_set_pdl(qw_gpu *g, bool on);
 
+/* Attention core + merge with NO allocation anywhere on the path (no counterpart in the reference: its device
+ * layer allocates freely from unified memory).  For callers that cannot allocate device memory -- a process whose
+ * HBM was fully planned at start-up, or a host thread that may not call cudaMalloc because a stream capture is open.
+ * The split-K partials live in a static device array inside the library (8.45 MB per GPU, held until exit), so
+ * nb * max_chunks must be <= 512 (e.g. 16 slots of up to 8192 tokens); heads fixed at 16 q / 2 kv / dim 256.
+ * Inputs are what qsa_attn + qsa_merge take through a batch: q fp16 [nb][16][256] (already normalised and rotated),
+ * the paged KV pool and its size in bytes, the page table int32 [slots][max_pages], pos / slot_ids int32 [nb],
+ * qkv fp16 rows (for the output gate), y fp16 [nb][4096] out; `stream` is a cudaStream_t.  All pointers are device
+ * pointers.  The first call on a device looks up the array's address: make it outside any stream capture.  Calls
+ * that overlap on the GPU share the array and race: serialise them.  Returns 0, or a negative code with a message
+ * in err (-2: the request exceeds the static scratch). */
+int qw_attn_decode_static(const void *q, const void *kv_pool, size_t kv_pool_bytes, const int32_t *page_table, const int32_t *pos,
+                          const int32_t *slot_ids, const void *qkv, void *y, uint32_t nb, uint32_t layer, uint32_t nlayers, uint32_t qkv_stride,
+                          uint32_t max_pages, uint32_t max_chunks, void *stream, char *err, size_t errlen);
+
+/* What qw_gpu_compile would make of a source text, without a device: writes "family entry NAME=VALUE ..." (or the
+ * error message) into out and returns whether the prelude is valid. */
+bool qw_gpu_prelude_describe(const char *src, size_t len, char *out, size_t outlen);
+
 /* Precompiled kernel families that qw_gpu_compile can register. */
 int qw_gpu_family_count(void);
 const char *qw_gpu_family_name(int i);

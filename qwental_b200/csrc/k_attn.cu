@@ -501,3 +501,61 @@ static cudaError_t launch_qsa_merge(const QwLaunch &L) {
 }
 QW_FAMILY(qsa_merge, launch_qsa_merge, 256)
 
+// ------------------------------------------------------------------------------------------------ no-allocation entry point
+// qw_attn_decode_static: the attention core + merge for callers that must not allocate device memory at all --
+// for example code running inside someone else's memory plan (a serving process whose whole HBM budget was handed
+// out at start-up, or a host that calls in while a stream capture is open elsewhere and therefore cannot call
+// cudaMalloc).  The split-K partials, which the batch path keeps in a caller-provided buffer, live here in a
+// file-scope device array; every GPU that loads this library holds that array (8.45 MB) until the process exits.
+//
+//   limit     nb * max_chunks <= QW_ATTN_STATIC_MAX_CHUNK_SLOTS (512 page-chunks in flight, e.g. 16 slots of up to
+//             8192 tokens, or 2 slots of 65536); QH = 16, KVH = 2, HD = 256 only.  Larger requests are rejected.
+//   set-up    the first call on a device resolves the array's device address (cudaGetSymbolAddress, with that
+//             device current) and remembers it; make that first call outside any stream capture.
+//   contents  nothing has to start at zero: the core writes every partial (accumulator, max, sum) that the merge
+//             of the same call reads, so what an earlier call left behind is never looked at.
+//   sharing   all calls on a device use the same array: two calls whose kernels overlap on the GPU (different
+//             streams, or different host threads) race and corrupt each other's result.  Serialise them.
+// No cudaMalloc / cudaFree / host allocation happens on this path: the tensor map is encoded on the stack, the
+// per-device address table is a static array.
+#define QW_ATTN_STATIC_MAX_CHUNK_SLOTS 512
+static __device__ __align__(256) float g_attn_static_part[(size_t)QW_ATTN_STATIC_MAX_CHUNK_SLOTS * 16 * (256 + 2)];
+static float *g_attn_static_ptr[64];  // per device: address of the array above (host code may not use the symbol itself)
+
+extern "C" int qw_attn_decode_static(const void *q, const void *kv_pool, size_t kv_pool_bytes, const int32_t *page_table, const int32_t *pos,
+                                     const int32_t *slot_ids, const void *qkv, void *y, uint32_t nb, uint32_t layer, uint32_t nlayers,
+                                     uint32_t qkv_stride, uint32_t max_pages, uint32_t max_chunks, void *stream, char *err, size_t errlen) {
+    auto fail = [&](int code, const char *msg) {
+        if (err && errlen) snprintf(err, errlen, "qw_attn_decode_static: %s", msg);
+        return code;
+    };
+    constexpr uint32_t QH = 16, KVH = 2, HD = 256;
+    if (!q || !kv_pool || !page_table || !pos || !slot_ids || !qkv || !y) return fail(-1, "null pointer argument");
+    if (nb < 1 || nb > 64 || max_chunks < 1 || max_chunks > max_pages || layer >= nlayers) return fail(-1, "bad nb / max_chunks / layer");
+    if ((uint64_t)nb * max_chunks > QW_ATTN_STATIC_MAX_CHUNK_SLOTS)
+        return fail(-2, "nb * max_chunks exceeds the static scratch (512 page-chunks); use the batch path with a caller-provided buffer");
+    if (qkv_stride < QH * 2 * HD + 2 * KVH * HD || ((uintptr_t)kv_pool & 15) || kv_pool_bytes < 512 || kv_pool_bytes / 512 >= 0x7fffffffull)
+        return fail(-1, "bad qkv stride or KV pool");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(-3, "no current CUDA device");
+    if (!g_attn_static_ptr[dev]) {  // once per device, with that device current
+        float *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_attn_static_part);
+        if (e != cudaSuccess || !p) return fail(-3, cudaGetErrorString(e));
+        g_attn_static_ptr[dev] = p;
+    }
+    float *part = g_attn_static_ptr[dev];
+    CUtensorMap tm;  // encoded on the stack: no allocation
+    if (!attn_encode_map(&tm, kv_pool, kv_pool_bytes / 512 * 512)) return fail(-3, "tensor map encoding failed");
+    qsa_args a = {nb, layer, nlayers, qkv_stride, max_pages, max_chunks, 0, 0};
+    const size_t smem = 4 * AT_WARP_BYTES + 64 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(qsa_attn_mma_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(-3, cudaGetErrorString(e));
+    cudaStream_t st = (cudaStream_t)stream;
+    qsa_attn_mma_k<<<dim3(max_chunks, KVH, nb), 128, smem, st>>>(tm, (const __half *)q, page_table, pos, slot_ids, part, a, QH, KVH, nullptr);
+    qsa_merge_k<<<dim3(QH, nb), 1024, 0, st>>>(part, (const __half *)qkv, (__half *)y, pos, a, QH);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(-3, cudaGetErrorString(e));
+    if (err && errlen) err[0] = 0;
+    return 0;
+}
