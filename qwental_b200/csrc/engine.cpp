@@ -219,7 +219,8 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     if (c.hd != 256 || c.qh != 8 * c.kvh) return bad("attention kernels need head_dim 256 and 8 query heads per kv head");
     if (c.max_slots < 1 || c.max_slots > QW_PAR_MAX) return bad("max_slots must be 1..64");
     if (c.ep_size < 1 || c.experts % c.ep_size || c.ep_rank < 0 || c.ep_rank >= c.ep_size) return bad("bad expert-parallel slice");
-    if (c.expert_inter % 256 || c.hidden % 256 || c.vocab % 16 || c.experts % 32 || c.topk < 1 || c.topk > 15) return bad("unsupported MoE / vocab shape");
+    if (c.expert_inter % 256 || c.hidden % 256 || c.vocab % 16 || c.experts % 32 || (c.experts != 512 && c.experts > 256) || c.topk < 1 || c.topk > 15)
+        return bad("unsupported MoE / vocab shape (experts: 512, or a multiple of 32 up to 256)");
     if (c.hv % c.hk || c.layers < 1 || c.attn_every < 1) return bad("bad layer shape");
     e->D = c.hidden; e->L = c.layers; e->V = c.vocab; e->E = c.experts; e->EL = c.experts / c.ep_size; e->e_lo = c.ep_rank * e->EL;
     e->TOPK = c.topk; e->I = c.expert_inter; e->QH = c.qh; e->KVH = c.kvh; e->HD = c.hd; e->HK = c.hk; e->HV = c.hv;

@@ -204,6 +204,10 @@ __device__ __forceinline__ float hash_normal(uint64_t seed, uint64_t i) {
 __global__ void qw_fill_k(uint8_t *dst, fill_args a) {
     pdl_sync();
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    if (a.mode == 0 && (((uintptr_t)dst | a.count) & 15) == 0) {  // zeroing: 16 bytes per store
+        for (uint64_t li = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; li < a.count / 16; li += stride) ((uint4 *)dst)[li] = make_uint4(0, 0, 0, 0);
+        return;
+    }
     for (uint64_t li = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; li < a.count; li += stride) {
         const uint64_t i = a.base + li;
         if (a.mode == 0) dst[li] = 0;
@@ -231,7 +235,7 @@ static cudaError_t launch_qw_fill(const QwLaunch &L) {
     QW_CHECK_ARG(L.buf<void>(0) && L.has_bytes(1, 36) && a.mode <= 5 && a.count > 0);
     const size_t esz = a.mode <= 2 ? 1 : a.mode == 3 ? 2 : 4;
     QW_CHECK_ARG(L.avail(0) >= a.count * esz);
-    const uint64_t blocks = (a.count + 255) / 256;
+    const uint64_t blocks = ((a.mode == 0 ? a.count / 16 : a.count) + 255) / 256 + 1;
     const unsigned grid = (unsigned)(blocks < (uint64_t)L.sm_count * 32 ? blocks : (uint64_t)L.sm_count * 32);
     qw_launch(qw_fill_k, grid, 256, 0, L.stream, L.buf<uint8_t>(0), a);
     return cudaGetLastError();

@@ -89,28 +89,63 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         const float *lg = logits + (size_t)t * (E + 1);
         // Logits as order-preserving unsigned keys (a float's bits with the sign folded), so a maximum is one hardware
         // warp reduction.  Equal floats give equal keys (a logit is never -0: every dot product starts from +0).
-        uint32_t v[32];
-#pragma unroll
-        for (uint32_t j = 0; j < 32; j++) {
-            const uint32_t u = j < PER ? __float_as_uint(__ldcg(lg + lane + 32 * j)) : 0xff800000u;  // -inf
-            v[j] = u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
-        }
+        auto key_of = [&](uint32_t j) {
+            const uint32_t u = __float_as_uint(__ldcg(lg + lane + 32 * j));
+            return u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
+        };
         uint32_t pkey = 0;
-        for (uint32_t k = 0; k < topk; k++) {
-            uint32_t b0 = v[0], j0 = 0;
+        if (PER == 16) {
+            // The lane sorts its 16 (key, ~id) pairs once with a 63-comparator odd-even merge network (descending key,
+            // ascending id); each of the topk rounds then only looks at the lanes' heads and the winning lane pops its
+            // head -- instead of rescanning 16 values per lane per round.
+            uint64_t s[16];
 #pragma unroll
-            for (uint32_t j = 1; j < 32; j++)
-                if (j < PER && v[j] > b0) { b0 = v[j]; j0 = j; }
-            const uint32_t m = __reduce_max_sync(0xffffffffu, b0);
-            const uint32_t id = __reduce_min_sync(0xffffffffu, b0 == m ? lane + 32 * j0 : 0xffffffffu);
-            if (lane == 0) {
-                ms->ids[t][k] = (int32_t)id;
-                sid[t * MOE_MAXK + k] = (uint16_t)id;
+            for (uint32_t j = 0; j < 16; j++) s[j] = ((uint64_t)key_of(j) << 32) | (0xffffffffu - (lane + 32 * j));
+#define CE(A, B)                          \
+    {                                     \
+        const uint64_t x_ = s[A], y_ = s[B]; \
+        const bool sw_ = y_ > x_;         \
+        s[A] = sw_ ? y_ : x_;             \
+        s[B] = sw_ ? x_ : y_;             \
+    }
+            CE(0, 1) CE(2, 3) CE(4, 5) CE(6, 7) CE(8, 9) CE(10, 11) CE(12, 13) CE(14, 15) CE(0, 2) CE(1, 3) CE(4, 6) CE(5, 7) CE(8, 10) CE(9, 11) CE(12, 14) CE(13, 15) CE(1, 2) CE(5, 6) CE(9, 10) CE(13, 14) CE(0, 4) CE(1, 5) CE(2, 6) CE(3, 7) CE(8, 12) CE(9, 13) CE(10, 14) CE(11, 15) CE(2, 4) CE(3, 5) CE(10, 12) CE(11, 13) CE(1, 2) CE(3, 4) CE(5, 6) CE(9, 10) CE(11, 12) CE(13, 14) CE(0, 8) CE(1, 9) CE(2, 10) CE(3, 11) CE(4, 12) CE(5, 13) CE(6, 14) CE(7, 15) CE(4, 8) CE(5, 9) CE(6, 10) CE(7, 11) CE(2, 4) CE(3, 5) CE(6, 8) CE(7, 9) CE(10, 12) CE(11, 13) CE(1, 2) CE(3, 4) CE(5, 6) CE(7, 8) CE(9, 10) CE(11, 12) CE(13, 14)
+#undef CE
+            for (uint32_t k = 0; k < topk; k++) {
+                const uint32_t hk = (uint32_t)(s[0] >> 32), hi_ = (uint32_t)s[0];
+                const uint32_t m = __reduce_max_sync(0xffffffffu, hk);
+                const uint32_t nid = __reduce_max_sync(0xffffffffu, hk == m ? hi_ : 0u);  // largest ~id = lowest id
+                const uint32_t id = 0xffffffffu - nid;
+                if (lane == 0) {
+                    ms->ids[t][k] = (int32_t)id;
+                    sid[t * MOE_MAXK + k] = (uint16_t)id;
+                }
+                if (lane == k) pkey = m;
+                if (lane == (id & 31)) {  // pop the head
+#pragma unroll
+                    for (uint32_t j = 0; j < 15; j++) s[j] = s[j + 1];
+                    s[15] = 0;
+                }
             }
-            if (lane == k) pkey = m;
-            const uint32_t bl = id & 31, bj = id >> 5;
+        } else {
+            uint32_t v[8];  // small expert counts (E <= 256): rescan the lane's few values every round
 #pragma unroll
-            for (uint32_t j = 0; j < 32; j++) v[j] = (lane == bl && j == bj) ? 0u : v[j];  // below every real key
+            for (uint32_t j = 0; j < 8; j++) v[j] = j < PER ? key_of(j) : 0u;
+            for (uint32_t k = 0; k < topk; k++) {
+                uint32_t b0 = v[0], j0 = 0;
+#pragma unroll
+                for (uint32_t j = 1; j < 8; j++)
+                    if (j < PER && v[j] > b0) { b0 = v[j]; j0 = j; }
+                const uint32_t m = __reduce_max_sync(0xffffffffu, b0);
+                const uint32_t id = __reduce_min_sync(0xffffffffu, b0 == m ? lane + 32 * j0 : 0xffffffffu);
+                if (lane == 0) {
+                    ms->ids[t][k] = (int32_t)id;
+                    sid[t * MOE_MAXK + k] = (uint16_t)id;
+                }
+                if (lane == k) pkey = m;
+                const uint32_t bl = id & 31, bj = id >> 5;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; j++) v[j] = (lane == bl && j == bj) ? 0u : v[j];  // below every real key
+            }
         }
         const float pk = __uint_as_float(pkey ^ ((pkey >> 31) ? 0x80000000u : 0xffffffffu));
         const float mx = __shfl_sync(0xffffffffu, pk, 0), ex = expf(pk - mx);
@@ -182,7 +217,7 @@ static cudaError_t launch_moe_select(const QwLaunch &L) {
     const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
     sel_args a = L.bytes<sel_args>(2);
     QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && L.has_bytes(2, 12));
-    QW_CHECK_ARG(E % 32 == 0 && E <= MOE_MAXE && topk >= 1 && topk < MOE_MAXK && topk <= E && a.nb >= 1 && a.nb <= MOE_MAXB);
+    QW_CHECK_ARG(E % 32 == 0 && (E == 512 || E <= 256) && topk >= 1 && topk < MOE_MAXK && topk <= E && a.nb >= 1 && a.nb <= MOE_MAXB);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * (E + 1) * 4 && L.avail(1) >= sizeof(moe_sel));
     if (a.e_hi > E) a.e_hi = E;
     qw_launch(moe_select_k, 1, 1024, 0, L.stream, L.buf<float>(0), L.buf<moe_sel>(1), E, topk, a);
@@ -245,7 +280,7 @@ static cudaError_t launch_moe_route(const QwLaunch &L) {
     sel_args a = L.bytes<sel_args>(14);
     QW_CHECK_ARG(L.has_bytes(14, 12) && a.nb >= 1 && a.nb <= MOE_MAXB);
     for (int i = 0; i <= 5; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
-    QW_CHECK_ARG(E % 32 == 0 && E <= MOE_MAXE && topk >= 1 && topk < MOE_MAXK && topk <= E);
+    QW_CHECK_ARG(E % 32 == 0 && (E == 512 || E <= 256) && topk >= 1 && topk < MOE_MAXK && topk <= E);
     QW_CHECK_ARG(L.avail(0) >= (size_t)E * D * 2 && L.avail(1) >= (size_t)D * 2 && L.avail(2) >= (size_t)a.nb * D * 2 &&
                  L.avail(3) >= (size_t)a.nb * (E + 1) * 4 && L.avail(4) >= 4 && L.avail(5) >= sizeof(moe_sel));
     if (a.e_hi > E) a.e_hi = E;
