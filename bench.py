@@ -166,10 +166,11 @@ def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
     return nslots / step, cores, kind, sample, t
 
 
-def workload_config(layers, slots, ctx_sum, world, graphs):
+def workload_config(layers, slots, ctx_sum, world, graphs, ep="nccl"):
     return {"workload": "full %d-layer Qwen3-Next-80B-A3B-shaped decode step, %d ragged slots (contexts log-uniform 1K-48K, sum %d tokens), "
                         "IQ3_S weights, Q8_0 lm_head, greedy" % (layers, slots, ctx_sum),
-            "parallelism": "ep%d (experts sharded, rest replicated)" % world if world > 1 else "1 GPU",
+            "parallelism": "ep%d (experts sharded, rest replicated; exchange: %s)" % (
+                world, "peer stores fused into the down projection" if ep == "fused" else "NCCL all-reduce") if world > 1 else "1 GPU",
             "l2": "inputs larger than L2 (weights 35 GB, KV and state several GB per step)", "cuda_graphs": bool(graphs)}
 
 
@@ -210,6 +211,8 @@ def main():
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; a number measured with fewer layers is not a benchmark value")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graphs", type=int, default=1)
+    ap.add_argument("--ep", default="nccl", choices=["nccl", "fused"],
+                    help="expert-parallel exchange at N > 1: one NCCL all-reduce per layer, or peer stores fused into the down projection")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -242,6 +245,12 @@ def main():
             idt.copy_(torch.frombuffer(bytearray(ep_unique_id()), dtype=torch.uint8))
         dist.broadcast(idt, 0)
         eng.ep_init(bytes(idt.cpu().numpy().tobytes()))
+        if args.ep == "fused":
+            mine = torch.frombuffer(bytearray(eng.ep_export()), dtype=torch.uint8).cuda()
+            allh = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+            dist.all_gather(allh, mine)
+            eng.ep_connect([bytes(t.cpu().numpy().tobytes()) for t in allh])
+            dist.barrier()
     for s in range(B):
         eng.seed_slot(s, int(ctx[s]), 100 + s)
     gpu.L.qw_gpu_set_graphs(gpu.g, bool(args.graphs))
@@ -317,7 +326,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x int (IQ3_S / Q8_0 weights), f32 accumulate",
             "data": "synthetic",
-            "config": workload_config(cfg.layers, B, int(ctx.sum()), world, args.graphs),
+            "config": workload_config(cfg.layers, B, int(ctx.sum()), world, args.graphs, args.ep),
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 3 * 64 * 4, "d2h_bytes_per_step": B * 4, "ms_per_step": e2e_wall_ms / K},
             "gpu_launches": int(launches),
             "clocks": clocks,
@@ -334,6 +343,8 @@ def main():
             v, cores, kind, sample = cpu_baseline_avg(B, ctx)
             out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}
         print(json.dumps(out))
+    if dist is not None:
+        dist.barrier()  # nobody unmaps or frees an exchange buffer while another rank may still be stepping
     eng.close()
     gpu.close()
     if dist is not None:

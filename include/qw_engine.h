@@ -88,6 +88,15 @@ size_t qw_engine_tap(qw_engine *e, const char *name, int index, void *dst, size_
 int qw_ep_unique_id(void *id128);
 int qw_engine_ep_init(qw_engine *e, const void *id128);
 
+/* Fused exchange (optional, after or instead of qw_engine_ep_init; ranks on one NVLink/NVSwitch machine, even layer
+ * count): the down projection of every rank stores its expert rows directly into every rank's buffer and publishes a
+ * sequence number; the next norm kernel waits (bounded) for all ranks' numbers.  No collective call and no zero fill
+ * remain on the step.  Every rank calls qw_engine_ep_export, the 64-byte handles are gathered in rank order by any
+ * means, then every rank calls qw_engine_ep_connect with the ep_size handles.  All ranks must then step in lockstep
+ * with identical inputs.  0 on success, -1 with qw_engine_error set. */
+int qw_engine_ep_export(qw_engine *e, void *handle64);
+int qw_engine_ep_connect(qw_engine *e, const void *handles, int n);
+
 #ifdef __cplusplus
 }
 #endif

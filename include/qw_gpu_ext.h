@@ -23,6 +23,12 @@ bool qw_buf_upload(qw_gpu *g, const qw_buf *dst, size_t offset, const void *src,
 bool qw_buf_download(qw_gpu *g, const qw_buf *src, size_t offset, void *dst, size_t len);
 bool qw_buf_zero(qw_gpu *g, const qw_buf *dst, size_t offset, size_t len);
 
+/* Sharing a QW_BUF_DEVICE buffer between the processes of one machine (one process per GPU; no counterpart in the
+ * single-device reference): the owner exports a 64-byte handle, a peer imports it and gets a buffer that maps the
+ * owner's memory through NVLink peer access.  Free an imported buffer with qw_buf_free before the owner frees it. */
+bool qw_buf_ipc_export(const qw_buf *b, void *handle64);
+bool qw_buf_ipc_import(qw_gpu *g, const void *handle64, size_t size, qw_buf *out);
+
 /* Device address of a buffer (for interop with other CUDA code in the same process). */
 void *qw_buf_device_ptr(const qw_buf *b);
 /* cudaStream_t of stream s (0 or 1), as an opaque pointer. */

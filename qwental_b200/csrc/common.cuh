@@ -12,7 +12,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)_
 
 // ---- status word (pinned host memory mapped into the device): a kernel that gives up on a wait records
 // where and returns, the host sees it at the batch's wait.
-enum : unsigned { ST_OK = 0, ST_MBAR_TIMEOUT = 0x100, ST_BAD_ARG = 0x200 };
+enum : unsigned { ST_OK = 0, ST_MBAR_TIMEOUT = 0x100, ST_BAD_ARG = 0x200, ST_PEER_TIMEOUT = 0x400 };
 __device__ __forceinline__ void set_status(unsigned *status, unsigned code) {
     if (status) *(volatile unsigned *)status = code;  // plain store: the word lives in host memory
 }
@@ -25,6 +25,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_sync() {
     pdl_launch();
     pdl_wait();
+}
+
+// ---- flags shared with other GPUs (peer memory over NVLink): system-scope release / acquire
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
 }
 
 // ---- mbarrier

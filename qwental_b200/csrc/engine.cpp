@@ -93,6 +93,12 @@ struct qw_engine {
     qw_kernel *k_begin, *k_embed, *k_norm, *k_norm0, *k_norm_cmb, *k_route, *k_adv_feed, *k_qmv_in_a, *k_qmv_in_g, *k_qmv_o_a, *k_qmv_o_g, *k_lm, *k_prep, *k_attn, *k_merge, *k_epi, *k_gdn, *k_router, *k_select,
         *k_gu, *k_dn, *k_cmb, *k_argmax, *k_adv, *k_fill, *k_ar;
     bool ep_ready = false;
+    // fused exchange: each rank's down projection stores its rows straight into every rank's Pg (peer memory)
+    bool ep_fused = false;
+    qw_buf epx{};            // [2][Pg] (double-buffered by layer parity) + flag array, exported to the other ranks
+    qw_buf ep_peer[8]{};     // the other ranks' epx (ep_peer[own rank] aliases epx)
+    qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr;
+    size_t pg_bytes = 0;
     // bookkeeping
     double cost[QW_PAR_MAX + 1];
     int lastB = 0;
@@ -196,6 +202,10 @@ extern "C" void qw_engine_close(qw_engine *e) {
     qw_buf *all[] = {&e->emb, &e->lm_head, &e->dense, &e->small, &e->router, &e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd, &e->kvpool,
                      &e->ptab, &e->sstate, &e->cstate, &e->ctl_h, &e->ctl_d, &e->h, &e->x, &e->proj, &e->cv, &e->la, &e->be, &e->gy, &e->qb,
                      &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt};
+    // mappings of the other ranks' exchange buffers go first (their owners free the memory), then this rank's own
+    for (int r = 0; r < 8; r++)
+        if (r != e->c.ep_rank && e->ep_peer[r].handle) qw_buf_free(&e->ep_peer[r]);
+    qw_buf_free(&e->epx);
     for (qw_buf *b : all) qw_buf_free(b);
     delete e;
 }
@@ -423,11 +433,15 @@ void enc_qmv(qw_batch *b, qw_kernel *k, const qw_buf *W, size_t woff, uint32_t N
 void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_floats, uint32_t nb, int cmb_layer = -1) {
     const uint32_t a[2] = {nb, (uint32_t)e->D};
     const bool cmb = delta == &e->Pg;
-    qw_batch_kernel(b, cmb ? e->k_norm_cmb : delta ? e->k_norm : e->k_norm0);
+    qw_batch_kernel(b, cmb ? (e->ep_fused ? e->k_norm_cmb_x : e->k_norm_cmb) : delta ? e->k_norm : e->k_norm0);
     qw_batch_buf(b, 0, &e->h, 0);
     if (cmb) {
         qw_batch_buf(b, 5, &e->msel, (size_t)cmb_layer * e->sel_bytes);
-        qw_batch_buf(b, 6, &e->Pg, 0);
+        if (e->ep_fused) {
+            qw_batch_buf(b, 6, &e->epx, (size_t)(cmb_layer & 1) * e->pg_bytes);
+            qw_batch_buf(b, 7, &e->epx, 2 * e->pg_bytes);
+            qw_batch_buf(b, 8, &e->rcnt, 64);
+        } else qw_batch_buf(b, 6, &e->Pg, 0);
     } else qw_batch_buf(b, 1, delta, 0);
     qw_batch_buf(b, 2, &e->small, w_off_floats * 4);
     qw_batch_buf(b, 3, &e->x, 0);
@@ -546,20 +560,32 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
         qw_batch_buf(b, 7, &e->Hlo, 0);
         qw_batch_bytes(b, 10, &ebase, 4);
         qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
-        if (e->c.ep_size > 1) {  // rows of experts held elsewhere must read as zero before the exchange
+        if (e->c.ep_size > 1 && !e->ep_fused) {  // rows of experts held elsewhere must read as zero before the exchange
             const fill_args z = {0, (uint64_t)nb * (e->TOPK + 1) * D * 4, 0, 0, 0.f, 0.f};
             enc_fill(e, b, &e->Pg, 0, z);
         }
-        qw_batch_kernel(b, e->k_dn);
+        qw_batch_kernel(b, e->ep_fused ? e->k_dn_x : e->k_dn);
         qw_batch_buf(b, 0, &e->exd, (size_t)l * ex_bytes);
         qw_batch_buf(b, 2, &e->shd, (size_t)l * gu_bytes);
         qw_batch_buf(b, 5, &e->msel, selo);
         qw_batch_buf(b, 6, &e->Hhi, 0);
         qw_batch_buf(b, 7, &e->Hlo, 0);
-        qw_batch_buf(b, 9, &e->Pg, 0);
+        if (e->ep_fused) {
+            // every row goes into Pg[layer parity] of every rank; two buffers suffice because a rank can run at most one
+            // down projection ahead of the slowest rank (its next norm waits for everybody's flags)
+            const uint32_t rk = (uint32_t)e->c.ep_rank;
+            const size_t po = (size_t)(l & 1) * e->pg_bytes;
+            qw_batch_buf(b, 9, &e->epx, po);
+            qw_batch_buf(b, 11, &e->rcnt, 64);
+            qw_batch_bytes(b, 12, &rk, 4);
+            for (int r = 0; r < e->c.ep_size; r++) {
+                qw_batch_buf(b, 16 + r, &e->ep_peer[r], po);
+                qw_batch_buf(b, 24 + r, &e->ep_peer[r], 2 * e->pg_bytes);
+            }
+        } else qw_batch_buf(b, 9, &e->Pg, 0);
         qw_batch_bytes(b, 10, &ebase, 4);
         qw_batch_dispatch(b, D / 64, nb * e->TOPK + 1, 1, 256, 1, 1);
-        if (e->c.ep_size > 1) {
+        if (e->c.ep_size > 1 && !e->ep_fused) {
             // every (token, rank) row has exactly one non-zero contributor (a routed expert's owner, or rank 0 for
             // the shared expert), so the sum reproduces the one-GPU rows bit for bit
             const uint64_t cnt = (uint64_t)nb * (e->TOPK + 1) * D;
@@ -758,5 +784,37 @@ extern "C" int qw_engine_ep_init(qw_engine *e, const void *id128) {
         return -1;
     }
     e->ep_ready = true;
+    return 0;
+}
+
+// Fused exchange, step 1: allocate this rank's exchange buffer and export its 64-byte handle.
+extern "C" int qw_engine_ep_export(qw_engine *e, void *handle64) {
+    if (!e || !handle64) return -1;
+    if (e->c.ep_size < 2 || e->c.ep_size > 8) return e->fail("ep_export: needs 2..8 expert-parallel ranks"), -1;
+    if (e->L & 1) return e->fail("ep_export: the fused exchange alternates two buffers by layer and needs an even layer count"), -1;
+    if (!e->epx.handle) {
+        e->pg_bytes = (size_t)QW_PAR_MAX * (e->TOPK + 1) * e->D * 4;
+        if (!new_buf(e, &e->epx, 2 * e->pg_bytes + 256) || !qw_buf_zero(e->g, &e->epx, 0, e->epx.size)) return -1;
+    }
+    if (!qw_buf_ipc_export(&e->epx, handle64)) return e->fail(qw_gpu_last_error(e->g)), -1;
+    return 0;
+}
+
+// Step 2 (after every rank has exported and the handles were gathered in rank order): map the other ranks' buffers and
+// switch the step to the fused exchange.  All ranks must have zeroed their buffers (= returned from qw_engine_ep_export)
+// before any rank steps; the gather between the two calls orders that.
+extern "C" int qw_engine_ep_connect(qw_engine *e, const void *handles, int n) {
+    if (!e || !handles || n != e->c.ep_size || !e->epx.handle) return e ? (e->fail("ep_connect: export first, pass one handle per rank"), -1) : -1;
+    for (int r = 0; r < n; r++) {
+        if (r == e->c.ep_rank) e->ep_peer[r] = e->epx;
+        else if (!qw_buf_ipc_import(e->g, (const char *)handles + 64 * r, e->epx.size, &e->ep_peer[r])) return e->fail(qw_gpu_last_error(e->g)), -1;
+    }
+    std::vector<std::pair<const char *, long>> md = {{"E", e->E}, {"EL", e->EL}, {"D", (long)e->D}, {"I", e->I}, {"TOPK", e->TOPK},
+                                                      {"SHARED", e->c.ep_rank == 0 ? 1 : 0}, {"RESID", 0}, {"EPX", n}};
+    if (!compile(e, "moe_dn", "moe_dn_epx", md, &e->k_dn_x) ||
+        !compile(e, "add_rmsnorm", "cmb_add_rmsnorm_epx", {{"CMB", 1}, {"TOPK", e->TOPK}, {"EPX", n}}, &e->k_norm_cmb_x))
+        return -1;
+    if (!qw_buf_zero(e->g, &e->rcnt, 64, 8)) return -1;
+    e->ep_fused = true;
     return 0;
 }

@@ -335,6 +335,7 @@ extern "C" void qw_buf_free(qw_buf *b) {
     BufRec *r = (BufRec *)b->handle;
     cudaSetDevice(r->device);
     if (r->kind == QW_BUF_HOSTIO) cudaFreeHost(r->host);
+    else if (r->kind == 4) cudaIpcCloseMemHandle(r->dev);
     else cudaFree(r->dev);
     delete r;
     memset(b, 0, sizeof *b);
@@ -361,6 +362,42 @@ extern "C" bool qw_buf_wrap(qw_gpu *g, void *ptr, size_t len, qw_buf *out) {
     out->handle = r;
     out->ptr = ptr;
     out->size = len;
+    return true;
+}
+
+// ---- sharing a device buffer with the other processes of the same machine (one process per GPU): the owner exports a
+// 64-byte handle, a peer imports it and gets a buffer whose device address maps the owner's memory over NVLink.
+extern "C" bool qw_buf_ipc_export(const qw_buf *b, void *handle64) {
+    if (!b || !b->handle || !handle64) return false;
+    BufRec *r = (BufRec *)b->handle;
+    if (r->kind != QW_BUF_DEVICE) return false;
+    cudaIpcMemHandle_t h;
+    cudaSetDevice(r->device);
+    if (cudaIpcGetMemHandle(&h, r->dev) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    static_assert(sizeof h == 64, "CUDA IPC handles are 64 bytes");
+    memcpy(handle64, &h, 64);
+    return true;
+}
+extern "C" bool qw_buf_ipc_import(qw_gpu *g, const void *handle64, size_t size, qw_buf *out) {
+    if (!g || !handle64 || !out) return false;
+    memset(out, 0, sizeof *out);
+    cudaSetDevice(g->dev);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        set_err(g, "qw_buf_ipc_import", e);
+        cudaGetLastError();
+        return false;
+    }
+    BufRec *r = new BufRec{p, nullptr, size, 4 /* imported */, g->dev};
+    out->handle = r;
+    out->ptr = nullptr;
+    out->size = size;
     return true;
 }
 

@@ -39,9 +39,27 @@ QW_FAMILY(kb_embed, launch_kb_embed, 256)
 // the fly: 5 = moe_sel, 6 = Pg fp32 [nb][TOPK+1][D], define TOPK.  grid nb x 256
 template <int MODE>  // 0: norm only, 1: h += delta, 2: h += fp16(combine)
 __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *delta, const float *w, __half *x, uint32_t D, const moe_sel *ms,
-                                                     const float *Pg, uint32_t topk) {
+                                                     const float *Pg, uint32_t topk, const unsigned *flags, const unsigned *seq, uint32_t nranks,
+                                                     unsigned *status) {
     __shared__ float tmp[32];
     pdl_sync();
+    if (MODE == 2 && nranks > 1) {
+        // expert-parallel: the rows of Pg were stored by every rank's down projection; wait (bounded, about 2 s) until each
+        // rank has published the sequence number this rank's own down projection has just reached
+        if (threadIdx.x < nranks) {
+            const unsigned want = *(volatile const unsigned *)seq;
+            const uint64_t t0 = global_ns();
+            while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
+                const uint64_t dt = global_ns() - t0;
+                if (dt > 1000000ull && *(volatile unsigned *)status != 0) break;  // an earlier kernel already gave up: do not wait again
+                if (dt > 2000000000ull) {
+                    set_status(status, ST_PEER_TIMEOUT | threadIdx.x);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
     float *hr = h + (size_t)t * D;
     float wk[MOE_MAXK];
@@ -83,12 +101,17 @@ static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
     if (L.def("CMB", 0)) {
         const uint32_t topk = (uint32_t)L.def("TOPK", 10);
         QW_CHECK_ARG(L.buf<void>(5) && L.buf<void>(6) && L.avail(5) >= sizeof(moe_sel) && L.avail(6) >= (size_t)a.nb * (topk + 1) * a.D * 4 && topk < MOE_MAXK);
-        qw_launch(add_rmsnorm_k<2>, a.nb, 1024, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, L.buf<moe_sel>(5), L.buf<float>(6), topk);
+        // EPX = number of expert-parallel ranks whose down projections store into Pg: 7 = this rank's flag array
+        // (one sequence number per rank), 8 = this rank's sequence counter
+        const uint32_t nranks = (uint32_t)L.def("EPX", 1);
+        if (nranks > 1) QW_CHECK_ARG(nranks <= 8 && L.buf<void>(7) && L.avail(7) >= nranks * 4 && L.buf<void>(8) && L.avail(8) >= 4);
+        qw_launch(add_rmsnorm_k<2>, a.nb, 1024, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, L.buf<moe_sel>(5), L.buf<float>(6), topk,
+                  nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
     } else if (L.def("ADD", 0)) {
         QW_CHECK_ARG(L.buf<void>(1) && L.avail(1) >= (size_t)a.nb * a.D * 2);
-        qw_launch(add_rmsnorm_k<1>, a.nb, 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0);
+        qw_launch(add_rmsnorm_k<1>, a.nb, 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0, nullptr, nullptr, 1, nullptr);
     } else {
-        qw_launch(add_rmsnorm_k<0>, a.nb, 512, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0);
+        qw_launch(add_rmsnorm_k<0>, a.nb, 512, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0, nullptr, nullptr, 1, nullptr);
     }
     return cudaGetLastError();
 }

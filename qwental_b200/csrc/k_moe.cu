@@ -308,6 +308,12 @@ struct MoeP {
     unsigned *status;
     uint32_t D, I, rbD, rbI, tiles;
     uint32_t ebase;             // id of the first expert stored in Wa / Wb (expert-parallel slice)
+    // expert-parallel exchange fused into the down projection (nranks > 1): every output row is stored into the Pg
+    // buffer of every rank (peer memory), then the last block publishes this rank's sequence number to every rank
+    float *PgR[8];              // Pg of rank r (PgR[rank] is the local one)
+    unsigned *flagR[8];         // flag array of rank r: slot [q] = sequence number rank q has completed
+    unsigned *seq, *done;       // local: sequence counter, finished-block counter
+    uint32_t nranks, rank;
 };
 
 constexpr int MOE_STG = 2;
@@ -482,11 +488,14 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                 red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
                 red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
                 team_sync(team);
+                // output element = (column, row of the 128-row tile), rows fastest across threads: 512-byte runs per
+                // column, which is what peer stores over NVLink want
                 for (int e = tt; e < 8 * 128; e += 256) {
-                    const int jj = e & 3, ln = (e >> 2) & 31, m = e >> 7, mt = m & 3, j = m >> 2;
+                    const int rt = e & 127, col = e >> 7, m = rt >> 4, r16 = rt & 15, mt = m & 3, j = m >> 2;
+                    const int ln = (r16 & 7) * 4 + (col >> 1), jj = ((r16 >> 3) << 1) | (col & 1);
                     float sum = ((const float *)&red[((mt * 2 + 0) * 2 + j) * 32 + ln])[jj];
                     if (KS > 1) sum += ((const float *)&red[((mt * 2 + 1) * 2 + j) * 32 + ln])[jj];
-                    const uint32_t row = tile * 128 + m * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
+                    const uint32_t row = tile * 128 + rt;
                     if (c0 + col < cnt) {
                         uint32_t tk, rk;
                         if (u < U) {
@@ -497,7 +506,10 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                             tk = c0 + col;
                             rk = topk;
                         }
-                        p.Pg[((size_t)tk * (topk + 1) + rk) * p.D + row] = sum;
+                        const size_t o = ((size_t)tk * (topk + 1) + rk) * p.D + row;
+                        if (p.nranks > 1) {
+                            for (uint32_t r = 0; r < p.nranks; r++) p.PgR[r][o] = sum;
+                        } else p.Pg[o] = sum;
                     }
                 }
             } else {
@@ -542,6 +554,21 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         }
     }
     if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | (DOWN ? 3 : 2));
+    if (DOWN && p.nranks > 1) {
+        // publish: every thread makes its peer stores visible system-wide, the block counts itself done, the last block
+        // advances this rank's sequence number and writes it into slot [rank] of every rank's flag array
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            if (atomicAdd(p.done, 1u) == gridDim.x - 1) {
+                *p.done = 0;
+                const unsigned sv = *p.seq + 1;
+                *p.seq = sv;
+                __threadfence_system();
+                for (uint32_t r = 0; r < p.nranks; r++) st_release_sys(p.flagR[r] + p.rank, sv);
+            }
+        }
+    }
 }
 
 // binds (gate/up): 0 = Wg, 1 = Wu, 2 = shared gate, 3 = shared up (used unless SHARED is defined 0), 4 = x, 5 = moe_sel,
@@ -570,6 +597,25 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     p.Pg = L.buf<float>(9);
     p.tab = (const QwTables *)L.tables;
     p.status = L.status;
+    p.nranks = 1;
+    p.rank = 0;
+    p.seq = p.done = nullptr;
+    for (int r = 0; r < 8; r++) p.PgR[r] = nullptr, p.flagR[r] = nullptr;
+    if (down && L.def("EPX", 0) > 1) {
+        // binds 16 + r = Pg of rank r, 24 + r = flag array of rank r, 11 = {seq, done} counters (local, 8 bytes, zeroed),
+        // 12 = {rank}; define EPX = number of ranks (2..8)
+        p.nranks = (uint32_t)L.def("EPX", 0);
+        QW_CHECK_ARG(p.nranks <= 8 && L.has_bytes(12, 4) && L.buf<unsigned>(11) && L.avail(11) >= 8);
+        p.rank = L.bytes<uint32_t>(12);
+        QW_CHECK_ARG(p.rank < p.nranks);
+        p.seq = L.buf<unsigned>(11);
+        p.done = p.seq + 1;
+        for (uint32_t r = 0; r < p.nranks; r++) {
+            p.PgR[r] = L.buf<float>(16 + r);
+            p.flagR[r] = L.buf<unsigned>(24 + r);
+            QW_CHECK_ARG(p.PgR[r] && p.flagR[r] && L.avail(24 + r) >= p.nranks * 4);
+        }
+    }
     // experts held in the bound weight buffers: EL of them starting at id bytes(10) (default: all E from 0);
     // moe_select must have been given the same range
     const uint32_t EL = (uint32_t)L.def("EL", E);
@@ -588,6 +634,7 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
         p.tiles = p.I / 16;
     } else {
         QW_CHECK_ARG(p.Pg && L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
+        for (uint32_t r = 0; r < p.nranks && p.nranks > 1; r++) QW_CHECK_ARG(L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
         p.tiles = p.D / 128;
     }
     return cudaSuccess;

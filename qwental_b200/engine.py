@@ -37,6 +37,7 @@ def _bind(L):
         "qw_engine_last_step_bytes": (None, [vp, C.POINTER(StepBytes)]),
         "qw_engine_tap": (C.c_size_t, [vp, C.c_char_p, C.c_int, vp, C.c_size_t]),
         "qw_ep_unique_id": (C.c_int, [vp]), "qw_engine_ep_init": (C.c_int, [vp, vp]),
+        "qw_engine_ep_export": (C.c_int, [vp, vp]), "qw_engine_ep_connect": (C.c_int, [vp, vp, C.c_int]),
     }
     for name, (res, args) in sig.items():
         f = getattr(L, name)
@@ -145,6 +146,20 @@ class Engine:
         buf = C.create_string_buffer(id128, 128)
         if self.L.qw_engine_ep_init(self.e, C.cast(buf, C.c_void_p)) != 0:
             raise GpuError("ep_init: " + self.error())
+
+    def ep_export(self) -> bytes:
+        """Fused exchange, step 1: this rank's 64-byte buffer handle (gather them in rank order)."""
+        buf = C.create_string_buffer(64)
+        if self.L.qw_engine_ep_export(self.e, C.cast(buf, C.c_void_p)) != 0:
+            raise GpuError("ep_export: " + self.error())
+        return buf.raw
+
+    def ep_connect(self, handles):
+        """Fused exchange, step 2: map every rank's buffer (handles: list of ep_size 64-byte strings)."""
+        raw = b"".join(handles)
+        buf = C.create_string_buffer(raw, len(raw))
+        if self.L.qw_engine_ep_connect(self.e, C.cast(buf, C.c_void_p), len(handles)) != 0:
+            raise GpuError("ep_connect: " + self.error())
 
     def close(self):
         if self.e:

@@ -1,6 +1,7 @@
 """Expert-parallel decode step on 2 GPUs (skipped with fewer): experts sharded over the ranks, everything else
-replicated, one NCCL all-reduce per MoE layer.  The logits of every rank must be bit-identical to the single-GPU
-step (each exchanged row has exactly one non-zero contributor)."""
+replicated.  Two exchanges are covered: one NCCL all-reduce per MoE layer, and the fused one (the down projection
+stores its rows into every rank's buffer over NVLink and the next norm waits on sequence flags).  The logits of every
+rank must be bit-identical to the single-GPU step (each exchanged row has exactly one contributor)."""
 import os
 
 import numpy as np
@@ -12,37 +13,50 @@ CTX = {0: 300, 2: 17, 5: 700}
 SIDS, TOKS = [0, 2, 5], [5, 9, 33]
 
 
-def _worker(rank, world, uid, q):
+def _worker(rank, world, uid, q, up, down):
     os.environ["QW_CUDA_DEVICE"] = str(rank)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     from qwental_b200.engine import Engine, tiny_cfg
     from qwental_b200.gpu import Gpu
     gpu = Gpu()
     eng = Engine(gpu, tiny_cfg(ep_rank=rank, ep_size=world))
-    eng.ep_init(uid)
+    if uid is not None:
+        eng.ep_init(uid)
+    else:  # fused exchange: the parent gathers the buffer handles and hands the list back
+        up.put((rank, eng.ep_export()))
+        eng.ep_connect(down.get(timeout=120))
     for s, n in CTX.items():
         eng.seed_slot(s, n, 1000 + s)
     l1, _ = eng.step(SIDS, TOKS)
     l2, _ = eng.step(SIDS, list(l1.argmax(1).astype(np.int32)))
     q.put((rank, l1, l2))
+    down.get(timeout=120)  # nobody unmaps or frees an exchange buffer before every rank has finished stepping
     eng.close()
     gpu.close()
 
 
-def test_expert_parallel_step_bit_identical_to_single_gpu():
+@pytest.mark.parametrize("fused", [False, True])
+def test_expert_parallel_step_bit_identical_to_single_gpu(fused):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
     from qwental_b200.engine import Engine, ep_unique_id, tiny_cfg
     from qwental_b200.gpu import Gpu
-    uid = ep_unique_id()
+    uid = None if fused else ep_unique_id()
     ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, uid, q)) for r in range(2)]
+    q, up = ctx.Queue(), ctx.Queue()
+    down = [ctx.Queue() for _ in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, uid, q, up, down[r])) for r in range(2)]
     for p in procs:
         p.start()
+    if fused:
+        hs = dict(up.get(timeout=240) for _ in procs)
+        for d in down:
+            d.put([hs[0], hs[1]])
     res = sorted((q.get(timeout=240) for _ in procs), key=lambda r: r[0])
+    for d in down:
+        d.put("done")
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
