@@ -40,8 +40,8 @@ unsigned long long qw_gpu_launch_count(const qw_gpu *g);
 /* Replay identical batches as CUDA graphs (default off; QW_GRAPH=1 in the environment turns it on). */
 void qw_gpu_set_graphs(qw_gpu *g, bool on);
 
-/* Programmatic dependent launch for the kernels of later batches (default off; QW_PDL=1 in the environment turns it
- * on): each kernel may start while its predecessor drains and waits on the device for the predecessor's results. */
+/* Programmatic dependent launch for the kernels of later batches (default on; QW_PDL=0 in the environment turns it
+ * off): each kernel may start while its predecessor drains and waits on the device for the predecessor's results. */
 void qw_gpu_set_pdl(qw_gpu *g, bool on);
 
 /* Attention core + merge with NO allocation anywhere on the path (no counterpart in the reference: its device

@@ -19,7 +19,7 @@ static int g_pdl = -1;
 bool qw_pdl_enabled() {
     if (g_pdl < 0) {
         const char *e = getenv("QW_PDL");
-        g_pdl = e ? (atoi(e) != 0) : 0;
+        g_pdl = e ? (atoi(e) != 0) : 1;
     }
     return g_pdl != 0;
 }

@@ -73,19 +73,21 @@ struct sel_args {
     uint32_t nb, e_lo, e_hi;
 };
 
-// Body of the selection for one block of 1024 threads.  Logits are read with .cg loads: in the fused router + select
+// Body of the selection for one block of NTH threads (NTH >= E: thread e owns expert e in the scans).  Logits are read with .cg loads: in the fused router + select
 // kernel they were written by other blocks of the same launch.
+template <int NTH>
 __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
     __shared__ uint32_t mlo[MOE_MAXE], mhi[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];  // token bit masks per expert
     __shared__ uint16_t sid[MOE_MAXB * MOE_MAXK];
     __shared__ uint32_t wsum[2][32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t PER = E / 32;
-    for (uint32_t e = tid; e < MOE_MAXE; e += 1024) mlo[e] = mhi[e] = 0;
+    constexpr uint32_t NW = NTH / 32;
+    for (uint32_t e = tid; e < MOE_MAXE; e += NTH) mlo[e] = mhi[e] = 0;
     // 1. top-k per token: one warp per token, lane owns experts lane, lane + 32, ... (coalesced reads).  Equal
     //    logits -> lowest expert id: within a lane the strict '>' keeps the lowest id, across lanes the smallest id
     //    among the lanes holding the maximum wins.
-    for (uint32_t t = warp; t < a.nb; t += 32) {
+    for (uint32_t t = warp; t < a.nb; t += NW) {
         const float *lg = logits + (size_t)t * (E + 1);
         // Logits as order-preserving unsigned keys (a float's bits with the sign folded), so a maximum is one hardware
         // warp reduction.  Equal floats give equal keys (a logit is never -0: every dot product starts from +0).
@@ -158,7 +160,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
     // 2. group by expert.  mask[e] = tokens that chose e; an entry's place inside its group is the number of
     //    earlier tokens in the mask, so groups are filled in token order without any serial scan.
     const uint32_t nent = a.nb * topk;
-    for (uint32_t i = tid; i < nent; i += 1024) {
+    for (uint32_t i = tid; i < nent; i += NTH) {
         const uint32_t t = i / topk, e = sid[t * MOE_MAXK + (i - t * topk)];
         if (e >= a.e_lo && e < a.e_hi) atomicOr(t < 32 ? &mlo[e] : &mhi[e], 1u << (t & 31));
     }
@@ -174,7 +176,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         if (lane == 31) { wsum[0][warp] = sc; wsum[1][warp] = sf; }
         __syncthreads();
         if (warp == 0) {
-            uint32_t xc = wsum[0][lane], xf = wsum[1][lane];
+            uint32_t xc = lane < NW ? wsum[0][lane] : 0, xf = lane < NW ? wsum[1][lane] : 0;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const uint32_t tc = __shfl_up_sync(0xffffffffu, xc, o), tf = __shfl_up_sync(0xffffffffu, xf, o);
@@ -191,7 +193,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
             ms->ue[bf + sf - f] = tid;
             ms->off[bf + sf - f] = bc + sc - c;
         }
-        if (tid == 1023) {
+        if (tid == NTH - 1) {
             ms->U = bf + sf;
             ms->nb = a.nb;
             ms->topk = topk;
@@ -199,7 +201,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         }
     }
     __syncthreads();
-    for (uint32_t i = tid; i < nent; i += 1024) {
+    for (uint32_t i = tid; i < nent; i += NTH) {
         const uint32_t t = i / topk, k = i - t * topk, e = sid[t * MOE_MAXK + k];
         if (e >= a.e_lo && e < a.e_hi) {
             const uint32_t before = t < 32 ? __popc(mlo[e] & ((1u << t) - 1)) : __popc(mlo[e]) + __popc(mhi[e] & ((1u << (t - 32)) - 1));
@@ -210,7 +212,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
 
 __global__ void __launch_bounds__(1024) moe_select_k(const float *logits, moe_sel *ms, uint32_t E, uint32_t topk, sel_args a) {
     pdl_sync();
-    moe_select_body(logits, ms, E, topk, a);
+    moe_select_body<1024>(logits, ms, E, topk, a);
 }
 
 static cudaError_t launch_moe_select(const QwLaunch &L) {
@@ -227,42 +229,75 @@ QW_FAMILY(moe_select, launch_moe_select, 1024)
 
 // ------------------------------------------------------------------------------------------------ router + select in one launch
 // The role of moe_pre_gg's hand-over (kernels/moe_gg.metal:574-589): the block that finishes the router last (device
-// counter + fences) runs the selection.  Blocks of 1024 threads: warp = (row blockIdx*8 + warp%8, token group warp/8),
-// each (row, token) dot product is the same single-lane-chain expression as moe_router, so logits are bit-identical.
+// counter + fences) runs the selection.  Blocks of 512 threads: warp = (row blockIdx*4 + warp%4, token group warp/4); the
+// row sits in registers and the tokens in shared memory, both converted to fp32 once.
 // binds: 0 = Wr, 1 = Wsg, 2 = x, 3 = logits, 4 = counter (uint32, zero before the first launch; left zero), 5 = moe_sel,
-// 14 = {nb, e_lo, e_hi}.  grid ceil((E+1)/8) x 1024
+// 14 = {nb, e_lo, e_hi}.  The launcher sets the grid itself: ceil((E+1)/4) blocks of 512 threads.
 template <int D>
-__global__ void __launch_bounds__(1024) moe_route_k(const __half *Wr, const __half *Wsg, const __half *x, float *logits, unsigned *counter, moe_sel *ms,
-                                                    uint32_t E, uint32_t topk, sel_args a) {
+__global__ void __launch_bounds__(512) moe_route_k(const __half *Wr, const __half *Wsg, const __half *x, float *logits, unsigned *counter, moe_sel *ms,
+                                                   uint32_t E, uint32_t topk, sel_args a) {
     constexpr int CH = D / 8 / 32;
+    // the tokens of one pass as fp32, converted once per block: [16 tokens][CH][2][32 lanes] float4, so that a lane's
+    // eight values of a chunk are two conflict-free 16-byte loads
+    extern __shared__ __align__(16) uint8_t route_smem[];
+    float4 *xs = (float4 *)route_smem;
     __shared__ bool last;
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = blockIdx.x * 8 + (warp & 7), tg = warp >> 3;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = blockIdx.x * 4 + (warp & 3), tg = warp >> 2;
     pdl_launch();
+    float wf[CH * 8];
     if (r <= E) {
         const uint4 *w = (const uint4 *)(r < E ? Wr + (size_t)r * D : Wsg);
-        uint4 wr[CH];
 #pragma unroll
-        for (int c = 0; c < CH; c++) wr[c] = __ldg(w + lane + 32 * c);
-        pdl_wait();  // the router row is static; the tokens are the previous kernel's output
-        for (uint32_t t = tg; t < a.nb; t += 4) {
-            const uint4 *xt = (const uint4 *)(x + (size_t)t * D);
-            float acc = 0.f;
+        for (int c = 0; c < CH; c++) {
+            const uint4 v = __ldg(w + lane + 32 * c);
+            const uint32_t a4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int c = 0; c < CH; c++) {
-                const uint4 xv = __ldg(xt + lane + 32 * c);
-                const uint32_t a4[4] = {wr[c].x, wr[c].y, wr[c].z, wr[c].w}, b4[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float2 fa = __half22float2(*(const __half2 *)&a4[j]), fb = __half22float2(*(const __half2 *)&b4[j]);
-                    acc = __fmaf_rn(fa.x, fb.x, acc);
-                    acc = __fmaf_rn(fa.y, fb.y, acc);
-                }
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(*(const __half2 *)&a4[j]);
+                wf[8 * c + 2 * j] = f.x;
+                wf[8 * c + 2 * j + 1] = f.y;
             }
-            const float v = warp_sum_canon(acc);
-            if (lane == 0) logits[(size_t)t * (E + 1) + r] = v;
         }
     }
-    pdl_wait();  // (blocks without a row have not waited yet; the selection below reads and writes shared buffers)
+    pdl_wait();  // the router row is static; the tokens are the previous kernel's output
+    // Passes of 16 tokens.  Each warp runs its tokens (tg, tg + 4, tg + 8, tg + 12) against its row; every dot product is
+    // the same single-lane chain as in moe_router (element k of lane l, chunk c is column (l + 32 c) * 8 + k), so logits
+    // are bit-identical.
+    for (uint32_t t0 = 0; t0 < a.nb; t0 += 16) {
+        const uint32_t nt = a.nb - t0 < 16 ? a.nb - t0 : 16;
+        if (t0) __syncthreads();
+        for (uint32_t e = threadIdx.x; e < nt * (D / 8); e += 512) {
+            const uint4 v = __ldg((const uint4 *)(x + (size_t)t0 * D) + e);
+            const uint32_t tl = e / (D / 8), ce = e % (D / 8), c = ce >> 5, ln = ce & 31;
+            const float2 f0 = __half22float2(*(const __half2 *)&v.x), f1 = __half22float2(*(const __half2 *)&v.y);
+            const float2 f2 = __half22float2(*(const __half2 *)&v.z), f3 = __half22float2(*(const __half2 *)&v.w);
+            xs[((tl * CH + c) * 2 + 0) * 32 + ln] = make_float4(f0.x, f0.y, f1.x, f1.y);
+            xs[((tl * CH + c) * 2 + 1) * 32 + ln] = make_float4(f2.x, f2.y, f3.x, f3.y);
+        }
+        __syncthreads();
+        if (r <= E) {
+#pragma unroll 1
+            for (uint32_t tl = tg; tl < nt; tl += 4) {
+                const float4 *xt = xs + tl * CH * 64 + lane;
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < CH; c++) {
+                    const float4 u = xt[c * 64], v = xt[c * 64 + 32];
+                    acc = __fmaf_rn(wf[8 * c + 0], u.x, acc);
+                    acc = __fmaf_rn(wf[8 * c + 1], u.y, acc);
+                    acc = __fmaf_rn(wf[8 * c + 2], u.z, acc);
+                    acc = __fmaf_rn(wf[8 * c + 3], u.w, acc);
+                    acc = __fmaf_rn(wf[8 * c + 4], v.x, acc);
+                    acc = __fmaf_rn(wf[8 * c + 5], v.y, acc);
+                    acc = __fmaf_rn(wf[8 * c + 6], v.z, acc);
+                    acc = __fmaf_rn(wf[8 * c + 7], v.w, acc);
+                }
+                const float s = warp_sum_canon(acc);
+                if (lane == 0) logits[(size_t)(t0 + tl) * (E + 1) + r] = s;
+            }
+        }
+    }
+    pdl_wait();
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -271,8 +306,17 @@ __global__ void __launch_bounds__(1024) moe_route_k(const __half *Wr, const __ha
     }
     __syncthreads();
     if (!last) return;
-    moe_select_body(logits, ms, E, topk, a);
+    moe_select_body<512>(logits, ms, E, topk, a);
     if (threadIdx.x == 0) *counter = 0;
+}
+
+template <int DD>
+static cudaError_t moe_route_go(const QwLaunch &L, unsigned grid, uint32_t E, uint32_t topk, const sel_args &a) {
+    cudaError_t e = cudaFuncSetAttribute(moe_route_k<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * DD * 4);
+    if (e != cudaSuccess) return e;
+    qw_launch(moe_route_k<DD>, grid, 512, 16 * DD * 4, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), L.buf<unsigned>(4),
+              L.buf<moe_sel>(5), E, topk, a);
+    return cudaGetLastError();
 }
 
 static cudaError_t launch_moe_route(const QwLaunch &L) {
@@ -280,17 +324,14 @@ static cudaError_t launch_moe_route(const QwLaunch &L) {
     sel_args a = L.bytes<sel_args>(14);
     QW_CHECK_ARG(L.has_bytes(14, 12) && a.nb >= 1 && a.nb <= MOE_MAXB);
     for (int i = 0; i <= 5; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
-    QW_CHECK_ARG(E % 32 == 0 && (E == 512 || E <= 256) && topk >= 1 && topk < MOE_MAXK && topk <= E);
+    QW_CHECK_ARG(E % 32 == 0 && (E == 512 || E <= 256) && topk >= 1 && topk < MOE_MAXK && topk <= E);  // E <= the block's 512 threads
     QW_CHECK_ARG(L.avail(0) >= (size_t)E * D * 2 && L.avail(1) >= (size_t)D * 2 && L.avail(2) >= (size_t)a.nb * D * 2 &&
                  L.avail(3) >= (size_t)a.nb * (E + 1) * 4 && L.avail(4) >= 4 && L.avail(5) >= sizeof(moe_sel));
     if (a.e_hi > E) a.e_hi = E;
-    const unsigned grid = (E + 1 + 7) / 8;
-#define GO(DD) qw_launch(moe_route_k<DD>, grid, 1024, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<float>(3), L.buf<unsigned>(4), L.buf<moe_sel>(5), E, topk, a)
-    if (D == 2048) GO(2048);
-    else if (D == 256) GO(256);
-    else return cudaErrorInvalidValue;
-#undef GO
-    return cudaGetLastError();
+    const unsigned grid = (E + 1 + 3) / 4;  // (the grid given by the host is ignored)
+    if (D == 2048) return moe_route_go<2048>(L, grid, E, topk, a);
+    if (D == 256) return moe_route_go<256>(L, grid, E, topk, a);
+    return cudaErrorInvalidValue;
 }
 QW_FAMILY(moe_route, launch_moe_route, 1024)
 
@@ -316,9 +357,11 @@ struct MoeP {
     uint32_t nranks, rank;
 };
 
-constexpr int MOE_STG = 2;
+constexpr int MOE_STG_GU = 2, MOE_STG_DN = 3;  // staged tiles per team: 28 KB tiles for gate/up, 14 KB tiles for down
 constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
-constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // per team two buffers (alternating by unit) of 16 x 32 float4
+constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // per team two buffers (alternating by unit): gate/up 16 x 32 float4, down [2][8][68] floats
+constexpr int MOE_DN_ROWS = 64;                        // rows of a down-projection tile (4 m-tiles x 2 K-slices over the 8 warps)
+constexpr int MOE_DN_LD = MOE_DN_ROWS + 4;            // padded column length of the down partials: conflict-free both ways
 
 __device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 256;" ::"r"(team + 1) : "memory"); }
 
@@ -337,27 +380,29 @@ __device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0,
 template <bool DOWN>
 __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = (uint64_t *)smem;  // [team * 2 + stage], [4] = table
+    uint64_t *bars = (uint64_t *)smem;  // [team * stages + stage], then the table's
     uint2 *tab = (uint2 *)(smem + 128);
     const int tid = threadIdx.x, team = tid >> 8, tt = tid & 255, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     float4 *red0 = (float4 *)(smem + 128 + MOE_TAB_BYTES) + team * 2 * 16 * 32;
     const uint32_t rb = DOWN ? p.rbI : p.rbD, K = DOWN ? p.I : p.D, units = K / 256;
-    const uint32_t tile_bytes = DOWN ? 128 * rb : 2 * 16 * rb, half_bytes = 16 * rb;
+    constexpr int MOE_STG = DOWN ? MOE_STG_DN : MOE_STG_GU;
+    const uint32_t tile_bytes = DOWN ? MOE_DN_ROWS * rb : 2 * 16 * rb, half_bytes = 16 * rb;
     const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
     uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)team * MOE_STG * stage_stride;
-    // down: warp = (m-tile grp, K-slice ks of 2); gate/up: warp = K-slice ks of 8, the same warp does the gate rows and
-    // then the up rows of its unit, so one set of B fragments (32 registers) serves both
+    // down: warp = (m-tile grp of 4, K-slice ks of 2); gate/up: warp = K-slice ks of 8, the same warp does the gate rows
+    // and then the up rows of its unit, so one set of B fragments (32 registers) serves both
     const uint32_t KS = DOWN ? (units < 2 ? units : 2) : (units < 8 ? units : 8);
     const uint32_t ks = DOWN ? (warp & 1) : warp, grp = warp >> 1;
     const bool active = ks < KS;
-    // independent of earlier kernels: barriers and the codebook table (thread 0 both initialises and uses bars[4] here;
-    // the other threads see the initialised barriers after the __syncthreads below)
+    // independent of earlier kernels: barriers and the codebook table (thread 0 both initialises and uses the table's
+    // barrier here; the other threads see the initialised barriers after the __syncthreads below)
+    uint64_t *tab_bar = bars + 2 * MOE_STG;
     pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < 5; s++) mbar_init(&bars[s], 1);
+        for (int s = 0; s < 2 * MOE_STG + 1; s++) mbar_init(&bars[s], 1);
         mbar_init_fence();
-        mbar_expect_tx(&bars[4], MOE_TAB_BYTES);
-        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, &bars[4]);
+        mbar_expect_tx(tab_bar, MOE_TAB_BYTES);
+        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, tab_bar);
     }
     pdl_wait();  // the selection record, the tokens / H planes and the outputs belong to earlier kernels
     const moe_sel *ms = p.ms;
@@ -403,9 +448,9 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         u = lo;
         pass = q - pre[lo];
     };
-    uint64_t *full = bars + team * 2;
-    __shared__ uint4 meta[2][MOE_STG];   // per team and stage: {group, tile, first entry of the group, entries in the group}
-    __shared__ uint32_t meta_c0[2][MOE_STG];
+    uint64_t *full = bars + team * MOE_STG;
+    __shared__ uint4 meta[2][4];   // per team and stage: {group, tile, first entry of the group, entries in the group}
+    __shared__ uint32_t meta_c0[2][4];
     auto issue = [&](uint32_t i) {  // team leader only: locate the unit, publish its description, start the copies
         if (i0 + i >= i1) return;
         uint32_t u, pass, tile;
@@ -418,7 +463,7 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         uint8_t *dst = stage0 + (size_t)(i % MOE_STG) * stage_stride;
         mbar_expect_tx(&full[i % MOE_STG], tile_bytes);
         if (DOWN) {
-            const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * 128) * rb : p.Sa + (size_t)tile * 128 * rb;
+            const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * MOE_DN_ROWS) * rb : p.Sa + (size_t)tile * MOE_DN_ROWS * rb;
             bulk_g2s(dst, src, tile_bytes, &full[i % MOE_STG]);
         } else {
             const size_t o = u < U ? ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * rb : (size_t)tile * 16 * rb;
@@ -426,16 +471,20 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
             bulk_g2s(dst + half_bytes, (u < U ? p.Wb : p.Sb) + o, half_bytes, &full[i % MOE_STG]);
         }
     };
-    if (tt == 0) issue(0);
-    bool ok = mbar_wait(&bars[4], 0);
+    if (tt == 0)
+        for (uint32_t i = 0; i + 1 < MOE_STG; i++) issue(i);
+    bool ok = mbar_wait(tab_bar, 0);
     const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
 
     const ZeroRegs zr = zero_regs();
     uint4 xf[DOWN ? 2 : 1][8];  // gate/up: the warp's unit; down: [0] = high plane, [1] = low plane of the warp's unit
     uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
+    // output rows of this thread's columns in the epilogue (element offsets of the (token, rank) rows, ~0 = column absent);
+    // like the B fragments they change only with (group, pass)
+    uint32_t oo[2] = {0xffffffffu, 0xffffffffu};
 
     for (uint32_t i = 0; ok && i0 + i < i1; i++) {
-        if (tt == 0) issue(i + 1);
+        if (tt == 0) issue(i + MOE_STG - 1);
         if (!mbar_wait(&full[i % MOE_STG], (i / MOE_STG) & 1)) {
             ok = false;
             break;
@@ -446,67 +495,75 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         const uint32_t st = smem_u32(stage0) + (i % MOE_STG) * stage_stride;  // shared-space address of the staged tile
         // partial tiles alternate between two buffers, so one team barrier per unit is enough: a buffer is rewritten two
         // units later, after every thread has passed the next unit's barrier; the same barrier frees the stage for the
-        // copy that the leader starts at the top of the next iteration
+        // copy that the leader starts at the top of the next iteration (the stage consumed one unit earlier)
         float4 *red = red0 + (i & 1) * 16 * 32;
         {
-            if (active && (u != cur_u || c0 != cur_c0)) {  // (re)load this warp's B fragments: column g = entry c0 + g
+            if (u != cur_u || c0 != cur_c0) {  // new (group, pass): team-uniform
                 cur_u = u;
                 cur_c0 = c0;
-                const bool have = c0 + g < cnt;
-                uint32_t tok = 0, rank = topk;
-                if (have) {
+                auto entry = [&](uint32_t col, uint32_t &tok, uint32_t &rank) {  // column col of this pass -> (token, rank)
+                    if (c0 + col >= cnt) return false;
                     if (u < U) {
-                        const uint32_t en = ms->ent[e0 + c0 + g];
+                        const uint32_t en = ms->ent[e0 + c0 + col];
                         tok = en >> 8;
                         rank = en & 255;
-                    } else tok = c0 + g;
-                }
-                const uint4 zero = make_uint4(0, 0, 0, 0);
-                if (DOWN) {
-                    const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
-                    const uint4 *hi = (const uint4 *)(p.Hhi + ho) + ks * 32 + t, *lo = (const uint4 *)(p.Hlo + ho) + ks * 32 + t;
-#pragma unroll
-                    for (int ib = 0; ib < 8; ib++) {
-                        xf[0][ib] = have ? __ldg(hi + 4 * ib) : zero;
-                        xf[1][ib] = have ? __ldg(lo + 4 * ib) : zero;
+                    } else {
+                        tok = c0 + col;
+                        rank = topk;
                     }
-                } else {
-                    const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
+                    return true;
+                };
+                {   // epilogue columns of this thread: down (tt >> 6) and (tt >> 6) + 4; gate/up 2 * ((tt >> 2) & 3) + (tt & 1)
+                    uint32_t tok = 0, rank = 0;
+                    if (DOWN) {
+                        oo[0] = entry(tt >> 6, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
+                        oo[1] = entry((tt >> 6) + 4, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
+                    } else {
+                        oo[0] = entry(2 * ((tt >> 2) & 3) + (tt & 1), tok, rank) ? (tok * (topk + 1) + rank) * p.I : 0xffffffffu;
+                    }
+                }
+                if (active) {  // (re)load this warp's B fragments: column g = entry c0 + g
+                    uint32_t tok = 0, rank = topk;
+                    const bool have = entry(g, tok, rank);
+                    const uint4 zero = make_uint4(0, 0, 0, 0);
+                    if (DOWN) {
+                        const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
+                        const uint4 *hi = (const uint4 *)(p.Hhi + ho) + ks * 32 + t, *lo = (const uint4 *)(p.Hlo + ho) + ks * 32 + t;
 #pragma unroll
-                    for (int ib = 0; ib < 8; ib++) xf[0][ib] = have ? __ldg(xr + 4 * ib) : zero;
+                        for (int ib = 0; ib < 8; ib++) {
+                            xf[0][ib] = have ? __ldg(hi + 4 * ib) : zero;
+                            xf[1][ib] = have ? __ldg(lo + 4 * ib) : zero;
+                        }
+                    } else {
+                        const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
+#pragma unroll
+                        for (int ib = 0; ib < 8; ib++) xf[0][ib] = have ? __ldg(xr + 4 * ib) : zero;
+                    }
                 }
             }
             if (DOWN) {
-                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 if (active) {
-#pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        const uint32_t rows = st + (16 * (grp + 4 * j) + g) * rb + ks * 110;
-                        unit_mma1<true>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[1], acc[j]);
-                    }
+                    const uint32_t rows = st + (16 * grp + g) * rb + ks * 110;
+                    unit_mma1<true>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[1], acc);
                 }
-                red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-                red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+                // partials as [K-slice][column][row] with padded columns: this store and the row-contiguous reads below are
+                // both free of bank conflicts
+                float *rs = (float *)red + (ks * 8 + 2 * t) * MOE_DN_LD + 16 * grp + g;
+                rs[0] = acc[0];
+                rs[MOE_DN_LD] = acc[1];
+                rs[8] = acc[2];
+                rs[MOE_DN_LD + 8] = acc[3];
                 team_sync(team);
-                // output element = (column, row of the 128-row tile), rows fastest across threads: 512-byte runs per
-                // column, which is what peer stores over NVLink want
-                for (int e = tt; e < 8 * 128; e += 256) {
-                    const int rt = e & 127, col = e >> 7, m = rt >> 4, r16 = rt & 15, mt = m & 3, j = m >> 2;
-                    const int ln = (r16 & 7) * 4 + (col >> 1), jj = ((r16 >> 3) << 1) | (col & 1);
-                    float sum = ((const float *)&red[((mt * 2 + 0) * 2 + j) * 32 + ln])[jj];
-                    if (KS > 1) sum += ((const float *)&red[((mt * 2 + 1) * 2 + j) * 32 + ln])[jj];
-                    const uint32_t row = tile * 128 + rt;
-                    if (c0 + col < cnt) {
-                        uint32_t tk, rk;
-                        if (u < U) {
-                            const uint32_t en = ms->ent[e0 + c0 + col];
-                            tk = en >> 8;
-                            rk = en & 255;
-                        } else {
-                            tk = c0 + col;
-                            rk = topk;
-                        }
-                        const size_t o = ((size_t)tk * (topk + 1) + rk) * p.D + row;
+                // rows fastest across threads: every warp stores 128 contiguous bytes of one (token, rank) row, which is
+                // also what the peer stores of the expert-parallel exchange want
+#pragma unroll
+                for (int it = 0; it < 2; it++) {
+                    const int rt = tt & 63, col = (tt >> 6) + 4 * it;
+                    float sum = ((const float *)red)[col * MOE_DN_LD + rt];
+                    if (KS > 1) sum += ((const float *)red)[(8 + col) * MOE_DN_LD + rt];
+                    if (oo[it] != 0xffffffffu) {
+                        const size_t o = (size_t)oo[it] + tile * MOE_DN_ROWS + rt;
                         if (p.nranks > 1) {
                             for (uint32_t r = 0; r < p.nranks; r++) p.PgR[r][o] = sum;
                         } else p.Pg[o] = sum;
@@ -524,30 +581,21 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
                 red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
                 red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
                 team_sync(team);
-                if (tt < 128) {
+                if (tt < 128) {  // four warps finish the unit while the other four already start on the next one
                     const int jj = tt & 3, ln = tt >> 2;
                     float gs = 0.f, us = 0.f;
                     for (uint32_t k2 = 0; k2 < KS; k2++) {
                         gs += ((const float *)&red[(k2 * 2 + 0) * 32 + ln])[jj];
                         us += ((const float *)&red[(k2 * 2 + 1) * 32 + ln])[jj];
                     }
-                    const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1), col = 2 * (ln & 3) + (jj & 1);
-                    if (c0 + col < cnt) {
-                        uint32_t tk, rk;
-                        if (u < U) {
-                            const uint32_t en = ms->ent[e0 + c0 + col];
-                            tk = en >> 8;
-                            rk = en & 255;
-                        } else {
-                            tk = c0 + col;
-                            rk = topk;
-                        }
+                    if (oo[0] != 0xffffffffu) {
+                        const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1);
                         const float h = gs / (1.0f + expf(-gs)) * us;
                         const __nv_bfloat16 hi = __float2bfloat16_rn(h);
                         const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
-                        const size_t o = ((size_t)tk * (topk + 1) + rk) * p.I + row;
-                        p.Hhi[o] = __bfloat16_as_ushort(hi);
-                        p.Hlo[o] = __bfloat16_as_ushort(lo);
+                        const size_t ho = (size_t)oo[0] + row;
+                        p.Hhi[ho] = __bfloat16_as_ushort(hi);
+                        p.Hlo[ho] = __bfloat16_as_ushort(lo);
                     }
                 }
             }
@@ -583,7 +631,7 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     QW_CHECK_ARG(p.D % 256 == 0 && p.I % 256 == 0 && p.I % 16 == 0 && p.D % 128 == 0 && (L.tx == 256 || L.tx == 512));
     p.rbD = p.D / 256 * 110;
     p.rbI = p.I / 256 * 110;
-    QW_CHECK_ARG((16 * p.rbD) % 16 == 0 && (128 * p.rbI) % 16 == 0);
+    QW_CHECK_ARG((16 * p.rbD) % 16 == 0 && (MOE_DN_ROWS * p.rbI) % 16 == 0);
     p.Wa = L.buf<uint8_t>(0);
     p.Wb = L.buf<uint8_t>(1);
     const bool shared = L.def("SHARED", 1) != 0;  // bind slots persist across dispatches: optional inputs are opted into by a define
@@ -635,15 +683,15 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     } else {
         QW_CHECK_ARG(p.Pg && L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
         for (uint32_t r = 0; r < p.nranks && p.nranks > 1; r++) QW_CHECK_ARG(L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
-        p.tiles = p.D / 128;
+        p.tiles = p.D / MOE_DN_ROWS;
     }
     return cudaSuccess;
 }
 
 template <bool DOWN>
 static cudaError_t moe_ffn_go(const MoeP &p, int sm_count, cudaStream_t st) {
-    const uint32_t tile_bytes = DOWN ? 128 * p.rbI : 2 * 16 * p.rbD;
-    const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * MOE_STG * ((tile_bytes + 127) & ~127u);
+    const uint32_t tile_bytes = DOWN ? MOE_DN_ROWS * p.rbI : 2 * 16 * p.rbD;
+    const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * (DOWN ? MOE_STG_DN : MOE_STG_GU) * ((tile_bytes + 127) & ~127u);
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
     auto k = moe_ffn_k<DOWN>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -282,38 +282,47 @@ static cudaError_t qmv_mma_nt(const QmvMmaP &p, int sm, cudaStream_t st) {
     return qmv_mma_go<GF, 8, MT, F32OUT>(p, sm, st);
 }
 
-// ---- IQ3_S variant used for the dense projections: one warp per 256-K unit of the tile (8 warps at K = 2048, 16 at
-// K = 4096), the activations' B fragments of up to 16 tokens held in registers for the whole kernel (they are
-// loaded while the first tile is still in flight), decode through the shared-space path of unit_mma1 with a
-// 4-copy codebook (16 KB).  More than 16 tokens run as passes of 16 over the staged tile.
-template <int GF, int WARPS, bool F32OUT>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) qmv_mma2_k(const QmvMmaP p) {
-    constexpr int NT = 2, TS = 32, STG = GF == 8 ? 2 : QMV_STAGES, UB = GF == 21 ? 110 : 272;
+// ---- Variant used for the dense projections: a team of WARPS warps per 16-row tile, one warp per 256-K unit (8 warps
+// at K = 2048, 16 at K = 4096); TEAMS teams share one block (and, for IQ3_S, one conflict-free 16-copy codebook of 64 KB
+// that arrives by a bulk copy while the activations are loaded).  The activations' B fragments of up to 16 tokens stay
+// in registers for the whole kernel; more than 16 tokens run as passes of 16 over the staged tile.
+template <int N>
+__device__ __forceinline__ void team_bar(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(N) : "memory");
+}
+template <int GF, int WARPS, int TEAMS, bool F32OUT>
+__global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 : 1) qmv_mma2_k(const QmvMmaP p) {
+    constexpr int NT = 2, TS = 128, STG = GF == 8 ? 2 : QMV_STAGES, UB = GF == 21 ? 110 : 272, TABB = GF == 21 ? 65536 : 0;
+    constexpr int TT = WARPS * 32;  // threads of a team
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = (uint64_t *)smem;
-    uint2 *tab = (uint2 *)(smem + 64);                             // [512][4]
-    float4 *red = (float4 *)(smem + 64 + 16384);                   // [2][WARPS][NT][32]
-    uint8_t *stage0 = smem + 64 + 16384 + 2 * WARPS * NT * 32 * 16;
+    uint64_t *bars = (uint64_t *)smem;  // [team][STG], then the table's
+    uint2 *tab = (uint2 *)(smem + 128);
     const uint32_t tile_bytes = 16 * p.rb, stage_stride = (tile_bytes + 127) & ~127u;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, team = tid / TT, tt = tid % TT, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    float4 *red = (float4 *)(smem + 128 + TABB) + team * 2 * WARPS * NT * 32;  // [2][WARPS][NT][32] per team
+    uint8_t *stage0 = smem + 128 + TABB + TEAMS * 2 * WARPS * NT * 32 * 16 + (size_t)team * STG * stage_stride;
+    uint64_t *full = bars + team * STG;
+    pdl_launch();
     if (tid == 0) {
-        for (int s = 0; s < STG; s++) mbar_init(&bars[s], 1);
+        for (int s = 0; s < TEAMS * STG + 1; s++) mbar_init(&bars[s], 1);
         mbar_init_fence();
+        if (GF == 21) {
+            mbar_expect_tx(&bars[TEAMS * STG], TABB);
+            bulk_g2s(tab, p.tab->grid_h4, TABB, &bars[TEAMS * STG]);
+        }
     }
     __syncthreads();
-    const uint32_t first = blockIdx.x, step = gridDim.x;
+    const uint32_t first = blockIdx.x * TEAMS + team, step = gridDim.x * TEAMS;
     auto issue = [&](uint32_t j) {
         const uint32_t item = first + j * step;
         if (item >= p.items) return;
         const int s = j % STG;
-        mbar_expect_tx(&bars[s], tile_bytes);
-        bulk_g2s(stage0 + (size_t)s * stage_stride, p.W + (size_t)item * tile_bytes, tile_bytes, &bars[s]);
+        mbar_expect_tx(&full[s], tile_bytes);
+        bulk_g2s(stage0 + (size_t)s * stage_stride, p.W + (size_t)item * tile_bytes, tile_bytes, &full[s]);
     };
-    if (tid == 0)
+    if (tt == 0)
         for (uint32_t j = 0; j < STG - 1; j++) issue(j);
-    if (GF == 21)
-        for (int e = tid; e < 512 * 4; e += WARPS * 32) tab[e] = p.tab->grid_h4[(e >> 2) * 16 + (e & 3)];
-    const uint32_t tabc = smem_u32(tab) + (lane & 3) * 8;
+    const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;
     const ZeroRegs zr = zero_regs();
     const uint4 zero = make_uint4(0, 0, 0, 0);
     uint4 xf[NT][8];
@@ -326,18 +335,17 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) qmv_mma2_k(con
             for (int ib = 0; ib < 8; ib++) xf[nt][ib] = col < p.nb ? __ldg(xr + 4 * ib) : zero;
         }
     };
-    pdl_sync();  // weight tiles and the codebook are static; the activations (and the output buffer) are not
+    pdl_wait();  // weight tiles and the codebook are static; the activations (and the output buffer) are not
     load_x(0);
-    __syncthreads();  // table ready
+    bool ok = GF == 21 ? mbar_wait(&bars[TEAMS * STG], 0) : true;
     const uint32_t passes = (p.nb + 15) / 16;
-    bool ok = true;
     uint32_t rb_i = 0;  // alternating reduce buffer
     for (uint32_t j = 0; ok; j++) {
         const uint32_t item = first + j * step;
         if (item >= p.items) break;
-        if (tid == 0) issue(j + STG - 1);
+        if (tt == 0) issue(j + STG - 1);
         const int s = j % STG;
-        if (!mbar_wait(&bars[s], (j / STG) & 1)) {
+        if (!mbar_wait(&full[s], (j / STG) & 1)) {
             ok = false;
             break;
         }
@@ -351,8 +359,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) qmv_mma2_k(con
             rb_i ^= 1;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) rd[(warp * NT + nt) * 32 + lane] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-            __syncthreads();  // partial tiles visible; on the last pass every warp is also done with stage s
-            for (int e = tid; e < NT * 32 * 4; e += WARPS * 32) {
+            team_bar<TT>(team + 1);  // partial tiles visible; on the last pass every warp is also done with stage s
+            for (int e = tt; e < NT * 32 * 4; e += TT) {
                 const int jj = e & 3, ln = (e >> 2) & 31, nt = e >> 7;
                 float sum = 0.f;
 #pragma unroll
@@ -368,19 +376,21 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) qmv_mma2_k(con
     if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 5);
 }
 
-template <int GF, int WARPS, bool F32OUT>
+template <int GF, int WARPS, int TEAMS, bool F32OUT>
 static cudaError_t qmv_mma2_go(const QmvMmaP &p, int sm_count, cudaStream_t st) {
     const uint32_t tile_bytes = 16 * p.rb;
-    const size_t smem = 64 + 16384 + (size_t)2 * WARPS * 2 * 32 * 16 + (size_t)(GF == 8 ? 2 : QMV_STAGES) * ((tile_bytes + 127) & ~127u);
-    auto k = qmv_mma2_k<GF, WARPS, F32OUT>;
+    const size_t smem = 128 + (GF == 21 ? 65536 : 0) + (size_t)TEAMS * 2 * WARPS * 2 * 32 * 16 +
+                        (size_t)TEAMS * (GF == 8 ? 2 : QMV_STAGES) * ((tile_bytes + 127) & ~127u);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    auto k = qmv_mma2_k<GF, WARPS, TEAMS, F32OUT>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     int occ = 1;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, WARPS * 32, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k, WARPS * TEAMS * 32, smem);
     if (e != cudaSuccess) return e;
     occ = occ < 1 ? 1 : occ > 4 ? 4 : occ;
-    const uint32_t cap = (uint32_t)(sm_count * occ), grid = p.items < cap ? p.items : cap;
-    qw_launch(k, grid, WARPS * 32, smem, st, p);
+    const uint32_t want = (p.items + TEAMS - 1) / TEAMS, cap = (uint32_t)(sm_count * occ), grid = want < cap ? want : cap;
+    qw_launch(k, grid, WARPS * TEAMS * 32, smem, st, p);
     return cudaGetLastError();
 }
 
@@ -405,9 +415,9 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     p.items = a.N / (16 * mt);
 #define GO(G, M)                                                        \
     return f32 ? qmv_mma_nt<G, M, true>(p, L.sm_count, L.stream) : qmv_mma_nt<G, M, false>(p, L.sm_count, L.stream)
-    if (gf == 21 && K == 2048) return f32 ? qmv_mma2_go<21, 8, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 8, false>(p, L.sm_count, L.stream);
-    if (gf == 21 && K == 4096) return f32 ? qmv_mma2_go<21, 16, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 16, false>(p, L.sm_count, L.stream);
-    if (gf == 8 && K == 2048) return f32 ? qmv_mma2_go<8, 8, true>(p, L.sm_count, L.stream) : qmv_mma2_go<8, 8, false>(p, L.sm_count, L.stream);
+    if (gf == 21 && K == 2048) return f32 ? qmv_mma2_go<21, 8, 2, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 8, 2, false>(p, L.sm_count, L.stream);
+    if (gf == 21 && K == 4096) return f32 ? qmv_mma2_go<21, 16, 1, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 16, 1, false>(p, L.sm_count, L.stream);
+    if (gf == 8 && K == 2048) return f32 ? qmv_mma2_go<8, 8, 1, true>(p, L.sm_count, L.stream) : qmv_mma2_go<8, 8, 1, false>(p, L.sm_count, L.stream);
     if (gf == 21) GO(21, 1);
     else GO(8, 1);
 #undef GO

@@ -63,7 +63,7 @@ struct QwTables {
 };
 cudaError_t qw_tables_create(void **out, cudaStream_t s);
 
-// Kernel launch used by every family.  With programmatic dependent launch enabled (QW_PDL=1 or qw_set_pdl) the launch
+// Kernel launch used by every family.  With programmatic dependent launch enabled (the default; QW_PDL=0 or qw_set_pdl turn it off) the launch
 // carries the programmatic-stream-serialization attribute: the kernel may start while its predecessor in the stream is
 // still finishing, runs its data-independent prologue (barrier set-up, lookup tables, staging of weights) and blocks in
 // pdl_wait() (common.cuh) until the predecessor's results are complete and visible.  Every kernel of this library
