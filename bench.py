@@ -211,7 +211,7 @@ def main():
     ap.add_argument("--layers", type=int, default=48, help="(debug) fewer layers; a number measured with fewer layers is not a benchmark value")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graphs", type=int, default=1)
-    ap.add_argument("--ep", default="nccl", choices=["nccl", "fused"],
+    ap.add_argument("--ep", default="fused", choices=["nccl", "fused"],
                     help="expert-parallel exchange at N > 1: one NCCL all-reduce per layer, or peer stores fused into the down projection")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -246,10 +246,20 @@ def main():
         dist.broadcast(idt, 0)
         eng.ep_init(bytes(idt.cpu().numpy().tobytes()))
         if args.ep == "fused":
-            mine = torch.frombuffer(bytearray(eng.ep_export()), dtype=torch.uint8).cuda()
-            allh = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
-            dist.all_gather(allh, mine)
-            eng.ep_connect([bytes(t.cpu().numpy().tobytes()) for t in allh])
+            # every rank must take the same branch: agree on the outcome of the export before connecting
+            try:
+                mine = torch.frombuffer(bytearray(eng.ep_export()), dtype=torch.uint8).cuda()
+                okf = torch.ones(1, device="cuda")
+            except Exception as ex:  # e.g. no peer access between the GPUs: keep the NCCL exchange
+                print("rank %d: fused exchange unavailable (%s), using the NCCL all-reduce" % (rank, ex), file=sys.stderr)
+                mine, okf = torch.zeros(64, dtype=torch.uint8, device="cuda"), torch.zeros(1, device="cuda")
+            dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+            if okf.item() > 0:
+                allh = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+                dist.all_gather(allh, mine)
+                eng.ep_connect([bytes(t.cpu().numpy().tobytes()) for t in allh])
+            else:
+                args.ep = "nccl"
             dist.barrier()
     for s in range(B):
         eng.seed_slot(s, int(ctx[s]), 100 + s)

@@ -357,119 +357,134 @@ struct MoeP {
     uint32_t nranks, rank;
 };
 
-constexpr int MOE_STG_GU = 2, MOE_STG_DN = 3;  // staged tiles per team: 28 KB tiles for gate/up, 14 KB tiles for down
+constexpr int MOE_STG = 2;                             // staged tiles per team (28 KB each)
 constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
-constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // per team two buffers (alternating by unit): gate/up 16 x 32 float4, down [2][8][68] floats
-constexpr int MOE_DN_ROWS = 64;                        // rows of a down-projection tile (4 m-tiles x 2 K-slices over the 8 warps)
-constexpr int MOE_DN_LD = MOE_DN_ROWS + 4;            // padded column length of the down partials: conflict-free both ways
+constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // gate/up: per team two buffers (alternating by unit) of 16 x 32 float4
+constexpr int MOE_DN_ROWS = 128;                       // rows of a down-projection tile: 16 per consumer warp
 
 __device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 256;" ::"r"(team + 1) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
 
-// One kernel for both halves of the expert FFN.  A block is two independent teams of 8 warps; each team walks a
-// contiguous range of items (so consecutive items mostly belong to the same expert) through its own two-stage
-// pipeline of bulk (TMA) copies.  The 64 KB codebook table (16 interleaved copies: conflict-free lookups) is
-// shared by the teams.
-//   gate/up (DOWN = false): item = 16 rows of the gate matrix + the same 16 rows of the up matrix; warp = K-slice
-//       (one 256-K unit, KS = min(8, units) slices): it multiplies the gate rows and then the up rows of its unit
-//       with the same B fragments; the KS partial tiles of each matrix are summed in slice order,
-//       H = silu(g) * u is written as a bf16 high + low pair.
-//   down (DOWN = true): item = 128 rows; warp = (m-tile mt and mt + 4, K-slice of KS = min(2, units)); the B
-//       operand is the H pair (two MMAs per codebook word); the KS partial tiles are summed in slice order.
-// The B fragments of a warp's units (the token columns of the current expert) stay in registers while
-// consecutive items belong to the same expert.
-template <bool DOWN>
-__global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
+// Work units = (group, pass of 8 token columns, row tile), enumerated group-major, then pass, then tile, so that a team's
+// contiguous range keeps one set of B fragments for many consecutive units and every team gets the same number of units
+// whatever the group sizes.  Group U (one past the routed groups) is the shared expert with every token at rank topk.
+// pre[g] = passes of all groups before g (shared memory, MOE_MAXE + 2 words).  Called by every thread of the block.
+struct MoeSched {
+    uint32_t U, nb, topk, groups, i0, i1;
+};
+template <int NTHR>
+__device__ __forceinline__ MoeSched moe_sched(const moe_sel *ms, bool shared_expert, uint32_t tiles, uint32_t *pre, int tid, uint32_t team_id, uint32_t teams) {
+    MoeSched w;
+    w.U = ms->U;
+    w.nb = ms->nb;
+    w.topk = ms->topk;
+    w.groups = w.U + (shared_expert ? 1u : 0u);
+    for (uint32_t gi = tid; gi < w.groups; gi += NTHR) {
+        const uint32_t c = gi < w.U ? ms->off[gi + 1] - ms->off[gi] : w.nb;
+        pre[gi + 1] = (c + 7) / 8;
+    }
+    if (tid == 0) pre[0] = 0;
+    __syncthreads();
+    if (tid < 32) {  // inclusive scan of pre[1..groups] in chunks of 32
+        uint32_t carry = 0;
+        for (uint32_t b0 = 1; b0 <= w.groups; b0 += 32) {
+            const uint32_t idx = b0 + tid;
+            uint32_t v = idx <= w.groups ? pre[idx] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
+                if (tid >= o) v += n;
+            }
+            if (idx <= w.groups) pre[idx] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const uint32_t total = pre[w.groups] * tiles;
+    w.i0 = (uint32_t)((uint64_t)total * team_id / teams);
+    w.i1 = (uint32_t)((uint64_t)total * (team_id + 1) / teams);
+    return w;
+}
+__device__ __forceinline__ void moe_locate(const uint32_t *pre, uint32_t groups, uint32_t tiles, uint32_t w, uint32_t &u, uint32_t &pass, uint32_t &tile) {
+    const uint32_t q = w / tiles;
+    tile = w % tiles;
+    uint32_t lo = 0, hi = groups;  // largest u with pre[u] <= q
+    while (hi - lo > 1) {
+        const uint32_t mid = (lo + hi) >> 1;
+        if (pre[mid] <= q) lo = mid;
+        else hi = mid;
+    }
+    u = lo;
+    pass = q - pre[lo];
+}
+// Column col of a unit's pass -> (token, rank); false when the pass has fewer columns.
+__device__ __forceinline__ bool moe_entry(const moe_sel *ms, uint32_t u, uint32_t U, uint32_t e0, uint32_t c0, uint32_t cnt, uint32_t topk, uint32_t col,
+                                          uint32_t &tok, uint32_t &rank) {
+    if (c0 + col >= cnt) return false;
+    if (u < U) {
+        const uint32_t en = ms->ent[e0 + c0 + col];
+        tok = en >> 8;
+        rank = en & 255;
+    } else {
+        tok = c0 + col;
+        rank = topk;
+    }
+    return true;
+}
+
+// ---- gate/up.  Persistent blocks of two teams of 8 warps; a unit is 16 gate rows + 16 up rows of one expert over the
+// full K, warp = K-slice of 256: the same warp does the gate rows and then the up rows of its slice, so one set of B
+// fragments (32 registers) serves both.  Partial sums of the 8 slices meet in shared memory; four warps finish the unit
+// (SiLU(g) * u as bf16 high + low planes) while the other four already start on the next one.
+__global__ void __launch_bounds__(512, 1) moe_gu_k(const MoeP p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = (uint64_t *)smem;  // [team * stages + stage], then the table's
+    uint64_t *bars = (uint64_t *)smem;  // [team * MOE_STG + stage], then the table's
     uint2 *tab = (uint2 *)(smem + 128);
     const int tid = threadIdx.x, team = tid >> 8, tt = tid & 255, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     float4 *red0 = (float4 *)(smem + 128 + MOE_TAB_BYTES) + team * 2 * 16 * 32;
-    const uint32_t rb = DOWN ? p.rbI : p.rbD, K = DOWN ? p.I : p.D, units = K / 256;
-    constexpr int MOE_STG = DOWN ? MOE_STG_DN : MOE_STG_GU;
-    const uint32_t tile_bytes = DOWN ? MOE_DN_ROWS * rb : 2 * 16 * rb, half_bytes = 16 * rb;
+    const uint32_t rb = p.rbD, units = p.D / 256;
+    const uint32_t tile_bytes = 2 * 16 * rb, half_bytes = 16 * rb;
     const uint32_t stage_stride = (tile_bytes + 127) & ~127u;
     uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)team * MOE_STG * stage_stride;
-    // down: warp = (m-tile grp of 4, K-slice ks of 2); gate/up: warp = K-slice ks of 8, the same warp does the gate rows
-    // and then the up rows of its unit, so one set of B fragments (32 registers) serves both
-    const uint32_t KS = DOWN ? (units < 2 ? units : 2) : (units < 8 ? units : 8);
-    const uint32_t ks = DOWN ? (warp & 1) : warp, grp = warp >> 1;
+    const uint32_t KS = units < 8 ? units : 8, ks = warp;
     const bool active = ks < KS;
     // independent of earlier kernels: barriers and the codebook table (thread 0 both initialises and uses the table's
-    // barrier here; the other threads see the initialised barriers after the __syncthreads below)
+    // barrier here; the other threads see the initialised barriers after the __syncthreads in moe_sched)
     uint64_t *tab_bar = bars + 2 * MOE_STG;
     pdl_launch();
     if (tid == 0) {
         for (int s = 0; s < 2 * MOE_STG + 1; s++) mbar_init(&bars[s], 1);
         mbar_init_fence();
         mbar_expect_tx(tab_bar, MOE_TAB_BYTES);
-        bulk_g2s(tab, DOWN ? p.tab->grid_b4 : p.tab->grid_h4, MOE_TAB_BYTES, tab_bar);
+        bulk_g2s(tab, p.tab->grid_h4, MOE_TAB_BYTES, tab_bar);
     }
-    pdl_wait();  // the selection record, the tokens / H planes and the outputs belong to earlier kernels
+    pdl_wait();  // the selection record, the tokens and the H planes belong to earlier kernels
     const moe_sel *ms = p.ms;
-    const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
-    const uint32_t groups = U + (p.Sa ? 1u : 0u);
-    // Work units = (group, pass of 8 token columns, row tile), enumerated group-major, then pass, then tile, so that
-    // a team's contiguous range keeps one set of B fragments for many consecutive units and every team gets the
-    // same number of units whatever the group sizes.  pre[g] = passes of all groups before g.
     __shared__ uint32_t pre[MOE_MAXE + 2];
-    for (uint32_t gi = tid; gi < groups; gi += 512) {
-        const uint32_t c = gi < U ? ms->off[gi + 1] - ms->off[gi] : nb;
-        pre[gi + 1] = (c + 7) / 8;
-    }
-    if (tid == 0) pre[0] = 0;
-    __syncthreads();
-    if (warp == 0 && team == 0) {  // inclusive scan of pre[1..groups] in chunks of 32
-        uint32_t carry = 0;
-        for (uint32_t b0 = 1; b0 <= groups; b0 += 32) {
-            const uint32_t idx = b0 + lane;
-            uint32_t v = idx <= groups ? pre[idx] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
-                if (lane >= o) v += n;
-            }
-            if (idx <= groups) pre[idx] = v + carry;
-            carry += __shfl_sync(0xffffffffu, v, 31);
-        }
-    }
-    __syncthreads();
-    const uint32_t total = pre[groups] * p.tiles;
-    const uint32_t T = gridDim.x * 2, tg = blockIdx.x * 2 + team;
-    const uint32_t i0 = (uint32_t)((uint64_t)total * tg / T), i1 = (uint32_t)((uint64_t)total * (tg + 1) / T);
-    auto locate = [&](uint32_t w, uint32_t &u, uint32_t &pass, uint32_t &tile) {  // unit index -> (group, pass, tile)
-        const uint32_t q = w / p.tiles;
-        tile = w % p.tiles;
-        uint32_t lo = 0, hi = groups;  // largest u with pre[u] <= q
-        while (hi - lo > 1) {
-            const uint32_t mid = (lo + hi) >> 1;
-            if (pre[mid] <= q) lo = mid;
-            else hi = mid;
-        }
-        u = lo;
-        pass = q - pre[lo];
-    };
+    const MoeSched w = moe_sched<512>(ms, p.Sa != nullptr, p.tiles, pre, tid, blockIdx.x * 2 + team, gridDim.x * 2);
+    const uint32_t U = w.U, nb = w.nb, topk = w.topk, i0 = w.i0, i1 = w.i1;
     uint64_t *full = bars + team * MOE_STG;
-    __shared__ uint4 meta[2][4];   // per team and stage: {group, tile, first entry of the group, entries in the group}
-    __shared__ uint32_t meta_c0[2][4];
+    __shared__ uint4 meta[2][MOE_STG];  // per team and stage: {group, tile, first entry of the group, entries in the group}
+    __shared__ uint32_t meta_c0[2][MOE_STG];
     auto issue = [&](uint32_t i) {  // team leader only: locate the unit, publish its description, start the copies
         if (i0 + i >= i1) return;
         uint32_t u, pass, tile;
-        locate(i0 + i, u, pass, tile);
-        {
-            const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
-            meta[team][i % MOE_STG] = make_uint4(u, tile, e0, cnt);
-            meta_c0[team][i % MOE_STG] = pass * 8;
-        }
+        moe_locate(pre, w.groups, p.tiles, i0 + i, u, pass, tile);
+        const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+        meta[team][i % MOE_STG] = make_uint4(u, tile, e0, cnt);
+        meta_c0[team][i % MOE_STG] = pass * 8;
         uint8_t *dst = stage0 + (size_t)(i % MOE_STG) * stage_stride;
         mbar_expect_tx(&full[i % MOE_STG], tile_bytes);
-        if (DOWN) {
-            const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * MOE_DN_ROWS) * rb : p.Sa + (size_t)tile * MOE_DN_ROWS * rb;
-            bulk_g2s(dst, src, tile_bytes, &full[i % MOE_STG]);
-        } else {
-            const size_t o = u < U ? ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * rb : (size_t)tile * 16 * rb;
-            bulk_g2s(dst, (u < U ? p.Wa : p.Sa) + o, half_bytes, &full[i % MOE_STG]);
-            bulk_g2s(dst + half_bytes, (u < U ? p.Wb : p.Sb) + o, half_bytes, &full[i % MOE_STG]);
-        }
+        const size_t o = u < U ? ((size_t)(ms->ue[u] - p.ebase) * p.I + (size_t)tile * 16) * rb : (size_t)tile * 16 * rb;
+        bulk_g2s(dst, (u < U ? p.Wa : p.Sa) + o, half_bytes, &full[i % MOE_STG]);
+        bulk_g2s(dst + half_bytes, (u < U ? p.Wb : p.Sb) + o, half_bytes, &full[i % MOE_STG]);
     };
     if (tt == 0)
         for (uint32_t i = 0; i + 1 < MOE_STG; i++) issue(i);
@@ -477,11 +492,9 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
     const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
 
     const ZeroRegs zr = zero_regs();
-    uint4 xf[DOWN ? 2 : 1][8];  // gate/up: the warp's unit; down: [0] = high plane, [1] = low plane of the warp's unit
+    uint4 xf[8];  // B fragments of the warp's K-slice: column g = entry c0 + g of the group
     uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
-    // output rows of this thread's columns in the epilogue (element offsets of the (token, rank) rows, ~0 = column absent);
-    // like the B fragments they change only with (group, pass)
-    uint32_t oo[2] = {0xffffffffu, 0xffffffffu};
+    uint32_t oo = 0xffffffffu;  // element offset of the H row of this thread's epilogue column (~0 = column absent)
 
     for (uint32_t i = 0; ok && i0 + i < i1; i++) {
         if (tt == 0) issue(i + MOE_STG - 1);
@@ -495,114 +508,188 @@ __global__ void __launch_bounds__(512, 1) moe_ffn_k(const MoeP p) {
         const uint32_t st = smem_u32(stage0) + (i % MOE_STG) * stage_stride;  // shared-space address of the staged tile
         // partial tiles alternate between two buffers, so one team barrier per unit is enough: a buffer is rewritten two
         // units later, after every thread has passed the next unit's barrier; the same barrier frees the stage for the
-        // copy that the leader starts at the top of the next iteration (the stage consumed one unit earlier)
+        // copy that the leader starts at the top of the next iteration
         float4 *red = red0 + (i & 1) * 16 * 32;
-        {
-            if (u != cur_u || c0 != cur_c0) {  // new (group, pass): team-uniform
-                cur_u = u;
-                cur_c0 = c0;
-                auto entry = [&](uint32_t col, uint32_t &tok, uint32_t &rank) {  // column col of this pass -> (token, rank)
-                    if (c0 + col >= cnt) return false;
-                    if (u < U) {
-                        const uint32_t en = ms->ent[e0 + c0 + col];
-                        tok = en >> 8;
-                        rank = en & 255;
-                    } else {
-                        tok = c0 + col;
-                        rank = topk;
-                    }
-                    return true;
-                };
-                {   // epilogue columns of this thread: down (tt >> 6) and (tt >> 6) + 4; gate/up 2 * ((tt >> 2) & 3) + (tt & 1)
-                    uint32_t tok = 0, rank = 0;
-                    if (DOWN) {
-                        oo[0] = entry(tt >> 6, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
-                        oo[1] = entry((tt >> 6) + 4, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
-                    } else {
-                        oo[0] = entry(2 * ((tt >> 2) & 3) + (tt & 1), tok, rank) ? (tok * (topk + 1) + rank) * p.I : 0xffffffffu;
-                    }
-                }
-                if (active) {  // (re)load this warp's B fragments: column g = entry c0 + g
-                    uint32_t tok = 0, rank = topk;
-                    const bool have = entry(g, tok, rank);
-                    const uint4 zero = make_uint4(0, 0, 0, 0);
-                    if (DOWN) {
-                        const size_t ho = ((size_t)tok * (topk + 1) + rank) * p.I;
-                        const uint4 *hi = (const uint4 *)(p.Hhi + ho) + ks * 32 + t, *lo = (const uint4 *)(p.Hlo + ho) + ks * 32 + t;
+        if (u != cur_u || c0 != cur_c0) {  // new (group, pass): team-uniform
+            cur_u = u;
+            cur_c0 = c0;
+            uint32_t tok = 0, rank = 0;
+            // epilogue column of this thread: 2 * ((tt >> 2) & 3) + (tt & 1)
+            oo = moe_entry(ms, u, U, e0, c0, cnt, topk, 2 * ((tt >> 2) & 3) + (tt & 1), tok, rank) ? (tok * (topk + 1) + rank) * p.I : 0xffffffffu;
+            if (active) {
+                tok = 0;
+                const bool have = moe_entry(ms, u, U, e0, c0, cnt, topk, g, tok, rank);
+                const uint4 zero = make_uint4(0, 0, 0, 0);
+                const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
 #pragma unroll
-                        for (int ib = 0; ib < 8; ib++) {
-                            xf[0][ib] = have ? __ldg(hi + 4 * ib) : zero;
-                            xf[1][ib] = have ? __ldg(lo + 4 * ib) : zero;
-                        }
-                    } else {
-                        const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
-#pragma unroll
-                        for (int ib = 0; ib < 8; ib++) xf[0][ib] = have ? __ldg(xr + 4 * ib) : zero;
-                    }
-                }
+                for (int ib = 0; ib < 8; ib++) xf[ib] = have ? __ldg(xr + 4 * ib) : zero;
             }
-            if (DOWN) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                if (active) {
-                    const uint32_t rows = st + (16 * grp + g) * rb + ks * 110;
-                    unit_mma1<true>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[1], acc);
-                }
-                // partials as [K-slice][column][row] with padded columns: this store and the row-contiguous reads below are
-                // both free of bank conflicts
-                float *rs = (float *)red + (ks * 8 + 2 * t) * MOE_DN_LD + 16 * grp + g;
-                rs[0] = acc[0];
-                rs[MOE_DN_LD] = acc[1];
-                rs[8] = acc[2];
-                rs[MOE_DN_LD + 8] = acc[3];
-                team_sync(team);
-                // rows fastest across threads: every warp stores 128 contiguous bytes of one (token, rank) row, which is
-                // also what the peer stores of the expert-parallel exchange want
+        }
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (active) {
 #pragma unroll
-                for (int it = 0; it < 2; it++) {
-                    const int rt = tt & 63, col = (tt >> 6) + 4 * it;
-                    float sum = ((const float *)red)[col * MOE_DN_LD + rt];
-                    if (KS > 1) sum += ((const float *)red)[(8 + col) * MOE_DN_LD + rt];
-                    if (oo[it] != 0xffffffffu) {
-                        const size_t o = (size_t)oo[it] + tile * MOE_DN_ROWS + rt;
-                        if (p.nranks > 1) {
-                            for (uint32_t r = 0; r < p.nranks; r++) p.PgR[r][o] = sum;
-                        } else p.Pg[o] = sum;
-                    }
-                }
-            } else {
-                float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                if (active) {
-#pragma unroll
-                    for (int j = 0; j < 2; j++) {  // gate rows, then up rows, of unit ks
-                        const uint32_t rows = st + j * half_bytes + g * rb + ks * 110;
-                        unit_mma1<false>(rows, rows + 8 * rb, tabc, t, zr, xf[0], xf[0], acc[j]);
-                    }
-                }
-                red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
-                red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
-                team_sync(team);
-                if (tt < 128) {  // four warps finish the unit while the other four already start on the next one
-                    const int jj = tt & 3, ln = tt >> 2;
-                    float gs = 0.f, us = 0.f;
-                    for (uint32_t k2 = 0; k2 < KS; k2++) {
-                        gs += ((const float *)&red[(k2 * 2 + 0) * 32 + ln])[jj];
-                        us += ((const float *)&red[(k2 * 2 + 1) * 32 + ln])[jj];
-                    }
-                    if (oo[0] != 0xffffffffu) {
-                        const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1);
-                        const float h = gs / (1.0f + expf(-gs)) * us;
-                        const __nv_bfloat16 hi = __float2bfloat16_rn(h);
-                        const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
-                        const size_t ho = (size_t)oo[0] + row;
-                        p.Hhi[ho] = __bfloat16_as_ushort(hi);
-                        p.Hlo[ho] = __bfloat16_as_ushort(lo);
-                    }
-                }
+            for (int j = 0; j < 2; j++) {  // gate rows, then up rows, of unit ks
+                const uint32_t rows = st + j * half_bytes + g * rb + ks * 110;
+                unit_mma1<false>(rows, rows + 8 * rb, tabc, t, zr, xf, xf, acc[j]);
+            }
+        }
+        red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+        red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+        team_sync(team);
+        if (tt < 128) {
+            const int jj = tt & 3, ln = tt >> 2;
+            float gs = 0.f, us = 0.f;
+            for (uint32_t k2 = 0; k2 < KS; k2++) {
+                gs += ((const float *)&red[(k2 * 2 + 0) * 32 + ln])[jj];
+                us += ((const float *)&red[(k2 * 2 + 1) * 32 + ln])[jj];
+            }
+            if (oo != 0xffffffffu) {
+                const uint32_t row = tile * 16 + (ln >> 2) + 8 * (jj >> 1);
+                const float h = gs / (1.0f + expf(-gs)) * us;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(h);
+                const __nv_bfloat16 lo = __float2bfloat16_rn(h - __bfloat162float(hi));
+                const size_t ho = (size_t)oo + row;
+                p.Hhi[ho] = __bfloat16_as_ushort(hi);
+                p.Hlo[ho] = __bfloat16_as_ushort(lo);
             }
         }
     }
-    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | (DOWN ? 3 : 2));
-    if (DOWN && p.nranks > 1) {
+    if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 2);
+}
+
+// ---- down.  Persistent blocks of two teams; a team = 8 consumer warps + 1 producer warp.  A unit is 128 rows of one
+// expert's down matrix over the full K (28 KB); consumer warp w owns rows 16w .. 16w+15 over all of K, so nothing is
+// exchanged between warps and there is no team barrier per unit: the producer's copy completes the stage's "full"
+// mbarrier, each consumer warp arrives on its "empty" mbarrier when it has read the tile, and a warp stores its
+// 16 x 8 outputs straight from the accumulators.  The H rows of the pass (bf16 high and low planes of up to 8
+// (token, rank) columns) sit in shared memory, padded so that the B-fragment loads of a quarter warp hit 8 different
+// 16-byte bank groups; they are reloaded (two consumer barriers) only when (group, pass) changes.  MMA row g of a warp is
+// tile row 16w + 2g, row g + 8 is 16w + 2g + 1: with 220-byte rows that keeps the raw-byte loads free of bank conflicts,
+// and a lane's two rows of a column are one 8-byte store.
+constexpr int MOE_DN_THREADS = 2 * 9 * 32;
+template <int IB>
+__device__ __forceinline__ void dn_sub(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr, uint32_t hb_hi,
+                                       uint32_t hb_lo, float (&acc)[4]) {
+    const uint4 xv = lds_v4(hb_hi + IB * 64), xl = lds_v4(hb_lo + IB * 64);
+    sub_mma1<true, IB, 128>(u0, u1, t, h0, h1, tabc, zr, xv, xl, acc);
+}
+__global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = (uint64_t *)smem;  // full[team][stage], empty[team][stage], table
+    uint2 *tab = (uint2 *)(smem + 128);
+    const int tid = threadIdx.x, team = tid / 288, tt = tid % 288, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t rb = p.rbI, units = p.I / 256;
+    const uint32_t hs_stride = p.I * 2 + 64, hs_bytes = 16 * hs_stride;  // [plane][column] rows of I bf16 + 64 bytes of padding
+    uint8_t *hs = smem + 128 + MOE_TAB_BYTES + (size_t)team * hs_bytes;
+    const uint32_t tile_bytes = MOE_DN_ROWS * rb, stage_stride = (tile_bytes + 127) & ~127u;
+    uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 2 * hs_bytes + (size_t)team * MOE_STG * stage_stride;
+    uint64_t *full = bars + team * MOE_STG, *empty = bars + 2 * MOE_STG + team * MOE_STG, *tab_bar = bars + 4 * MOE_STG;
+    pdl_launch();
+    if (tid == 0) {
+        for (int s = 0; s < 2 * MOE_STG; s++) {
+            mbar_init(&bars[s], 1);
+            mbar_init(&bars[2 * MOE_STG + s], 8);  // one arrival per consumer warp
+        }
+        mbar_init(tab_bar, 1);
+        mbar_init_fence();
+        mbar_expect_tx(tab_bar, MOE_TAB_BYTES);
+        bulk_g2s(tab, p.tab->grid_b4, MOE_TAB_BYTES, tab_bar);
+    }
+    pdl_wait();  // the selection record, the H planes and the outputs belong to earlier kernels
+    const moe_sel *ms = p.ms;
+    __shared__ uint32_t pre[MOE_MAXE + 2];
+    const MoeSched w = moe_sched<MOE_DN_THREADS>(ms, p.Sa != nullptr, p.tiles, pre, tid, blockIdx.x * 2 + team, gridDim.x * 2);
+    const uint32_t U = w.U, nb = w.nb, topk = w.topk, i0 = w.i0, i1 = w.i1;
+    __shared__ uint4 meta[2][MOE_STG];  // per team and stage: {group, tile, first entry of the group, entries in the group}
+    __shared__ uint32_t meta_c0[2][MOE_STG];
+    bool ok = true;
+    if (warp == 8) {
+        // ---- producer: one lane walks the team's units, reusing a stage as soon as all 8 consumer warps have left it
+        if (lane == 0) {
+            for (uint32_t i = 0; i0 + i < i1; i++) {
+                const uint32_t s = i % MOE_STG;
+                if (i >= MOE_STG && !mbar_wait(&empty[s], (i / MOE_STG - 1) & 1)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t u, pass, tile;
+                moe_locate(pre, w.groups, p.tiles, i0 + i, u, pass, tile);
+                const uint32_t e0 = u < U ? ms->off[u] : 0, cnt = u < U ? ms->off[u + 1] - e0 : nb;
+                meta[team][s] = make_uint4(u, tile, e0, cnt);
+                meta_c0[team][s] = pass * 8;
+                mbar_expect_tx(&full[s], tile_bytes);
+                const uint8_t *src = u < U ? p.Wa + ((size_t)(ms->ue[u] - p.ebase) * p.D + (size_t)tile * MOE_DN_ROWS) * rb : p.Sa + (size_t)tile * MOE_DN_ROWS * rb;
+                bulk_g2s(stage0 + (size_t)s * stage_stride, src, tile_bytes, &full[s]);
+            }
+            if (!ok) set_status(p.status, ST_MBAR_TIMEOUT | 4);
+        }
+    } else {
+        // ---- consumers
+        ok = mbar_wait(tab_bar, 0);
+        const uint32_t tabc = smem_u32(tab) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
+        const ZeroRegs zr = zero_regs();
+        const uint32_t hb_hi = smem_u32(hs) + g * hs_stride + t * 16, hb_lo = hb_hi + 8 * hs_stride;
+        uint32_t cur_u = 0xffffffffu, cur_c0 = 0;
+        uint32_t oo[2] = {0xffffffffu, 0xffffffffu};  // element offsets of the output rows of columns 2t and 2t + 1 (~0 = absent)
+        for (uint32_t i = 0; ok && i0 + i < i1; i++) {
+            const uint32_t s = i % MOE_STG;
+            if (!mbar_wait(&full[s], (i / MOE_STG) & 1)) {
+                ok = false;
+                break;
+            }
+            // the producer wrote the unit's description before its mbarrier arrive (release); the wait above acquires it
+            const uint4 md = meta[team][s];
+            const uint32_t u = md.x, tile = md.y, e0 = md.z, cnt = md.w, c0 = meta_c0[team][s];
+            if (u != cur_u || c0 != cur_c0) {  // new (group, pass): uniform over the team's consumers
+                cur_u = u;
+                cur_c0 = c0;
+                team_sync(team);  // every consumer warp is done with the previous pass's H rows
+                const uint32_t i8 = p.I / 8;  // 16-byte pieces per row
+                for (uint32_t idx = tt; idx < 16 * i8; idx += 256) {
+                    const uint32_t pc = idx / i8, kk = idx - pc * i8, col = pc & 7;
+                    uint32_t tok = 0, rank = 0;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (moe_entry(ms, u, U, e0, c0, cnt, topk, col, tok, rank))
+                        v = __ldg((const uint4 *)((pc < 8 ? p.Hhi : p.Hlo) + ((size_t)tok * (topk + 1) + rank) * p.I) + kk);
+                    *(uint4 *)(hs + (size_t)pc * hs_stride + kk * 16) = v;
+                }
+                uint32_t tok = 0, rank = 0;
+                oo[0] = moe_entry(ms, u, U, e0, c0, cnt, topk, 2 * t, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
+                oo[1] = moe_entry(ms, u, U, e0, c0, cnt, topk, 2 * t + 1, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
+                team_sync(team);
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t r0 = smem_u32(stage0) + s * stage_stride + (16 * warp + 2 * g) * rb;
+#pragma unroll 1
+            for (uint32_t ks = 0; ks < units; ks++) {
+                const uint32_t u0 = r0 + ks * 110, u1 = u0 + rb, bh = hb_hi + ks * 512, bl = hb_lo + ks * 512;
+                const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
+                dn_sub<0>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<1>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<2>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<3>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<4>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<5>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<6>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+                dn_sub<7>(u0, u1, t, h0, h1, tabc, zr, bh, bl, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);  // this warp has read the tile
+            // acc[0], acc[2] = rows 2g and 2g + 1 of column 2t; acc[1], acc[3] = the same rows of column 2t + 1
+            const uint32_t row = tile * MOE_DN_ROWS + 16 * warp + 2 * g;
+            if (p.nranks > 1) {
+                for (uint32_t r = 0; r < p.nranks; r++) {
+                    if (oo[0] != 0xffffffffu) *(float2 *)(p.PgR[r] + oo[0] + row) = make_float2(acc[0], acc[2]);
+                    if (oo[1] != 0xffffffffu) *(float2 *)(p.PgR[r] + oo[1] + row) = make_float2(acc[1], acc[3]);
+                }
+            } else {
+                if (oo[0] != 0xffffffffu) *(float2 *)(p.Pg + oo[0] + row) = make_float2(acc[0], acc[2]);
+                if (oo[1] != 0xffffffffu) *(float2 *)(p.Pg + oo[1] + row) = make_float2(acc[1], acc[3]);
+            }
+        }
+        if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 3);
+    }
+    if (p.nranks > 1) {
         // publish: every thread makes its peer stores visible system-wide, the block counts itself done, the last block
         // advances this rank's sequence number and writes it into slot [rank] of every rank's flag array
         __threadfence_system();
@@ -688,15 +775,22 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     return cudaSuccess;
 }
 
-template <bool DOWN>
-static cudaError_t moe_ffn_go(const MoeP &p, int sm_count, cudaStream_t st) {
-    const uint32_t tile_bytes = DOWN ? MOE_DN_ROWS * p.rbI : 2 * 16 * p.rbD;
-    const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * (DOWN ? MOE_STG_DN : MOE_STG_GU) * ((tile_bytes + 127) & ~127u);
+static cudaError_t moe_gu_go(const MoeP &p, int sm_count, cudaStream_t st) {
+    const uint32_t tile_bytes = 2 * 16 * p.rbD;
+    const size_t smem = 128 + MOE_TAB_BYTES + MOE_RED_BYTES + (size_t)2 * MOE_STG * ((tile_bytes + 127) & ~127u);
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    auto k = moe_ffn_k<DOWN>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(moe_gu_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    qw_launch(k, sm_count, 512, smem, st, p);
+    qw_launch(moe_gu_k, sm_count, 512, smem, st, p);
+    return cudaGetLastError();
+}
+static cudaError_t moe_dn_go(const MoeP &p, int sm_count, cudaStream_t st) {
+    const uint32_t tile_bytes = MOE_DN_ROWS * p.rbI;
+    const size_t smem = 128 + MOE_TAB_BYTES + (size_t)2 * 16 * (p.I * 2 + 64) + (size_t)2 * MOE_STG * ((tile_bytes + 127) & ~127u);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    cudaError_t e = cudaFuncSetAttribute(moe_dn_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    qw_launch(moe_dn_k, sm_count, MOE_DN_THREADS, smem, st, p);
     return cudaGetLastError();
 }
 
@@ -707,7 +801,7 @@ static cudaError_t launch_moe_gu(const QwLaunch &L) {
     if (e != cudaSuccess) return e;
     const uint32_t units = p.D / 256;
     QW_CHECK_ARG(units == 1 || units == 2 || units == 4 || units == 8);
-    return moe_ffn_go<false>(p, L.sm_count, L.stream);
+    return moe_gu_go(p, L.sm_count, L.stream);
 }
 QW_FAMILY(moe_gu, launch_moe_gu, 512)
 
@@ -717,7 +811,7 @@ static cudaError_t launch_moe_dn(const QwLaunch &L) {
     cudaError_t e = moe_fill(L, p, E, topk, true);
     if (e != cudaSuccess) return e;
     QW_CHECK_ARG(p.I / 256 <= 2);
-    return moe_ffn_go<true>(p, L.sm_count, L.stream);
+    return moe_dn_go(p, L.sm_count, L.stream);
 }
 QW_FAMILY(moe_dn, launch_moe_dn, 512)
 
