@@ -67,20 +67,40 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
 #pragma unroll
         for (uint32_t s = 0; s < MOE_MAXK; s++) wk[s] = s <= topk ? ms->w[t][s] : 0.f;
     }
+    // a thread's values stay in registers between the two passes (D <= 4 * blockDim; beyond that they are read back)
+    float vv[4] = {0.f, 0.f, 0.f, 0.f};
     float ss = 0.f;
-    for (uint32_t d = tid; d < D; d += nth) {
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const uint32_t d = tid + it * nth;
+        if (d < D) {
+            float v = hr[d];
+            if (MODE == 1) {
+                v += __half2float(delta[(size_t)t * D + d]);
+                hr[d] = v;
+            } else if (MODE == 2) {
+                float pv[MOE_MAXK];  // all loads first (independent), then the rank-ordered chain
+#pragma unroll
+                for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? Pg[((size_t)t * (topk + 1) + s) * D + d] : 0.f;
+                float o = 0.f;
+#pragma unroll
+                for (uint32_t s = 0; s < MOE_MAXK; s++)
+                    if (s <= topk) o = fmaf(wk[s], pv[s], o);
+                v += __half2float(__float2half_rn(o));
+                hr[d] = v;
+            }
+            vv[it] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    for (uint32_t d = tid + 4 * nth; d < D; d += nth) {  // rows wider than the register copy
         float v = hr[d];
         if (MODE == 1) {
             v += __half2float(delta[(size_t)t * D + d]);
             hr[d] = v;
         } else if (MODE == 2) {
-            float pv[MOE_MAXK];  // all loads first (independent), then the rank-ordered chain
-#pragma unroll
-            for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? Pg[((size_t)t * (topk + 1) + s) * D + d] : 0.f;
             float o = 0.f;
-#pragma unroll
-            for (uint32_t s = 0; s < MOE_MAXK; s++)
-                if (s <= topk) o = fmaf(wk[s], pv[s], o);
+            for (uint32_t s = 0; s <= topk; s++) o = fmaf(wk[s], Pg[((size_t)t * (topk + 1) + s) * D + d], o);
             v += __half2float(__float2half_rn(o));
             hr[d] = v;
         }
@@ -89,10 +109,14 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
     ss = warp_sum(ss);
     if (lane == 0) tmp[warp] = ss;
     __syncthreads();
-    float tot = 0.f;
-    for (uint32_t i = 0; i < nth / 32; i++) tot += tmp[i];
+    const float tot = warp_sum(lane < nth / 32 ? tmp[lane] : 0.f);  // every warp sums the same 32 values in the same order
     const float r = rsqrtf(tot / D + 1e-6f);
-    for (uint32_t d = tid; d < D; d += nth) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const uint32_t d = tid + it * nth;
+        if (d < D) x[(size_t)t * D + d] = __float2half_rn(vv[it] * r * w[d]);
+    }
+    for (uint32_t d = tid + 4 * nth; d < D; d += nth) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
 }
 static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
     struct { uint32_t nb, D; } a = L.bytes<decltype(a)>(4);

@@ -168,6 +168,7 @@ struct QmvMmaP {
     const QwTables *tab;
     unsigned *status;
     uint32_t N, K, rb, xstride, ystride, nb, items;
+    uint32_t rs;  // qmv_mma2: distance of the rows of a staged tile in shared memory (rb plus padding against bank conflicts)
 };
 
 constexpr int QMV_STAGES = 3;
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;  // [team][STG], then the table's
     uint2 *tab = (uint2 *)(smem + 128);
-    const uint32_t tile_bytes = 16 * p.rb, stage_stride = (tile_bytes + 127) & ~127u;
+    const uint32_t tile_bytes = 16 * p.rb, stage_stride = (16 * p.rs + 127) & ~127u;
     const int tid = threadIdx.x, team = tid / TT, tt = tid % TT, warp = tt >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     float4 *red = (float4 *)(smem + 128 + TABB) + team * 2 * WARPS * NT * 32;  // [2][WARPS][NT][32] per team
     uint8_t *stage0 = smem + 128 + TABB + TEAMS * 2 * WARPS * NT * 32 * 16 + (size_t)team * STG * stage_stride;
@@ -318,7 +319,10 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
         if (item >= p.items) return;
         const int s = j % STG;
         mbar_expect_tx(&full[s], tile_bytes);
-        bulk_g2s(stage0 + (size_t)s * stage_stride, p.W + (size_t)item * tile_bytes, tile_bytes, &full[s]);
+        if (p.rs == p.rb) bulk_g2s(stage0 + (size_t)s * stage_stride, p.W + (size_t)item * tile_bytes, tile_bytes, &full[s]);
+        else  // one copy per row, so that the rows land rs bytes apart
+            for (uint32_t r = 0; r < 16; r++)
+                bulk_g2s(stage0 + (size_t)s * stage_stride + r * p.rs, p.W + (size_t)item * tile_bytes + (size_t)r * p.rb, p.rb, &full[s]);
     };
     if (tt == 0)
         for (uint32_t j = 0; j < STG - 1; j++) issue(j);
@@ -349,12 +353,12 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
             ok = false;
             break;
         }
-        const uint32_t rows = smem_u32(stage0) + s * stage_stride + g * p.rb + warp * UB;
+        const uint32_t rows = smem_u32(stage0) + s * stage_stride + g * p.rs + warp * UB;
         for (uint32_t ps = 0; ps < passes; ps++) {
             if (passes > 1) load_x(ps * 16);
             float acc[NT][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            if (GF == 21) unit_mma2<TS>(rows, rows + 8 * p.rb, tabc, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
-            else unit_mma2_q8(rows, rows + 8 * p.rb, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
+            if (GF == 21) unit_mma2<TS>(rows, rows + 8 * p.rs, tabc, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
+            else unit_mma2_q8(rows, rows + 8 * p.rs, t, zr, xf[0], xf[1], ps * 16 + 8 < p.nb, acc);
             float4 *rd = red + rb_i * WARPS * NT * 32;
             rb_i ^= 1;
 #pragma unroll
@@ -378,9 +382,8 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
 
 template <int GF, int WARPS, int TEAMS, bool F32OUT>
 static cudaError_t qmv_mma2_go(const QmvMmaP &p, int sm_count, cudaStream_t st) {
-    const uint32_t tile_bytes = 16 * p.rb;
     const size_t smem = 128 + (GF == 21 ? 65536 : 0) + (size_t)TEAMS * 2 * WARPS * 2 * 32 * 16 +
-                        (size_t)TEAMS * (GF == 8 ? 2 : QMV_STAGES) * ((tile_bytes + 127) & ~127u);
+                        (size_t)TEAMS * (GF == 8 ? 2 : QMV_STAGES) * ((16 * p.rs + 127) & ~127u);
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
     auto k = qmv_mma2_k<GF, WARPS, TEAMS, F32OUT>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -413,6 +416,17 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     p.status = L.status;
     p.N = a.N; p.K = K; p.rb = rb; p.xstride = a.xstride; p.ystride = a.ystride; p.nb = a.nb;
     p.items = a.N / (16 * mt);
+    // Rows of a staged tile: the eight rows a warp instruction touches must fall into different banks.  An IQ3_S lane
+    // reads 2 bytes (row distance = 4, 12, 20 or 28 words mod 32), a Q8_0 lane 8 bytes (8 or 24 words mod 32: two rows
+    // per bank group, the best a 32-byte-per-row access allows).  Padding is a multiple of 16 bytes (bulk-copy alignment).
+    p.rs = rb;
+    for (uint32_t pad = 0; pad < 128 && rb % 16 == 0; pad += 16) {
+        const uint32_t wds = ((rb + pad) / 4) % 32;
+        if (gf == 21 ? (wds % 8 == 4) : (wds % 16 == 8)) {
+            p.rs = rb + pad;
+            break;
+        }
+    }
 #define GO(G, M)                                                        \
     return f32 ? qmv_mma_nt<G, M, true>(p, L.sm_count, L.stream) : qmv_mma_nt<G, M, false>(p, L.sm_count, L.stream)
     if (gf == 21 && K == 2048) return f32 ? qmv_mma2_go<21, 8, 2, true>(p, L.sm_count, L.stream) : qmv_mma2_go<21, 8, 2, false>(p, L.sm_count, L.stream);
