@@ -325,6 +325,9 @@ def main():
     gu_bytes = (sb.unique_experts_sum / cfg.layers + (1 if rank == 0 else 0)) * 2 * cfg.expert_inter * (cfg.hidden // 256 * 110)
     gu_us = float(np.mean(per.get("moe_gu", [float("nan")])))
     achieved = gu_bytes / (gu_us * 1e-6) / 1e9
+    # DRAM traffic of a gate/up launch: ncu measured 124.4 MB read + written for 117.1 MB of weights on a launch of the
+    # same shape (profiles/moe_gu_dn_route_qmv_16slots_ncu_full.md); the ratio is applied to this run's own bytes
+    gu_traffic = gu_bytes * (124.4 / 117.1)
     tot_us = sum(sum(v) for v in per.values())
     shares = {k: round(sum(v) / tot_us, 4) for k, v in sorted(per.items(), key=lambda kv: -sum(kv[1]))}
 
@@ -341,7 +344,8 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "moe_gu (IQ3_S gate/up matvec over gathered experts)", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": gu_traffic, "traffic_source": "ncu dram bytes of one launch, scaled by algorithmic bytes",
+                         "peak_source": peak_src,
                          "bytes_per_launch": gu_bytes, "us_per_launch": gu_us},
             "step_bytes": {"total": sb.total, "moe": sb.moe, "dense": sb.dense, "lm_head": sb.lm_head, "kv": sb.kv, "gdn_state": sb.gdn_state,
                            "unique_experts_per_layer": sb.unique_experts_sum / cfg.layers, "ctx_tokens": int(sb.ctx_tokens),
