@@ -62,6 +62,15 @@ def tiny_cfg(**over) -> ModelCfg:
     return default_cfg(**base)
 
 
+def wide_cfg(**over) -> ModelCfg:
+    """Few layers and experts but the full-size layer shapes (hidden 2048, 16/2 attention heads, 16/32 GDN heads), so the
+    engine picks the same kernel variants as for the benchmark model (fused projection epilogues included)."""
+    base = dict(hidden=2048, layers=4, attn_every=4, vocab=512, experts=32, topk=4, expert_inter=512, qh=16, kvh=2, hd=256, hk=16, hv=32,
+                max_slots=8, max_ctx=2048, kv_pages=0, seed=2)
+    base.update(over)
+    return default_cfg(**base)
+
+
 class Engine:
     def __init__(self, gpu: Gpu, cfg: ModelCfg):
         self.L = gpu.L

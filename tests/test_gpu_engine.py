@@ -1,5 +1,6 @@
-"""GPU parity of the full decode step through the engine C ABI (benchmark config 4 at a reduced model size, so
-the FP64 oracle finishes in seconds): logits within fp16 tolerance of the chained FP64 reference with top-1
+"""GPU parity of the full decode step through the engine C ABI (benchmark config 4 at two reduced model sizes, so
+the FP64 oracle finishes in seconds: "tiny" shrinks every dimension, "wide" keeps the full-size layer shapes and with
+them the kernel variants of the benchmark model): logits within fp16 tolerance of the chained FP64 reference with top-1
 agreement, chosen experts identical, batched rows bit-identical to each slot alone, chained greedy decode equal to
 step-by-step decode, CUDA-graph replay equal to plain launches."""
 import numpy as np
@@ -16,10 +17,10 @@ def gpu():
     g.close()
 
 
-@pytest.fixture(scope="module")
-def eng(gpu):
-    from qwental_b200.engine import Engine, tiny_cfg
-    e = Engine(gpu, tiny_cfg())
+@pytest.fixture(scope="module", params=["tiny", "wide"])
+def eng(gpu, request):
+    from qwental_b200.engine import Engine, tiny_cfg, wide_cfg
+    e = Engine(gpu, tiny_cfg() if request.param == "tiny" else wide_cfg())
     yield e
     e.close()
 
