@@ -169,8 +169,9 @@ def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
 def workload_config(layers, slots, ctx_sum, world, graphs, ep="nccl"):
     return {"workload": "full %d-layer Qwen3-Next-80B-A3B-shaped decode step, %d ragged slots (contexts log-uniform 1K-48K, sum %d tokens), "
                         "IQ3_S weights, Q8_0 lm_head, greedy" % (layers, slots, ctx_sum),
-            "parallelism": "ep%d (experts sharded, rest replicated; exchange: %s)" % (
-                world, "peer stores fused into the down projection" if ep == "fused" else "NCCL all-reduce") if world > 1 else "1 GPU",
+            "parallelism": ("ep%d (experts sharded, attention and Gated DeltaNet sharded by slot, rest replicated; exchange: peer stores "
+                            "fused into the down and out projections)" % world if ep == "fused" else
+                            "ep%d (experts sharded, rest replicated; exchange: NCCL all-reduce)" % world) if world > 1 else "1 GPU",
             "l2": "inputs larger than L2 (weights 35 GB, KV and state several GB per step)", "cuda_graphs": bool(graphs)}
 
 

@@ -19,7 +19,10 @@ __device__ __forceinline__ void set_status(unsigned *status, unsigned code) {
 
 // ---- programmatic dependent launch: pdl_launch() lets the next kernel of the stream begin launching, pdl_wait() blocks
 // until the previous kernel has completed and its writes are visible (a no-op when the launch carried no such
-// attribute).  Rule of this library: nothing that another kernel reads or writes is touched before pdl_wait().
+// attribute).  Rules of this library: nothing that another kernel reads or writes is touched before pdl_wait(); and data that
+// an earlier kernel of the step produced is never read through the non-coherent path (__ldg / ld.global.nc) -- a kernel that
+// started early is already running while its predecessor writes, so that path may serve stale lines.  Such loads use
+// __ldcg (L2) or plain loads; __ldg is kept for weights and tables only.
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_sync() {
@@ -34,6 +37,30 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+
+// ---- exchange between the ranks of one machine through peer memory: a producing kernel stores its rows into every rank's
+// buffer and then publishes; the consuming kernel waits until every rank has published the same step.
+struct EpPeers {
+    unsigned *flagR[8];    // flag array of rank r (peer memory): slot [q] = sequence number rank q has completed
+    unsigned *seq, *done;  // local: this rank's sequence counter, finished-block counter (both start at zero)
+    uint32_t nranks, rank;
+};
+// Every thread of every block calls this after its last peer store: the stores are made visible system-wide, the block
+// counts itself done, the last block advances this rank's sequence number and writes it into slot [rank] of every rank.
+__device__ __forceinline__ void ep_publish(const EpPeers &ep) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        if (atomicAdd(ep.done, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) {
+            *ep.done = 0;
+            const unsigned sv = *ep.seq + 1;
+            *ep.seq = sv;
+            __threadfence_system();
+            for (uint32_t r = 0; r < ep.nranks; r++) st_release_sys(ep.flagR[r] + ep.rank, sv);
+        }
+    }
+}
+// ep_wait is defined after the status helpers below.
 
 // ---- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
@@ -61,6 +88,25 @@ __device__ __forceinline__ uint64_t global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+// Every thread of the block calls this before it reads rows that other ranks stored: thread r < nranks waits (bounded,
+// about 2 s, then ST_PEER_TIMEOUT through the status word) until rank r has published the sequence number this rank's own
+// producing kernel has just reached; ends with a block barrier.
+__device__ __forceinline__ void ep_wait(const unsigned *flags, const unsigned *seq, uint32_t nranks, unsigned *status) {
+    if (threadIdx.x < nranks) {
+        const unsigned want = *(volatile const unsigned *)seq;
+        const uint64_t t0 = global_ns();
+        while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
+            const uint64_t dt = global_ns() - t0;
+            if (dt > 1000000ull && *(volatile unsigned *)status != 0) break;  // an earlier kernel already gave up: do not wait again
+            if (dt > 2000000000ull) {
+                set_status(status, ST_PEER_TIMEOUT | threadIdx.x);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     for (int i = 0; i < 64; i++)
         if (mbar_try_wait(bar, parity)) return true;

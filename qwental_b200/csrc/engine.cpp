@@ -98,6 +98,14 @@ struct qw_engine {
     qw_buf epx{};            // [2][Pg] (double-buffered by layer parity) + flag array, exported to the other ranks
     qw_buf ep_peer[8]{};     // the other ranks' epx (ep_peer[own rank] aliases epx)
     qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr;
+    // slot sharding on top of the fused exchange: attention / GDN (their projections included) run only for the rows whose
+    // slot this rank owns (slot % ep_size == ep_rank); the out-projection stores its rows into every rank's `ob` and publishes
+    bool slot_shard = false;
+    qw_kernel *k_qmv_o_a_x = nullptr, *k_qmv_o_g_x = nullptr, *k_norm_x = nullptr, *k_pub = nullptr;
+    size_t ob_off = 0;            // offset of the gathered `ob` rows inside epx
+    int perm[QW_PAR_MAX] = {};    // device row j = caller's row perm[j] (rows are ordered by owning rank)
+    uint32_t row_lo = 0, row_hi = 0;  // this rank's rows of the current step
+    std::vector<int32_t> ids_out;     // sampled ids in the caller's row order
     size_t pg_bytes = 0;
     // bookkeeping
     double cost[QW_PAR_MAX + 1];
@@ -418,11 +426,12 @@ struct dn_epi_args { uint32_t nb, layer, nlayers, proj_stride; };
 struct gdn_args { uint32_t nb, layer, nlayers, z_stride; };
 struct sel_args { uint32_t nb, e_lo, e_hi; };
 
-void enc_qmv(qw_batch *b, qw_kernel *k, const qw_buf *W, size_t woff, uint32_t N, uint32_t K, const qw_buf *x, const qw_buf *y, uint32_t nb, uint32_t ystride) {
+void enc_qmv(qw_batch *b, qw_kernel *k, const qw_buf *W, size_t woff, uint32_t N, uint32_t K, const qw_buf *x, const qw_buf *y, uint32_t nb, uint32_t ystride,
+             size_t xoff = 0) {
     const qmv_args a = {N, K, ystride, nb};
     qw_batch_kernel(b, k);
     qw_batch_buf(b, 0, W, woff);
-    qw_batch_buf(b, 3, x, 0);
+    qw_batch_buf(b, 3, x, xoff);
     qw_batch_buf(b, 4, y, 0);
     qw_batch_bytes(b, 5, &a, sizeof a);
     qw_batch_dispatch(b, (N + 7) / 8, 1, 1, 256, 1, 1);
@@ -430,10 +439,11 @@ void enc_qmv(qw_batch *b, qw_kernel *k, const qw_buf *W, size_t woff, uint32_t N
 
 // h (+)= the previous block's output, x = rmsnorm(h) * w.  delta == &e->Pg means "the MoE combine of layer cmb_layer",
 // computed inside the norm kernel from Pg and that layer's selection record.
-void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_floats, uint32_t nb, int cmb_layer = -1) {
+void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_floats, uint32_t nb, int cmb_layer = -1, size_t delta_off = 0) {
     const uint32_t a[2] = {nb, (uint32_t)e->D};
     const bool cmb = delta == &e->Pg;
-    qw_batch_kernel(b, cmb ? (e->ep_fused ? e->k_norm_cmb_x : e->k_norm_cmb) : delta ? e->k_norm : e->k_norm0);
+    const bool gathered = delta == &e->epx;  // slot sharding: the rows were stored by the ranks that own the slots
+    qw_batch_kernel(b, cmb ? (e->ep_fused ? e->k_norm_cmb_x : e->k_norm_cmb) : gathered ? e->k_norm_x : delta ? e->k_norm : e->k_norm0);
     qw_batch_buf(b, 0, &e->h, 0);
     if (cmb) {
         qw_batch_buf(b, 5, &e->msel, (size_t)cmb_layer * e->sel_bytes);
@@ -442,7 +452,13 @@ void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_float
             qw_batch_buf(b, 7, &e->epx, 2 * e->pg_bytes);
             qw_batch_buf(b, 8, &e->rcnt, 64);
         } else qw_batch_buf(b, 6, &e->Pg, 0);
-    } else qw_batch_buf(b, 1, delta, 0);
+    } else if (delta) {
+        qw_batch_buf(b, 1, delta, delta_off);
+        if (gathered) {
+            qw_batch_buf(b, 7, &e->epx, 2 * e->pg_bytes);
+            qw_batch_buf(b, 8, &e->rcnt, 64);
+        }
+    }
     qw_batch_buf(b, 2, &e->small, w_off_floats * 4);
     qw_batch_buf(b, 3, &e->x, 0);
     qw_batch_bytes(b, 4, a, sizeof a);
@@ -471,12 +487,42 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
         qw_batch_dispatch(b, (D + 255) / 256, nb, 1, 256, 1, 1);
     }
     const qw_buf *pending = none;  // block output not yet added to the residual stream
+    // rows of the token mixers: all of them, or (slot sharding) the rows [lo, lo + nbl) whose slots this rank owns
+    const uint32_t lo = e->slot_shard ? e->row_lo : 0, nbl = e->slot_shard ? e->row_hi - e->row_lo : nb;
+    const size_t xo = (size_t)lo * D * 2, co = (size_t)lo * 4;  // byte offsets of row lo in x / ob and in the control arrays
+    const qw_buf *obuf = e->slot_shard ? &e->epx : &e->ob;
+    const size_t obo = e->slot_shard ? e->ob_off : 0;
+    // binds of a kernel that stores into every rank's buffer and publishes (moe_dn, the sharded out-projections, ep_publish)
+    auto bind_peers = [&](size_t peer_off, bool with_data) {
+        const uint32_t rk = (uint32_t)e->c.ep_rank;
+        qw_batch_buf(b, 11, &e->rcnt, 64);
+        qw_batch_bytes(b, 12, &rk, 4);
+        for (int r = 0; r < e->c.ep_size; r++) {
+            if (with_data) qw_batch_buf(b, 16 + r, &e->ep_peer[r], peer_off);
+            qw_batch_buf(b, 24 + r, &e->ep_peer[r], 2 * e->pg_bytes);
+        }
+    };
+    auto enc_out_proj = [&](qw_kernel *plain, qw_kernel *shared, size_t woff, uint32_t K, const qw_buf *in) {
+        if (!e->slot_shard) return enc_qmv(b, plain, &e->dense, woff, D, K, in, &e->ob, nb, D);
+        const qmv_args a = {D, K, D, nbl};
+        qw_batch_kernel(b, shared);
+        qw_batch_buf(b, 0, &e->dense, woff);
+        qw_batch_buf(b, 3, in, 0);
+        qw_batch_buf(b, 4, &e->epx, e->ob_off + xo);
+        qw_batch_bytes(b, 5, &a, sizeof a);
+        bind_peers(e->ob_off + xo, true);
+        qw_batch_dispatch(b, (D + 7) / 8, 1, 1, 256, 1, 1);
+    };
     for (int l = 0; l < e->L; l++) {
         const LayerW &w = e->layers[l];
         enc_norm(e, b, pending, w.small, nb, l - 1);  // h += previous block (the MoE combine of layer l-1); x = rmsnorm(h) * w1
-        if (w.attn) {
-            enc_qmv(b, e->k_qmv_in_a, &e->dense, w.w_in, e->qkv_rows, D, &e->x, &e->proj, nb, e->qkv_rows);
-            const qsa_args qa = {nb, (uint32_t)w.idx, (uint32_t)e->n_attn, e->qkv_rows, (uint32_t)e->max_pages, max_chunks, 0, 0};
+        if (nbl == 0) {  // no row of this rank in the step: only tell the others so
+            qw_batch_kernel(b, e->k_pub);
+            bind_peers(0, false);
+            qw_batch_dispatch(b, 1, 1, 1, 32, 1, 1);
+        } else if (w.attn) {
+            enc_qmv(b, e->k_qmv_in_a, &e->dense, w.w_in, e->qkv_rows, D, &e->x, &e->proj, nbl, e->qkv_rows, xo);
+            const qsa_args qa = {nbl, (uint32_t)w.idx, (uint32_t)e->n_attn, e->qkv_rows, (uint32_t)e->max_pages, max_chunks, 0, 0};
             qw_batch_kernel(b, e->k_prep);
             qw_batch_buf(b, 0, &e->proj, 0);
             qw_batch_buf(b, 1, &e->small, (w.small + 2 * D) * 4);
@@ -484,31 +530,31 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             qw_batch_buf(b, 3, &e->qb, 0);
             qw_batch_buf(b, 4, &e->kvpool, 0);
             qw_batch_buf(b, 5, &e->ptab, 0);
-            qw_batch_buf(b, 6, &e->ctl_d, 128 * 4);
-            qw_batch_buf(b, 7, &e->ctl_d, 64 * 4);
+            qw_batch_buf(b, 6, &e->ctl_d, 128 * 4 + co);
+            qw_batch_buf(b, 7, &e->ctl_d, 64 * 4 + co);
             qw_batch_bytes(b, 8, &qa, sizeof qa);
-            qw_batch_dispatch(b, e->QH + e->KVH, nb, 1, 256, 1, 1);
+            qw_batch_dispatch(b, e->QH + e->KVH, nbl, 1, 256, 1, 1);
             qw_batch_kernel(b, e->k_attn);
             qw_batch_buf(b, 0, &e->qb, 0);
             qw_batch_buf(b, 1, &e->kvpool, 0);
             qw_batch_buf(b, 2, &e->ptab, 0);
-            qw_batch_buf(b, 3, &e->ctl_d, 128 * 4);
-            qw_batch_buf(b, 4, &e->ctl_d, 64 * 4);
+            qw_batch_buf(b, 3, &e->ctl_d, 128 * 4 + co);
+            qw_batch_buf(b, 4, &e->ctl_d, 64 * 4 + co);
             qw_batch_buf(b, 5, &e->part, 0);
             qw_batch_bytes(b, 6, &qa, sizeof qa);
-            qw_batch_dispatch(b, max_chunks, e->KVH, nb, 128, 1, 1);
+            qw_batch_dispatch(b, max_chunks, e->KVH, nbl, 128, 1, 1);
             qw_batch_kernel(b, e->k_merge);
             qw_batch_buf(b, 0, &e->part, 0);
             qw_batch_buf(b, 1, &e->proj, 0);
             qw_batch_buf(b, 2, &e->ya, 0);
-            qw_batch_buf(b, 3, &e->ctl_d, 128 * 4);
+            qw_batch_buf(b, 3, &e->ctl_d, 128 * 4 + co);
             qw_batch_bytes(b, 4, &qa, sizeof qa);
-            qw_batch_dispatch(b, e->QH, nb, 1, 256, 1, 1);
-            enc_qmv(b, e->k_qmv_o_a, &e->dense, w.w_out, D, e->KA, &e->ya, &e->ob, nb, D);
+            qw_batch_dispatch(b, e->QH, nbl, 1, 256, 1, 1);
+            enc_out_proj(e->k_qmv_o_a, e->k_qmv_o_a_x, w.w_out, e->KA, &e->ya);
         } else {
-            enc_qmv(b, e->k_qmv_in_g, &e->dense, w.w_in, e->gdn_rows, D, &e->x, &e->proj, nb, e->gdn_rows);
+            enc_qmv(b, e->k_qmv_in_g, &e->dense, w.w_in, e->gdn_rows, D, &e->x, &e->proj, nbl, e->gdn_rows, xo);
             const size_t so = (w.small + 2 * D) * 4, sa = so + (size_t)e->C * 16;
-            const dn_epi_args ea = {nb, (uint32_t)w.idx, (uint32_t)e->n_gdn, e->gdn_rows};
+            const dn_epi_args ea = {nbl, (uint32_t)w.idx, (uint32_t)e->n_gdn, e->gdn_rows};
             qw_batch_kernel(b, e->k_epi);
             qw_batch_buf(b, 0, &e->proj, 0);
             qw_batch_buf(b, 1, &e->small, so);
@@ -518,10 +564,10 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             qw_batch_buf(b, 5, &e->cv, 0);
             qw_batch_buf(b, 6, &e->la, 0);
             qw_batch_buf(b, 7, &e->be, 0);
-            qw_batch_buf(b, 8, &e->ctl_d, 64 * 4);
+            qw_batch_buf(b, 8, &e->ctl_d, 64 * 4 + co);
             qw_batch_bytes(b, 9, &ea, sizeof ea);
-            qw_batch_dispatch(b, (e->C + 2 * e->HV + 255) / 256, nb, 1, 256, 1, 1);
-            const gdn_args ga = {nb, (uint32_t)w.idx, (uint32_t)e->n_gdn, e->gdn_rows};
+            qw_batch_dispatch(b, (e->C + 2 * e->HV + 255) / 256, nbl, 1, 256, 1, 1);
+            const gdn_args ga = {nbl, (uint32_t)w.idx, (uint32_t)e->n_gdn, e->gdn_rows};
             qw_batch_kernel(b, e->k_gdn);
             qw_batch_buf(b, 0, &e->cv, 0);
             qw_batch_buf(b, 1, &e->la, 0);
@@ -530,12 +576,12 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             qw_batch_buf(b, 4, &e->proj, (size_t)e->C * 2);
             qw_batch_buf(b, 5, &e->small, sa + 2 * e->HV * 4);
             qw_batch_buf(b, 6, &e->gy, 0);
-            qw_batch_buf(b, 7, &e->ctl_d, 64 * 4);
+            qw_batch_buf(b, 7, &e->ctl_d, 64 * 4 + co);
             qw_batch_bytes(b, 8, &ga, sizeof ga);
-            qw_batch_dispatch(b, e->HV, nb, 1, 512, 1, 1);
-            enc_qmv(b, e->k_qmv_o_g, &e->dense, w.w_out, D, e->KG, &e->gy, &e->ob, nb, D);
+            qw_batch_dispatch(b, e->HV, nbl, 1, 512, 1, 1);
+            enc_out_proj(e->k_qmv_o_g, e->k_qmv_o_g_x, w.w_out, e->KG, &e->gy);
         }
-        enc_norm(e, b, &e->ob, w.small + D, nb);  // h += mixer output; x = rmsnorm(h) * w2
+        enc_norm(e, b, obuf, w.small + D, nb, -1, obo);  // h += mixer output (all rows); x = rmsnorm(h) * w2
         // ---- MoE (gg_moe, src/engine.c:568-646)
         const size_t gu_bytes = (size_t)e->I * e->rbD, ex_bytes = (size_t)e->EL * gu_bytes, selo = (size_t)l * e->sel_bytes;
         const sel_args sa = {nb, (uint32_t)e->e_lo, (uint32_t)(e->e_lo + e->EL)};
@@ -573,15 +619,9 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
         if (e->ep_fused) {
             // every row goes into Pg[layer parity] of every rank; two buffers suffice because a rank can run at most one
             // down projection ahead of the slowest rank (its next norm waits for everybody's flags)
-            const uint32_t rk = (uint32_t)e->c.ep_rank;
             const size_t po = (size_t)(l & 1) * e->pg_bytes;
             qw_batch_buf(b, 9, &e->epx, po);
-            qw_batch_buf(b, 11, &e->rcnt, 64);
-            qw_batch_bytes(b, 12, &rk, 4);
-            for (int r = 0; r < e->c.ep_size; r++) {
-                qw_batch_buf(b, 16 + r, &e->ep_peer[r], po);
-                qw_batch_buf(b, 24 + r, &e->ep_peer[r], 2 * e->pg_bytes);
-            }
+            bind_peers(po, true);
         } else qw_batch_buf(b, 9, &e->Pg, 0);
         qw_batch_bytes(b, 10, &ebase, 4);
         qw_batch_dispatch(b, D / 64, nb * e->TOPK + 1, 1, 256, 1, 1);
@@ -633,11 +673,27 @@ uint32_t begin_step(qw_engine *e, const int *sids, const int32_t *toks, int B, i
         if (!reserve_pages(e, s, e->slots[s].pos + ahead)) return 0;
         maxpos = std::max(maxpos, e->slots[s].pos + ahead);
     }
+    // device row order: the caller's, or (slot sharding) grouped by the rank that owns the slot, stable within a rank, so
+    // that every rank's rows are one contiguous range -- the same order on every rank
+    for (int i = 0; i < B; i++) e->perm[i] = i;
+    e->row_lo = 0;
+    e->row_hi = (uint32_t)B;
+    if (e->slot_shard) {
+        const int n = e->c.ep_size;
+        std::stable_sort(e->perm, e->perm + B, [&](int a, int b2) { return sids[a] % n < sids[b2] % n; });
+        e->row_lo = e->row_hi = 0;
+        for (int j = 0; j < B; j++) {
+            const int own = sids[e->perm[j]] % n;
+            if (own < e->c.ep_rank) e->row_lo++;
+            if (own <= e->c.ep_rank) e->row_hi++;
+        }
+    }
     int32_t *ctl = (int32_t *)e->ctl_h.ptr;
-    for (int i = 0; i < B; i++) {
-        ctl[i] = toks[i];
-        ctl[64 + i] = sids[i];
-        ctl[128 + i] = e->slots[sids[i]].pos;
+    for (int j = 0; j < B; j++) {
+        const int i = e->perm[j];
+        ctl[j] = toks[i];
+        ctl[64 + j] = sids[i];
+        ctl[128 + j] = e->slots[sids[i]].pos;
     }
     // chunk count of the attention grid: a multiple of 8 pages so the recorded batch (and its graph) changes rarely
     uint32_t mc = (uint32_t)((maxpos + PAGE - 1) / PAGE);
@@ -669,7 +725,9 @@ extern "C" const float *qw_engine_par_step(qw_engine *e, const int *sids, const 
     encode_step(e, b, (uint32_t)B, mc, true, 0);
     const double secs = qw_batch_end(b);
     if (secs < 0) return e->fail("par_step: device batch failed"), nullptr;
-    if (!qw_buf_download(e->g, &e->logits, 0, e->logits_h.ptr, (size_t)B * e->V * 4)) return e->fail("par_step: logits copy failed"), nullptr;
+    for (int j = 0; j < B; j++)  // device row j is the caller's row perm[j]
+        if (!qw_buf_download(e->g, &e->logits, (size_t)j * e->V * 4, (float *)e->logits_h.ptr + (size_t)e->perm[j] * e->V, (size_t)e->V * 4))
+            return e->fail("par_step: logits copy failed"), nullptr;
     if (gpu_ms) *gpu_ms = secs * 1e3;
     end_step(e, sids, B, 1, (qw_now() - t0) * 1e3);
     return (const float *)e->logits_h.ptr;
@@ -685,7 +743,9 @@ extern "C" const int32_t *qw_engine_par_step_greedy(qw_engine *e, const int *sid
     if (secs < 0) return e->fail("par_step_greedy: device batch failed"), nullptr;
     if (gpu_ms) *gpu_ms = secs * 1e3;
     end_step(e, sids, B, 1, (qw_now() - t0) * 1e3);
-    return (const int32_t *)e->ids_h.ptr;
+    e->ids_out.resize(QW_PAR_MAX);
+    for (int j = 0; j < B; j++) e->ids_out[e->perm[j]] = ((const int32_t *)e->ids_h.ptr)[j];
+    return e->ids_out.data();
 }
 
 extern "C" int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, int nsteps, int32_t *out_ids, double *gpu_ms) {
@@ -702,7 +762,7 @@ extern "C" int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const 
         const double secs = qw_batch_end(b);
         if (secs < 0) return e->fail("par_decode_greedy: device batch failed at step %d", s), -1;
         total += secs;
-        memcpy(out_ids + (size_t)s * B, e->ids_h.ptr, (size_t)B * 4);
+        for (int j = 0; j < B; j++) out_ids[(size_t)s * B + e->perm[j]] = ((const int32_t *)e->ids_h.ptr)[j];
     }
     if (gpu_ms) *gpu_ms = total * 1e3;
     end_step(e, sids, B, nsteps, (qw_now() - t0) * 1e3);
@@ -794,7 +854,8 @@ extern "C" int qw_engine_ep_export(qw_engine *e, void *handle64) {
     if (e->L & 1) return e->fail("ep_export: the fused exchange alternates two buffers by layer and needs an even layer count"), -1;
     if (!e->epx.handle) {
         e->pg_bytes = (size_t)QW_PAR_MAX * (e->TOPK + 1) * e->D * 4;
-        if (!new_buf(e, &e->epx, 2 * e->pg_bytes + 256) || !qw_buf_zero(e->g, &e->epx, 0, e->epx.size)) return -1;
+        e->ob_off = 2 * e->pg_bytes + 256;  // [2][Pg] | flags | gathered mixer outputs fp16 [rows][D]
+        if (!new_buf(e, &e->epx, e->ob_off + (size_t)QW_PAR_MAX * e->D * 2) || !qw_buf_zero(e->g, &e->epx, 0, e->epx.size)) return -1;
     }
     if (!qw_buf_ipc_export(&e->epx, handle64)) return e->fail(qw_gpu_last_error(e->g)), -1;
     return 0;
@@ -816,5 +877,16 @@ extern "C" int qw_engine_ep_connect(qw_engine *e, const void *handles, int n) {
         return -1;
     if (!qw_buf_zero(e->g, &e->rcnt, 64, 8)) return -1;
     e->ep_fused = true;
+    // slot sharding needs the persistent out-projection kernel (K = 2048 or 4096); QW_SLOT_SHARD=0 keeps every rank on all rows
+    const char *ss = getenv("QW_SLOT_SHARD");
+    const bool shapes = !e->c.fma && (e->KA == 2048 || e->KA == 4096) && (e->KG == 2048 || e->KG == 4096);
+    if (shapes && !(ss && atoi(ss) == 0)) {
+        const long NBX = QW_PAR_MAX;
+        if (!compile(e, "qmv_mma", "qmv_out_attn_epx", {{"GF", 21}, {"KD", (long)e->KA}, {"NB", NBX}, {"YT_F32", 0}, {"EPX", n}}, &e->k_qmv_o_a_x) ||
+            !compile(e, "qmv_mma", "qmv_out_gdn_epx", {{"GF", 21}, {"KD", (long)e->KG}, {"NB", NBX}, {"YT_F32", 0}, {"EPX", n}}, &e->k_qmv_o_g_x) ||
+            !compile(e, "add_rmsnorm", "add_rmsnorm_epx", {{"ADD", 1}, {"EPX", n}}, &e->k_norm_x) || !compile(e, "ep_publish", "ep_publish", {{"EPX", n}}, &e->k_pub))
+            return -1;
+        e->slot_shard = true;
+    }
     return 0;
 }

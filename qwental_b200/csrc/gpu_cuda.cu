@@ -16,12 +16,21 @@
 
 // ------------------------------------------------------------------------------------------------ launch mode
 static int g_pdl = -1;
+static const char *g_pdl_family = "";
+void qw_pdl_current_family(const char *name) { g_pdl_family = name ? name : ""; }
 bool qw_pdl_enabled() {
     if (g_pdl < 0) {
         const char *e = getenv("QW_PDL");
         g_pdl = e ? (atoi(e) != 0) : 1;
     }
-    return g_pdl != 0;
+    if (!g_pdl) return false;
+    static const char *off = getenv("QW_PDL_OFF");  // comma-separated families launched without the attribute
+    if (off && *g_pdl_family) {
+        const size_t n = strlen(g_pdl_family);
+        for (const char *p = off; (p = strstr(p, g_pdl_family)) != nullptr; p += n)
+            if ((p == off || p[-1] == ',') && (p[n] == 0 || p[n] == ',')) return false;
+    }
+    return true;
 }
 void qw_set_pdl(bool on) { g_pdl = on ? 1 : 0; }
 extern "C" void qw_gpu_set_pdl(qw_gpu *, bool on) { qw_set_pdl(on); }
@@ -521,6 +530,7 @@ static cudaError_t launch_one(qw_batch *b, const Rec &r) {
     L.sm_count = b->g->sm_count;
     L.tables = b->g->tables;
     L.status = b->g->status_dev;
+    qw_pdl_current_family(r.k->fam->name);
     cudaError_t e = r.k->fam->fn(L);
     if (e == cudaSuccess) e = cudaPeekAtLastError();
     return e;

@@ -142,8 +142,8 @@ __global__ void __launch_bounds__(256) qsa_attn_k(const __half *q, const __half 
         for (uint32_t u = 0; u < U4; u++) {
             const bool ok = i + u < n;
             const uint32_t tk = ok ? i + u : i;
-            const uint4 kk = __ldg((const uint4 *)(Kp + (size_t)tk * HD));
-            vv[u] = __ldg((const uint4 *)(Vp + (size_t)tk * HD));
+            const uint4 kk = __ldcg((const uint4 *)(Kp + (size_t)tk * HD));
+            vv[u] = __ldcg((const uint4 *)(Vp + (size_t)tk * HD));
             const uint32_t w4[4] = {kk.x, kk.y, kk.z, kk.w};
             float d = 0.f;
 #pragma unroll

@@ -43,23 +43,8 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
                                                      unsigned *status) {
     __shared__ float tmp[32];
     pdl_sync();
-    if (MODE == 2 && nranks > 1) {
-        // expert-parallel: the rows of Pg were stored by every rank's down projection; wait (bounded, about 2 s) until each
-        // rank has published the sequence number this rank's own down projection has just reached
-        if (threadIdx.x < nranks) {
-            const unsigned want = *(volatile const unsigned *)seq;
-            const uint64_t t0 = global_ns();
-            while ((int)(ld_acquire_sys(flags + threadIdx.x) - want) < 0) {
-                const uint64_t dt = global_ns() - t0;
-                if (dt > 1000000ull && *(volatile unsigned *)status != 0) break;  // an earlier kernel already gave up: do not wait again
-                if (dt > 2000000000ull) {
-                    set_status(status, ST_PEER_TIMEOUT | threadIdx.x);
-                    break;
-                }
-            }
-        }
-        __syncthreads();
-    }
+    // rows of Pg (MODE 2) or of delta (MODE 1) may have been stored by other ranks: wait until every rank has published
+    if (nranks > 1) ep_wait(flags, seq, nranks, status);
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
     float *hr = h + (size_t)t * D;
     float wk[MOE_MAXK];
@@ -133,13 +118,39 @@ static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
                   nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
     } else if (L.def("ADD", 0)) {
         QW_CHECK_ARG(L.buf<void>(1) && L.avail(1) >= (size_t)a.nb * a.D * 2);
-        qw_launch(add_rmsnorm_k<1>, a.nb, 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0, nullptr, nullptr, 1, nullptr);
+        const uint32_t nranks = (uint32_t)L.def("EPX", 1);  // the delta rows were stored by the ranks that own the slots: same binds 7, 8
+        if (nranks > 1) QW_CHECK_ARG(nranks <= 8 && L.buf<void>(7) && L.avail(7) >= nranks * 4 && L.buf<void>(8) && L.avail(8) >= 4);
+        qw_launch(add_rmsnorm_k<1>, a.nb, 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0,
+                  nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
     } else {
         qw_launch(add_rmsnorm_k<0>, a.nb, 512, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, nullptr, nullptr, 0, nullptr, nullptr, 1, nullptr);
     }
     return cudaGetLastError();
 }
 QW_FAMILY(add_rmsnorm, launch_add_rmsnorm, 256)
+
+// A rank that has no row to contribute to an exchange still has to publish its sequence number.
+// binds: 11 = {seq, done} counters, 12 = {rank}, 24 + r = flag array of rank r; define EPX = number of ranks.  grid 1 x 32
+__global__ void ep_publish_k(const EpPeers ep) {
+    pdl_sync();
+    ep_publish(ep);
+}
+static cudaError_t launch_ep_publish(const QwLaunch &L) {
+    EpPeers ep{};
+    ep.nranks = (uint32_t)L.def("EPX", 0);
+    QW_CHECK_ARG(ep.nranks >= 2 && ep.nranks <= 8 && L.has_bytes(12, 4) && L.buf<unsigned>(11) && L.avail(11) >= 8);
+    ep.rank = L.bytes<uint32_t>(12);
+    QW_CHECK_ARG(ep.rank < ep.nranks);
+    ep.seq = L.buf<unsigned>(11);
+    ep.done = ep.seq + 1;
+    for (uint32_t r = 0; r < ep.nranks; r++) {
+        ep.flagR[r] = L.buf<unsigned>(24 + r);
+        QW_CHECK_ARG(ep.flagR[r] && L.avail(24 + r) >= ep.nranks * 4);
+    }
+    qw_launch(ep_publish_k, 1, 32, 0, L.stream, ep);
+    return cudaGetLastError();
+}
+QW_FAMILY(ep_publish, launch_ep_publish, 32)
 
 // binds: 0 = logits fp32 [nb][V], 1 = ids out int32 [nb], 2 = {nb, V}, 3 = second ids out (with IDS2 defined 1,
 // e.g. a host-visible copy).  grid nb x 1024

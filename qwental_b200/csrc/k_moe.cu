@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(256) moe_router_k(const __half *Wr, const __ha
         float acc = 0.f;
 #pragma unroll
         for (int c = 0; c < CH; c++) {
-            const uint4 xv = __ldg(xt + lane + 32 * c);
+            const uint4 xv = __ldcg(xt + lane + 32 * c);
             const uint32_t a4[4] = {wr[c].x, wr[c].y, wr[c].z, wr[c].w}, b4[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -267,7 +267,7 @@ __global__ void __launch_bounds__(512) moe_route_k(const __half *Wr, const __hal
         const uint32_t nt = a.nb - t0 < 16 ? a.nb - t0 : 16;
         if (t0) __syncthreads();
         for (uint32_t e = threadIdx.x; e < nt * (D / 8); e += 512) {
-            const uint4 v = __ldg((const uint4 *)(x + (size_t)t0 * D) + e);
+            const uint4 v = __ldcg((const uint4 *)(x + (size_t)t0 * D) + e);
             const uint32_t tl = e / (D / 8), ce = e % (D / 8), c = ce >> 5, ln = ce & 31;
             const float2 f0 = __half22float2(*(const __half2 *)&v.x), f1 = __half22float2(*(const __half2 *)&v.y);
             const float2 f2 = __half22float2(*(const __half2 *)&v.z), f3 = __half22float2(*(const __half2 *)&v.w);
@@ -352,9 +352,7 @@ struct MoeP {
     // expert-parallel exchange fused into the down projection (nranks > 1): every output row is stored into the Pg
     // buffer of every rank (peer memory), then the last block publishes this rank's sequence number to every rank
     float *PgR[8];              // Pg of rank r (PgR[rank] is the local one)
-    unsigned *flagR[8];         // flag array of rank r: slot [q] = sequence number rank q has completed
-    unsigned *seq, *done;       // local: sequence counter, finished-block counter
-    uint32_t nranks, rank;
+    EpPeers ep;                 // ep.nranks == 1: single GPU or NCCL exchange
 };
 
 constexpr int MOE_STG = 2;                             // staged tiles per team (28 KB each)
@@ -522,7 +520,7 @@ __global__ void __launch_bounds__(512, 1) moe_gu_k(const MoeP p) {
                 const uint4 zero = make_uint4(0, 0, 0, 0);
                 const uint4 *xr = (const uint4 *)(p.x + (size_t)tok * p.D) + ks * 32 + t;
 #pragma unroll
-                for (int ib = 0; ib < 8; ib++) xf[ib] = have ? __ldg(xr + 4 * ib) : zero;
+                for (int ib = 0; ib < 8; ib++) xf[ib] = have ? __ldcg(xr + 4 * ib) : zero;
             }
         }
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -650,7 +648,7 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
                     uint32_t tok = 0, rank = 0;
                     uint4 v = make_uint4(0, 0, 0, 0);
                     if (moe_entry(ms, u, U, e0, c0, cnt, topk, col, tok, rank))
-                        v = __ldg((const uint4 *)((pc < 8 ? p.Hhi : p.Hlo) + ((size_t)tok * (topk + 1) + rank) * p.I) + kk);
+                        v = __ldcg((const uint4 *)((pc < 8 ? p.Hhi : p.Hlo) + ((size_t)tok * (topk + 1) + rank) * p.I) + kk);
                     *(uint4 *)(hs + (size_t)pc * hs_stride + kk * 16) = v;
                 }
                 uint32_t tok = 0, rank = 0;
@@ -677,8 +675,8 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
             if (lane == 0) mbar_arrive(&empty[s]);  // this warp has read the tile
             // acc[0], acc[2] = rows 2g and 2g + 1 of column 2t; acc[1], acc[3] = the same rows of column 2t + 1
             const uint32_t row = tile * MOE_DN_ROWS + 16 * warp + 2 * g;
-            if (p.nranks > 1) {
-                for (uint32_t r = 0; r < p.nranks; r++) {
+            if (p.ep.nranks > 1) {
+                for (uint32_t r = 0; r < p.ep.nranks; r++) {
                     if (oo[0] != 0xffffffffu) *(float2 *)(p.PgR[r] + oo[0] + row) = make_float2(acc[0], acc[2]);
                     if (oo[1] != 0xffffffffu) *(float2 *)(p.PgR[r] + oo[1] + row) = make_float2(acc[1], acc[3]);
                 }
@@ -689,21 +687,7 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
         }
         if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 3);
     }
-    if (p.nranks > 1) {
-        // publish: every thread makes its peer stores visible system-wide, the block counts itself done, the last block
-        // advances this rank's sequence number and writes it into slot [rank] of every rank's flag array
-        __threadfence_system();
-        __syncthreads();
-        if (tid == 0) {
-            if (atomicAdd(p.done, 1u) == gridDim.x - 1) {
-                *p.done = 0;
-                const unsigned sv = *p.seq + 1;
-                *p.seq = sv;
-                __threadfence_system();
-                for (uint32_t r = 0; r < p.nranks; r++) st_release_sys(p.flagR[r] + p.rank, sv);
-            }
-        }
-    }
+    if (p.ep.nranks > 1) ep_publish(p.ep);
 }
 
 // binds (gate/up): 0 = Wg, 1 = Wu, 2 = shared gate, 3 = shared up (used unless SHARED is defined 0), 4 = x, 5 = moe_sel,
@@ -732,23 +716,22 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
     p.Pg = L.buf<float>(9);
     p.tab = (const QwTables *)L.tables;
     p.status = L.status;
-    p.nranks = 1;
-    p.rank = 0;
-    p.seq = p.done = nullptr;
-    for (int r = 0; r < 8; r++) p.PgR[r] = nullptr, p.flagR[r] = nullptr;
+    p.ep = EpPeers{};
+    p.ep.nranks = 1;
+    for (int r = 0; r < 8; r++) p.PgR[r] = nullptr;
     if (down && L.def("EPX", 0) > 1) {
         // binds 16 + r = Pg of rank r, 24 + r = flag array of rank r, 11 = {seq, done} counters (local, 8 bytes, zeroed),
         // 12 = {rank}; define EPX = number of ranks (2..8)
-        p.nranks = (uint32_t)L.def("EPX", 0);
-        QW_CHECK_ARG(p.nranks <= 8 && L.has_bytes(12, 4) && L.buf<unsigned>(11) && L.avail(11) >= 8);
-        p.rank = L.bytes<uint32_t>(12);
-        QW_CHECK_ARG(p.rank < p.nranks);
-        p.seq = L.buf<unsigned>(11);
-        p.done = p.seq + 1;
-        for (uint32_t r = 0; r < p.nranks; r++) {
+        p.ep.nranks = (uint32_t)L.def("EPX", 0);
+        QW_CHECK_ARG(p.ep.nranks <= 8 && L.has_bytes(12, 4) && L.buf<unsigned>(11) && L.avail(11) >= 8);
+        p.ep.rank = L.bytes<uint32_t>(12);
+        QW_CHECK_ARG(p.ep.rank < p.ep.nranks);
+        p.ep.seq = L.buf<unsigned>(11);
+        p.ep.done = p.ep.seq + 1;
+        for (uint32_t r = 0; r < p.ep.nranks; r++) {
             p.PgR[r] = L.buf<float>(16 + r);
-            p.flagR[r] = L.buf<unsigned>(24 + r);
-            QW_CHECK_ARG(p.PgR[r] && p.flagR[r] && L.avail(24 + r) >= p.nranks * 4);
+            p.ep.flagR[r] = L.buf<unsigned>(24 + r);
+            QW_CHECK_ARG(p.PgR[r] && p.ep.flagR[r] && L.avail(24 + r) >= p.ep.nranks * 4);
         }
     }
     // experts held in the bound weight buffers: EL of them starting at id bytes(10) (default: all E from 0);
@@ -769,7 +752,7 @@ static cudaError_t moe_fill(const QwLaunch &L, MoeP &p, uint32_t &E, uint32_t &t
         p.tiles = p.I / 16;
     } else {
         QW_CHECK_ARG(p.Pg && L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
-        for (uint32_t r = 0; r < p.nranks && p.nranks > 1; r++) QW_CHECK_ARG(L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
+        for (uint32_t r = 0; r < p.ep.nranks && p.ep.nranks > 1; r++) QW_CHECK_ARG(L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
         p.tiles = p.D / MOE_DN_ROWS;
     }
     return cudaSuccess;

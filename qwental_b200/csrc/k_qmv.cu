@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(256) qmv_gg_k(const uint8_t *W, const __half *
                 float p = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const uint4 q = __ldg(xp + i);
+                    const uint4 q = __ldcg(xp + i);
                     const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -169,6 +169,10 @@ struct QmvMmaP {
     unsigned *status;
     uint32_t N, K, rb, xstride, ystride, nb, items;
     uint32_t rs;  // qmv_mma2: distance of the rows of a staged tile in shared memory (rb plus padding against bank conflicts)
+    // qmv_mma2 with EPX defined: the fp16 output rows are stored into the buffer of every rank (peer memory) and the kernel
+    // publishes afterwards -- the all-gather of a projection that every rank runs for its own slots only
+    void *yR[8];
+    EpPeers ep;  // ep.nranks <= 1: plain local output
 };
 
 constexpr int QMV_STAGES = 3;
@@ -336,7 +340,7 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
             const uint32_t col = c0 + g + 8 * nt;
             const uint4 *xr = (const uint4 *)(p.x + (size_t)col * p.xstride) + warp * 32 + t;
 #pragma unroll
-            for (int ib = 0; ib < 8; ib++) xf[nt][ib] = col < p.nb ? __ldg(xr + 4 * ib) : zero;
+            for (int ib = 0; ib < 8; ib++) xf[nt][ib] = col < p.nb ? __ldcg(xr + 4 * ib) : zero;
         }
     };
     pdl_wait();  // weight tiles and the codebook are static; the activations (and the output buffer) are not
@@ -372,12 +376,16 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
                 const uint32_t row = item * 16 + (ln >> 2) + 8 * (jj >> 1), col = ps * 16 + nt * 8 + 2 * (ln & 3) + (jj & 1);
                 if (col < p.nb && row < p.N) {
                     if (F32OUT) ((float *)p.y)[(size_t)col * p.ystride + row] = sum;
-                    else ((__half *)p.y)[(size_t)col * p.ystride + row] = __float2half_rn(sum);
+                    else if (p.ep.nranks > 1) {
+                        const __half hv = __float2half_rn(sum);
+                        for (uint32_t r = 0; r < p.ep.nranks; r++) ((__half *)p.yR[r])[(size_t)col * p.ystride + row] = hv;
+                    } else ((__half *)p.y)[(size_t)col * p.ystride + row] = __float2half_rn(sum);
                 }
             }
         }
     }
     if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 5);
+    if (!F32OUT && p.ep.nranks > 1) ep_publish(p.ep);
 }
 
 template <int GF, int WARPS, int TEAMS, bool F32OUT>
@@ -408,7 +416,7 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     // rows per item: fixed by the matrix shape alone (never by the batch), so results do not depend on nb
     const int mt = 1;
     QW_CHECK_ARG(a.N % (16 * mt) == 0 && ((uintptr_t)L.buf<uint8_t>(0) & 15) == 0 && (16 * rb) % 16 == 0);
-    QmvMmaP p;
+    QmvMmaP p{};
     p.W = L.buf<uint8_t>(0);
     p.x = L.buf<__half>(3);
     p.y = L.buf<void>(4);
@@ -425,6 +433,22 @@ static cudaError_t launch_qmv_mma(const QwLaunch &L) {
         if (gf == 21 ? (wds % 8 == 4) : (wds % 16 == 8)) {
             p.rs = rb + pad;
             break;
+        }
+    }
+    const uint32_t epx = (uint32_t)L.def("EPX", 0);
+    if (epx > 1) {
+        // binds 16 + r = y of rank r (row 0 = this rank's first row, as bind 4), 24 + r = flag array of rank r,
+        // 11 = {seq, done} counters, 12 = {rank}; only for the fp16-output IQ3_S projections of the persistent kernel
+        QW_CHECK_ARG(epx <= 8 && !f32 && gf == 21 && (K == 2048 || K == 4096) && L.has_bytes(12, 4) && L.buf<unsigned>(11) && L.avail(11) >= 8);
+        p.ep.nranks = epx;
+        p.ep.rank = L.bytes<uint32_t>(12);
+        QW_CHECK_ARG(p.ep.rank < epx);
+        p.ep.seq = L.buf<unsigned>(11);
+        p.ep.done = p.ep.seq + 1;
+        for (uint32_t r = 0; r < epx; r++) {
+            p.yR[r] = L.buf<void>(16 + r);
+            p.ep.flagR[r] = L.buf<unsigned>(24 + r);
+            QW_CHECK_ARG(p.yR[r] && p.ep.flagR[r] && L.avail(24 + r) >= epx * 4 && L.avail(16 + r) >= ((size_t)(a.nb - 1) * a.ystride + a.N) * 2);
         }
     }
 #define GO(G, M)                                                        \

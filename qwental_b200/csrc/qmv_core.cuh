@@ -109,10 +109,10 @@ __device__ __forceinline__ void unit_mma(const uint8_t *u0, const uint8_t *u1, c
         for (int nt = 0; nt < NT; nt++) {
             if (!(tile_on >> nt & 1)) continue;  // warp-uniform
             const uint4 zero = make_uint4(0, 0, 0, 0);
-            const uint4 xv = xcol[nt] ? __ldg(xcol[nt] + kk) : zero;
+            const uint4 xv = xcol[nt] ? __ldcg(xcol[nt] + kk) : zero;
             float p[4] = {0.f, 0.f, 0.f, 0.f};
             if (BF16) {
-                const uint4 xl = xcol[nt] ? __ldg(xlo[nt] + kk) : zero;
+                const uint4 xl = xcol[nt] ? __ldcg(xlo[nt] + kk) : zero;
                 mma_bf16(p, a0, xv.x, xv.y, p);
                 mma_bf16(p, a1, xv.z, xv.w, p);
                 mma_bf16(p, a0, xl.x, xl.y, p);

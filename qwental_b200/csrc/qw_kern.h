@@ -68,8 +68,9 @@ cudaError_t qw_tables_create(void **out, cudaStream_t s);
 // still finishing, runs its data-independent prologue (barrier set-up, lookup tables, staging of weights) and blocks in
 // pdl_wait() (common.cuh) until the predecessor's results are complete and visible.  Every kernel of this library
 // calls pdl_wait() before it reads or writes anything a predecessor may touch.
-bool qw_pdl_enabled();
+bool qw_pdl_enabled();  // for the kernel family being launched (QW_PDL_OFF=name,name excludes families, for debugging)
 void qw_set_pdl(bool on);
+void qw_pdl_current_family(const char *name);
 template <typename... KArgs, typename... Args>
 static inline cudaError_t qw_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
     cudaLaunchConfig_t cfg = {};

@@ -114,3 +114,23 @@ def test_slot_errors_and_accounting(eng):
     assert eng.pick(busy=0b1111111) == 7
     eng.finish(3)
     assert eng.pos(3) == -1 and eng.pick(busy=0) in (1, 2, 3, 4, 7)
+
+
+@pytest.mark.parametrize("attn_every", [4, 1])
+def test_fresh_engines_agree_bit_for_bit(gpu, attn_every):
+    """Two engines opened one after the other (so the second one's buffers hold the first one's leftovers) produce the
+    same logits, bit for bit, with dependent launch on: a kernel that read its predecessor's output too early, or through a
+    non-coherent path, shows up here as run-to-run noise."""
+    from qwental_b200.engine import Engine, wide_cfg
+    outs = []
+    for _ in range(3):
+        e = Engine(gpu, wide_cfg(layers=2, attn_every=attn_every))
+        for sid, n in CTX.items():
+            e.seed_slot(sid, n, 1000 + sid)
+        lg, _ = e.step([0, 3, 5, 6], [7, 100, 511, 0])
+        lg2, _ = e.step([0, 5], [1, 2])
+        outs.append((lg.copy(), lg2.copy()))
+        e.close()
+    for a, b2 in outs[1:]:
+        assert np.array_equal(a.view(np.uint32), outs[0][0].view(np.uint32))
+        assert np.array_equal(b2.view(np.uint32), outs[0][1].view(np.uint32))

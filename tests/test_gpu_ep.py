@@ -1,7 +1,10 @@
 """Expert-parallel decode step on 2 GPUs (skipped with fewer): experts sharded over the ranks, everything else
 replicated.  Two exchanges are covered: one NCCL all-reduce per MoE layer, and the fused one (the down projection
-stores its rows into every rank's buffer over NVLink and the next norm waits on sequence flags).  The logits of every
-rank must be bit-identical to the single-GPU step (each exchanged row has exactly one contributor)."""
+stores its rows into every rank's buffer over NVLink and the next norm waits on sequence flags).  With the fused exchange
+on full-size layer shapes the slots are sharded too: attention and Gated DeltaNet run only on the rank that owns a slot and
+the out-projection's rows are gathered the same way -- covered with rows on both ranks and with a step in which one rank
+owns no row at all.  The logits of every rank must be bit-identical to the single-GPU step (each exchanged row has exactly
+one contributor)."""
 import os
 
 import numpy as np
@@ -13,23 +16,34 @@ CTX = {0: 300, 2: 17, 5: 700}
 SIDS, TOKS = [0, 2, 5], [5, 9, 33]
 
 
+def _cfg(fused, **kw):
+    from qwental_b200.engine import tiny_cfg, wide_cfg
+    return wide_cfg(**kw) if fused else tiny_cfg(**kw)
+
+
+def _steps(eng):
+    for s, n in CTX.items():
+        eng.seed_slot(s, n, 1000 + s)
+    l1, _ = eng.step(SIDS, TOKS)
+    l2, _ = eng.step(SIDS, list(l1.argmax(1).astype(np.int32)))
+    l3, _ = eng.step([2, 0], [7, 8])  # even slots only: with two ranks and slot sharding rank 1 owns no row of this step
+    ids, _ = eng.decode_greedy(SIDS, TOKS, 3)
+    return l1, l2, l3, ids
+
+
 def _worker(rank, world, uid, q, up, down):
     os.environ["QW_CUDA_DEVICE"] = str(rank)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    from qwental_b200.engine import Engine, tiny_cfg
+    from qwental_b200.engine import Engine
     from qwental_b200.gpu import Gpu
     gpu = Gpu()
-    eng = Engine(gpu, tiny_cfg(ep_rank=rank, ep_size=world))
+    eng = Engine(gpu, _cfg(uid is None, ep_rank=rank, ep_size=world))
     if uid is not None:
         eng.ep_init(uid)
     else:  # fused exchange: the parent gathers the buffer handles and hands the list back
         up.put((rank, eng.ep_export()))
         eng.ep_connect(down.get(timeout=120))
-    for s, n in CTX.items():
-        eng.seed_slot(s, n, 1000 + s)
-    l1, _ = eng.step(SIDS, TOKS)
-    l2, _ = eng.step(SIDS, list(l1.argmax(1).astype(np.int32)))
-    q.put((rank, l1, l2))
+    q.put((rank,) + _steps(eng))
     down.get(timeout=120)  # nobody unmaps or frees an exchange buffer before every rank has finished stepping
     eng.close()
     gpu.close()
@@ -41,7 +55,7 @@ def test_expert_parallel_step_bit_identical_to_single_gpu(fused):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
-    from qwental_b200.engine import Engine, ep_unique_id, tiny_cfg
+    from qwental_b200.engine import Engine, ep_unique_id
     from qwental_b200.gpu import Gpu
     uid = None if fused else ep_unique_id()
     ctx = mp.get_context("spawn")
@@ -61,13 +75,11 @@ def test_expert_parallel_step_bit_identical_to_single_gpu(fused):
         p.join(60)
         assert p.exitcode == 0
     gpu = Gpu()
-    eng = Engine(gpu, tiny_cfg())
-    for s, n in CTX.items():
-        eng.seed_slot(s, n, 1000 + s)
-    r1, _ = eng.step(SIDS, TOKS)
-    r2, _ = eng.step(SIDS, list(r1.argmax(1).astype(np.int32)))
+    eng = Engine(gpu, _cfg(fused))
+    ref = _steps(eng)
     eng.close()
     gpu.close()
-    for rank, l1, l2 in res:
-        assert np.array_equal(l1.view(np.uint32), r1.view(np.uint32)), rank
-        assert np.array_equal(l2.view(np.uint32), r2.view(np.uint32)), rank
+    for r in res:
+        for got, want in zip(r[1:4], ref[:3]):
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r[0]
+        assert np.array_equal(r[4], ref[3]), r[0]
