@@ -74,27 +74,29 @@ struct gdn_args {
     uint32_t nb, layer, nlayers, z_stride;  // z: fp16 rows of stride z_stride (the z part of the projection)
 };
 
-// One block per (v-head, slot): 512 threads, thread (qr = tid / 128, c = tid % 128) holds the 32 rows
-// 32 qr .. 32 qr + 31 of column c of the head's [DK][DV] state in registers.  Row reads are 512-byte coalesced.
+// One block per (v-head, slot): 512 threads, thread (rq = tid / 32, c4 = tid % 32) holds rows 8 rq .. 8 rq + 7 of columns
+// 4 c4 .. 4 c4 + 3 of the head's [DK][DV] state in registers: every state access is a 16-byte load or store and a warp
+// moves one whole 512-byte row per instruction.  The 16 row groups meet in shared memory (summed in group order).
 // binds: 0 = cv fp16 [nb][C], 1 = la [nb][HV], 2 = beta [nb][HV], 3 = state pool fp32 [slot][nlayers][HV][DK][DV],
 // 4 = z fp16, 5 = norm weight fp32 [DV], 6 = gy out fp16 [nb][HV*DV], 7 = slot ids, 8 = gdn_args; with O_OUT
 // defined 1 also 9 = o out fp16 [nb][HV*DV] (the un-normalised output, for tests).  grid (HV, nb) x 512
 template <bool TILED>
-__global__ void __launch_bounds__(512) gdn_fstep_k(const __half *cv, const float *la, const float *beta, float *pool, const __half *z,
+__global__ void __launch_bounds__(512, 2) gdn_fstep_k(const __half *cv, const float *la, const float *beta, float *pool, const __half *z,
                                                   const float *nw, __half *gy, const int32_t *sids, __half *oo, gdn_args a, uint32_t HK, uint32_t HV) {
     constexpr int DK = 128, DV = 128;
-    __shared__ float ks[DK], qs[DK], part[4][DV], red[8];
+    __shared__ float ks[DK], qs[DK], red[8];
+    __shared__ float4 part[16][32];
     pdl_sync();
-    const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c = tid & 127, qr = tid >> 7, lane = tid & 31, warp = tid >> 5;
+    const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c4 = tid & 31, rq = tid >> 5, lane = tid & 31, warp = tid >> 5;
     const uint32_t hk = TILED ? hv % HK : hv / (HV / HK);
     const uint32_t C = 2 * HK * DK + HV * DV;
     const __half *row = cv + (size_t)t * C;
-    float *S = pool + (((size_t)sids[t] * a.nlayers + a.layer) * HV + hv) * DK * DV;
+    float4 *S = (float4 *)(pool + (((size_t)sids[t] * a.nlayers + a.layer) * HV + hv) * DK * DV) + c4;
 
-    // state column into registers (issued first: the long-latency part)
-    float s[32];
+    // state rows into registers (issued first: the long-latency part)
+    float4 s[8];
 #pragma unroll
-    for (int i = 0; i < 32; i++) s[i] = S[(size_t)(32 * qr + i) * DV + c];
+    for (int i = 0; i < 8; i++) s[i] = S[(size_t)(8 * rq + i) * (DV / 4)];
 
     // q / k L2 normalisation (threads 0..127 take q, 128..255 take k)
     float xv = 0.f;
@@ -113,30 +115,44 @@ __global__ void __launch_bounds__(512) gdn_fstep_k(const __half *cv, const float
     __syncthreads();
 
     const float gdec = expf(la[t * HV + hv]), b = beta[t * HV + hv];
-    float mem = 0.f;
+    float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-        s[i] = s[i] * gdec;
-        mem = fmaf(s[i], ks[32 * qr + i], mem);
+    for (int i = 0; i < 8; i++) {
+        const float kk = ks[8 * rq + i];
+        s[i].x *= gdec; s[i].y *= gdec; s[i].z *= gdec; s[i].w *= gdec;
+        mem.x = fmaf(s[i].x, kk, mem.x); mem.y = fmaf(s[i].y, kk, mem.y); mem.z = fmaf(s[i].z, kk, mem.z); mem.w = fmaf(s[i].w, kk, mem.w);
     }
-    part[qr][c] = mem;
+    part[rq][c4] = mem;
     __syncthreads();
-    mem = ((part[0][c] + part[1][c]) + part[2][c]) + part[3][c];
-    const float d = b * (__half2float(row[2 * HK * DK + hv * DV + c]) - mem);
-    __syncthreads();
-    float out = 0.f;
+    mem = part[0][c4];
 #pragma unroll
-    for (int i = 0; i < 32; i++) {
-        s[i] = fmaf(ks[32 * qr + i], d, s[i]);
-        out = fmaf(s[i], qs[32 * qr + i], out);
+    for (int r = 1; r < 16; r++) {
+        const float4 pv = part[r][c4];
+        mem.x += pv.x; mem.y += pv.y; mem.z += pv.z; mem.w += pv.w;
     }
-    part[qr][c] = out;
-#pragma unroll
-    for (int i = 0; i < 32; i++) S[(size_t)(32 * qr + i) * DV + c] = s[i];
+    const uint2 vraw = *(const uint2 *)(row + 2 * HK * DK + hv * DV + 4 * c4);
+    const float2 v01 = __half22float2(*(const __half2 *)&vraw.x), v23 = __half22float2(*(const __half2 *)&vraw.y);
+    const float4 d = make_float4(b * (v01.x - mem.x), b * (v01.y - mem.y), b * (v23.x - mem.z), b * (v23.y - mem.w));
     __syncthreads();
+    float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float kk = ks[8 * rq + i], qq = qs[8 * rq + i];
+        s[i].x = fmaf(kk, d.x, s[i].x); s[i].y = fmaf(kk, d.y, s[i].y); s[i].z = fmaf(kk, d.z, s[i].z); s[i].w = fmaf(kk, d.w, s[i].w);
+        out.x = fmaf(s[i].x, qq, out.x); out.y = fmaf(s[i].y, qq, out.y); out.z = fmaf(s[i].z, qq, out.z); out.w = fmaf(s[i].w, qq, out.w);
+    }
+    part[rq][c4] = out;
+#pragma unroll
+    for (int i = 0; i < 8; i++) S[(size_t)(8 * rq + i) * (DV / 4)] = s[i];
+    __syncthreads();
+    float o1 = 0.f;
+    const uint32_t c = tid;  // threads 0..127: one output column each
     if (tid < 128) {
-        out = ((part[0][c] + part[1][c]) + part[2][c]) + part[3][c];
-        const __half oh = __float2half_rn(out);
+        const float *pc = (const float *)&part[0][0] + c;
+        o1 = pc[0];
+#pragma unroll
+        for (int r = 1; r < 16; r++) o1 += pc[r * 128];
+        const __half oh = __float2half_rn(o1);
         if (oo) oo[(size_t)t * HV * DV + hv * DV + c] = oh;
         const float x = __half2float(oh);  // the norm sees the fp16-rounded output (kernels/gdn_decode.metal:386,408)
         const float p = warp_sum(x * x);
@@ -145,7 +161,7 @@ __global__ void __launch_bounds__(512) gdn_fstep_k(const __half *cv, const float
     __syncthreads();
     if (tid < 128) {
         const float r = rsqrtf((((red[0] + red[1]) + red[2]) + red[3]) / DV + GDN_EPS);
-        const float x = __half2float(__float2half_rn(out));
+        const float x = __half2float(__float2half_rn(o1));
         const float zz = __half2float(z[(size_t)t * a.z_stride + hv * DV + c]);
         gy[(size_t)t * HV * DV + hv * DV + c] = __float2half_rn(x * r * nw[c] * (1.0f / (1.0f + expf(-zz))));
     }

@@ -165,8 +165,9 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         if (e >= a.e_lo && e < a.e_hi) atomicOr(t < 32 ? &mlo[e] : &mhi[e], 1u << (t & 31));
     }
     __syncthreads();
-    {   // exclusive scans over experts (thread e = expert e): entries and non-empty flags
-        const uint32_t c = tid < E ? __popc(mlo[tid]) + __popc(mhi[tid]) : 0, f = c ? 1u : 0u;
+    {   // exclusive scans over experts (thread e = expert e): entries (low 16 bits of one word) and passes of 8 entries
+        // (high 16 bits: what the gate/up and down kernels enumerate their work units by), and non-empty flags
+        const uint32_t c0 = tid < E ? __popc(mlo[tid]) + __popc(mhi[tid]) : 0, f = c0 ? 1u : 0u, c = c0 | (((c0 + 7) / 8) << 16);
         uint32_t sc = c, sf = f;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -187,17 +188,20 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         }
         __syncthreads();
         const uint32_t bc = warp ? wsum[0][warp - 1] : 0, bf = warp ? wsum[1][warp - 1] : 0;
-        pos[tid] = bc + sc - c;   // first entry of expert tid
-        grp[tid] = bf + sf - f;   // group number of expert tid (if non-empty)
-        if (c) {
+        const uint32_t ex = bc + sc - c;  // exclusive prefix: entries | passes << 16
+        pos[tid] = ex & 0xffffu;          // first entry of expert tid
+        grp[tid] = bf + sf - f;           // group number of expert tid (if non-empty)
+        if (c0) {
             ms->ue[bf + sf - f] = tid;
-            ms->off[bf + sf - f] = bc + sc - c;
+            ms->off[bf + sf - f] = ex & 0xffffu;
+            ms->pre[bf + sf - f] = ex >> 16;
         }
         if (tid == NTH - 1) {
             ms->U = bf + sf;
             ms->nb = a.nb;
             ms->topk = topk;
-            ms->off[bf + sf] = bc + sc;
+            ms->off[bf + sf] = (bc + sc) & 0xffffu;
+            ms->pre[bf + sf] = (bc + sc) >> 16;
         }
     }
     __syncthreads();
@@ -379,31 +383,16 @@ struct MoeSched {
 };
 template <int NTHR>
 __device__ __forceinline__ MoeSched moe_sched(const moe_sel *ms, bool shared_expert, uint32_t tiles, uint32_t *pre, int tid, uint32_t team_id, uint32_t teams) {
+    // the selection already left the prefix sums of passes over the routed groups (ms->pre[0..U]); all loads here are
+    // independent of one another, so the table is in shared memory after one memory latency
     MoeSched w;
+    for (uint32_t gi = tid; gi <= MOE_MAXE; gi += NTHR) pre[gi] = ms->pre[gi];
     w.U = ms->U;
     w.nb = ms->nb;
     w.topk = ms->topk;
     w.groups = w.U + (shared_expert ? 1u : 0u);
-    for (uint32_t gi = tid; gi < w.groups; gi += NTHR) {
-        const uint32_t c = gi < w.U ? ms->off[gi + 1] - ms->off[gi] : w.nb;
-        pre[gi + 1] = (c + 7) / 8;
-    }
-    if (tid == 0) pre[0] = 0;
     __syncthreads();
-    if (tid < 32) {  // inclusive scan of pre[1..groups] in chunks of 32
-        uint32_t carry = 0;
-        for (uint32_t b0 = 1; b0 <= w.groups; b0 += 32) {
-            const uint32_t idx = b0 + tid;
-            uint32_t v = idx <= w.groups ? pre[idx] : 0;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t n = __shfl_up_sync(0xffffffffu, v, o);
-                if (tid >= o) v += n;
-            }
-            if (idx <= w.groups) pre[idx] = v + carry;
-            carry += __shfl_sync(0xffffffffu, v, 31);
-        }
-    }
+    if (tid == 0 && shared_expert) pre[w.U + 1] = pre[w.U] + (w.nb + 7) / 8;
     __syncthreads();
     const uint32_t total = pre[w.groups] * tiles;
     w.i0 = (uint32_t)((uint64_t)total * team_id / teams);

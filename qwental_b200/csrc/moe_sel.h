@@ -16,5 +16,6 @@ struct moe_sel {
     uint32_t ue[MOE_MAXE];                    // expert of group u
     uint32_t off[MOE_MAXE + 1];               // entries of group u: ent[off[u] .. off[u+1])
     uint16_t ent[MOE_MAXB * MOE_MAXK];        // token << 8 | rank
+    uint32_t pre[MOE_MAXE + 2];               // passes of 8 entries in the groups before u (pre[U] = all routed passes)
 };
 

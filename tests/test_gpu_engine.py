@@ -134,3 +134,26 @@ def test_fresh_engines_agree_bit_for_bit(gpu, attn_every):
     for a, b2 in outs[1:]:
         assert np.array_equal(a.view(np.uint32), outs[0][0].view(np.uint32))
         assert np.array_equal(b2.view(np.uint32), outs[0][1].view(np.uint32))
+
+
+def test_full_batch_of_64_rows_matches_each_slot_alone(gpu):
+    """The largest batch the step accepts (QW_PAR_MAX = 64 rows, contexts straddling page boundaries): a sample of its rows
+    is bit-identical to the same slots stepped alone, on both model sizes' kernel variants."""
+    from qwental_b200.engine import Engine, tiny_cfg, wide_cfg
+    for cfg in (tiny_cfg(max_slots=64, max_ctx=1024), wide_cfg(max_slots=64, max_ctx=1024, layers=2)):
+        e = Engine(gpu, cfg)
+        ctx = {s: [1, 255, 256, 257, 511, 512, 700, 33][s % 8] + s for s in range(64)}
+
+        def seed():
+            for s, n in ctx.items():
+                e.seed_slot(s, n, 5000 + s)
+        seed()
+        sids = list(range(63, -1, -1))
+        toks = [(s * 37 + 11) % cfg.vocab for s in sids]
+        lb, _ = e.step(sids, toks)
+        assert np.isfinite(lb).all()
+        for i in (0, 7, 31, 40, 63):
+            seed()
+            la, _ = e.step([sids[i]], [toks[i]])
+            assert np.array_equal(la[0].view(np.uint32), lb[i].view(np.uint32)), (cfg.hidden, sids[i])
+        e.close()
