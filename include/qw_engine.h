@@ -59,6 +59,21 @@ const float *qw_engine_par_step(qw_engine *e, const int *sids, const int32_t *to
 /* The same step with the arg-max fused on the device (ties -> lowest id, as src/engine.c:6144-6148):
  * returns B token ids in host-visible memory; logits are not copied to the host. */
 const int32_t *qw_engine_par_step_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms);
+/* Sampling.  qw_sample_params = the sampling fields of the reference's qw_gen (src/engine.h:40-42): temperature <= 0 is
+ * greedy; top_k <= 0 or > 256 means 256; top_p >= 1 (or <= 0) means no nucleus cut.  qw_engine_sample is the reference's
+ * function of that name (src/engine.h:125, src/engine.c:9410-9418; the vocabulary size is a parameter here): candidates =
+ * the top_k logits (ties -> lower id first), softmax(logit / T) over them, top-p cut, renormalise, one splitmix64 draw
+ * from *rng.  qw_engine_par_step_sample runs the decode step, selects the 256 best (id, logit) pairs of every row on the
+ * device and finishes on the host from those -- the same tokens as qw_engine_sample on the full logits, without copying or
+ * scanning the [B][vocab] logits on the host.  g and rng have one entry per row; out_ids [B].  Returns B or -1. */
+typedef struct {
+    float temperature;
+    int top_k;
+    float top_p;
+} qw_sample_params;
+int32_t qw_engine_sample(const float *logits, int vocab, const qw_sample_params *g, unsigned long long *rng);
+int qw_engine_par_step_sample(qw_engine *e, const int *sids, const int32_t *toks, int B, const qw_sample_params *g, unsigned long long *rng,
+                              int32_t *out_ids, double *gpu_ms);
 /* nsteps greedy steps back to back with no host round trip between them (each step's ids feed the next);
  * out_ids [nsteps][B].  Returns nsteps or -1. */
 int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, int nsteps, int32_t *out_ids, double *gpu_ms);

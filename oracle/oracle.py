@@ -243,3 +243,59 @@ def gdn_step_ref(S, q16, k16, v16, la, beta, z16, nw, hk_of, eps=1e-6):
     r = 1.0 / np.sqrt((o * o).mean(-1, keepdims=True) + eps)
     y = o * r * np.asarray(nw, np.float64) * sigmoid(np.asarray(z16, np.float16).astype(np.float64))
     return S, o, y
+
+
+# ---- sampling: make_dist + dist_draw + splitmix64 of the reference host (src/engine.c:6085-6143, 9410-9418), with its
+# float / double mix kept (p is float, the running sums are double; expf is the C library's)
+_libm = C.CDLL("libm.so.6")
+_libm.expf.restype = C.c_float
+_libm.expf.argtypes = [C.c_float]
+_M64 = (1 << 64) - 1
+
+
+def splitmix64(state: int):
+    state = (state + 0x9E3779B97F4A7C15) & _M64
+    z = state
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+    return state, z ^ (z >> 31)
+
+
+def sample_ref(logits: np.ndarray, temperature: float, top_k: int, top_p: float, rng_state: int):
+    """Returns (token, new rng state) as qw_engine_sample would (src/engine.c:9410-9418)."""
+    lg = np.asarray(logits, np.float32)
+    if temperature <= 0:
+        return int(np.argmax(lg)), rng_state  # first maximum, as argmax_cpu (src/engine.c:6144-6148)
+    k = top_k if 0 < top_k < 256 else 256
+    order = np.lexsort((np.arange(lg.size), -lg.astype(np.float64)))[:k]  # value descending, ties by id ascending
+    n = len(order)
+    f32 = np.float32
+    T, mx = f32(temperature), lg[order[0]]
+    p = [f32(_libm.expf(f32(f32(lg[i] - mx) / T))) for i in order]
+    total = 0.0
+    for v in p:
+        total += float(v)
+    c, keep = 0.0, n
+    for i in range(n):
+        p[i] = f32(float(p[i]) / total)
+        c += float(p[i])
+        if 0 < top_p < 1 and c >= float(f32(top_p)):
+            keep = i + 1
+            break
+    s2 = 0.0
+    for i in range(keep):
+        s2 += float(p[i])
+    for i in range(keep):
+        p[i] = f32(float(p[i]) / s2)
+    tot = 0.0
+    for i in range(keep):
+        tot += float(p[i])
+    if tot <= 0:
+        return int(order[0]), rng_state
+    rng_state, z = splitmix64(rng_state)
+    u = float(z >> 11) * (1.0 / 9007199254740992.0) * tot
+    for i in range(keep):
+        u -= float(p[i])
+        if u <= 0:
+            return int(order[i]), rng_state
+    return int(order[keep - 1]), rng_state

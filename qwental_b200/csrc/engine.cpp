@@ -86,7 +86,7 @@ struct qw_engine {
     std::vector<int> free_pages;
     unsigned long long clock = 0;
     // scratch
-    qw_buf ctl_h{}, ctl_d{}, h{}, x{}, proj{}, cv{}, la{}, be{}, gy{}, qb{}, part{}, ya{}, ob{}, mo{}, logits{}, ids{}, ids_h{}, logits_h{};
+    qw_buf ctl_h{}, ctl_d{}, h{}, x{}, proj{}, cv{}, la{}, be{}, gy{}, qb{}, part{}, ya{}, ob{}, mo{}, logits{}, ids{}, ids_h{}, logits_h{}, cand_h{};
     qw_buf mlog{}, msel{}, Hhi{}, Hlo{}, Pg{}, rcnt{};
     size_t sel_bytes = 0;
     // kernels
@@ -97,7 +97,7 @@ struct qw_engine {
     bool ep_fused = false;
     qw_buf epx{};            // [2][Pg] (double-buffered by layer parity) + flag array, exported to the other ranks
     qw_buf ep_peer[8]{};     // the other ranks' epx (ep_peer[own rank] aliases epx)
-    qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr;
+    qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr, *k_topk = nullptr;
     // slot sharding on top of the fused exchange: attention / GDN (their projections included) run only for the rows whose
     // slot this rank owns (slot % ep_size == ep_rank); the out-projection stores its rows into every rank's `ob` and publishes
     bool slot_shard = false;
@@ -209,7 +209,7 @@ extern "C" void qw_engine_close(qw_engine *e) {
     if (!e) return;
     qw_buf *all[] = {&e->emb, &e->lm_head, &e->dense, &e->small, &e->router, &e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd, &e->kvpool,
                      &e->ptab, &e->sstate, &e->cstate, &e->ctl_h, &e->ctl_d, &e->h, &e->x, &e->proj, &e->cv, &e->la, &e->be, &e->gy, &e->qb,
-                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt};
+                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->cand_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt};
     // mappings of the other ranks' exchange buffers go first (their owners free the memory), then this rank's own
     for (int r = 0; r < 8; r++)
         if (r != e->c.ep_rank && e->ep_peer[r].handle) qw_buf_free(&e->ep_peer[r]);
@@ -294,6 +294,7 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          compile(e, "moe_gu", "moe_gu", md, &e->k_gu) && compile(e, "moe_dn", "moe_dn", md, &e->k_dn) && compile(e, "moe_cmb", "moe_cmb", md, &e->k_cmb) &&
          compile(e, "moe_route", "moe_route", md, &e->k_route) &&
          compile(e, "add_rmsnorm", "cmb_add_rmsnorm", {{"CMB", 1}, {"TOPK", e->TOPK}}, &e->k_norm_cmb);
+    ok = ok && compile(e, "k_topk", "k_topk", {}, &e->k_topk);
     e->k_ar = nullptr;
     if (ok && c.ep_size > 1) ok = compile(e, "ep_allreduce", "ep_allreduce", {}, &e->k_ar);
     if (!ok) {
@@ -320,7 +321,7 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          new_buf(e, &e->la, B * c.hv * 4) && new_buf(e, &e->be, B * c.hv * 4) && new_buf(e, &e->gy, B * e->KG * 2) &&
          new_buf(e, &e->qb, B * c.qh * c.hd * 2) && new_buf(e, &e->part, B * (size_t)e->max_pages * c.qh * (c.hd + 2) * 4) &&
          new_buf(e, &e->ya, B * e->KA * 2) && new_buf(e, &e->ob, B * e->D * 2) && new_buf(e, &e->mo, B * e->D * 2) &&
-         new_buf(e, &e->logits, B * (size_t)e->V * 4) && new_buf(e, &e->ids, B * 4) && new_buf(e, &e->ids_h, B * 4, QW_BUF_HOSTIO) &&
+         new_buf(e, &e->logits, B * (size_t)e->V * 4) && new_buf(e, &e->ids, B * 4) && new_buf(e, &e->ids_h, B * 4, QW_BUF_HOSTIO) && new_buf(e, &e->cand_h, B * 256 * 8, QW_BUF_HOSTIO) &&
          new_buf(e, &e->logits_h, B * (size_t)e->V * 4, QW_BUF_HOSTIO) && new_buf(e, &e->mlog, B * (e->E + 1) * 4) &&
          new_buf(e, &e->msel, (size_t)e->L * e->sel_bytes) && new_buf(e, &e->Hhi, B * (e->TOPK + 1) * e->I * 2) &&
          new_buf(e, &e->Hlo, B * (e->TOPK + 1) * e->I * 2) && new_buf(e, &e->Pg, B * (e->TOPK + 1) * e->D * 4) && new_buf(e, &e->rcnt, 256);
@@ -638,7 +639,15 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
     }
     enc_norm(e, b, pending, e->final_norm, nb, e->L - 1);
     enc_qmv(b, e->k_lm, &e->lm_head, 0, (uint32_t)e->V, D, &e->x, &e->logits, nb, (uint32_t)e->V);
-    if (sample) {
+    if (sample == 3) {  // the 256 best (id, logit) pairs of every row, written straight into host-visible memory
+        const uint32_t a[3] = {nb, (uint32_t)e->V, 256};
+        qw_batch_kernel(b, e->k_topk);
+        qw_batch_buf(b, 0, &e->logits, 0);
+        qw_batch_buf(b, 1, &e->cand_h, 0);
+        qw_batch_buf(b, 2, &e->cand_h, (size_t)QW_PAR_MAX * 256 * 4);
+        qw_batch_bytes(b, 3, a, sizeof a);
+        qw_batch_dispatch(b, nb, 1, 1, 1024, 1, 1);
+    } else if (sample) {
         const uint32_t a[2] = {nb, (uint32_t)e->V};
         qw_batch_kernel(b, e->k_argmax);
         qw_batch_buf(b, 0, &e->logits, 0);
@@ -767,6 +776,99 @@ extern "C" int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const 
     if (gpu_ms) *gpu_ms = total * 1e3;
     end_step(e, sids, B, nsteps, (qw_now() - t0) * 1e3);
     return nsteps;
+}
+
+// ---- sampling on the host from an ordered candidate list: the reference's make_dist + dist_draw (src/engine.c:6094-6143)
+// restated for candidates that are already the top ones in its order (value descending, ties by id ascending)
+namespace {
+uint64_t rng_next(uint64_t *x) {  // splitmix64, src/engine.c:6085-6090
+    uint64_t z = (*x += 0x9e3779b97f4a7c15ull);
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+int32_t sample_candidates(const int32_t *id, const float *lg, int avail, const qw_sample_params *g, unsigned long long *rng) {
+    if (avail < 1) return -1;
+    if (g->temperature <= 0) return id[0];
+    const int k = g->top_k > 0 && g->top_k < 256 ? g->top_k : 256;
+    const int n = std::min(k, avail);
+    float p[256];
+    const float T = g->temperature, mx = lg[0];
+    double sum = 0;
+    for (int i = 0; i < n; i++) {
+        p[i] = expf((lg[i] - mx) / T);
+        sum += p[i];
+    }
+    double c = 0;
+    int keep = n;
+    for (int i = 0; i < n; i++) {
+        p[i] = (float)(p[i] / sum);
+        c += p[i];
+        if (g->top_p > 0 && g->top_p < 1 && c >= g->top_p) {
+            keep = i + 1;
+            break;
+        }
+    }
+    double s2 = 0;
+    for (int i = 0; i < keep; i++) s2 += p[i];
+    for (int i = 0; i < keep; i++) p[i] = (float)(p[i] / s2);
+    double tot = 0;
+    for (int i = 0; i < keep; i++) tot += p[i];
+    if (tot <= 0) return id[0];
+    uint64_t r = *rng;
+    double u = (double)(rng_next(&r) >> 11) * (1.0 / 9007199254740992.0) * tot;
+    *rng = r;
+    for (int i = 0; i < keep; i++) {
+        u -= p[i];
+        if (u <= 0) return id[i];
+    }
+    return id[keep - 1];
+}
+}  // namespace
+
+extern "C" int32_t qw_engine_sample(const float *lg, int vocab, const qw_sample_params *g, unsigned long long *rng) {
+    if (!lg || vocab < 1 || !g || !rng) return -1;
+    // the top candidates of the whole row in the reference's order: insertion into a list kept sorted by value, an equal
+    // value goes behind the ones already there (they have lower ids)
+    const int k = g->temperature <= 0 ? 1 : (g->top_k > 0 && g->top_k < 256 ? g->top_k : 256);
+    int32_t id[256];
+    float val[256];
+    int n = 0;
+    for (int v = 0; v < vocab; v++) {
+        const float x = lg[v];
+        if (n == k && !(x > val[n - 1])) continue;
+        int i = n < k ? n++ : n - 1;
+        while (i > 0 && val[i - 1] < x) {
+            id[i] = id[i - 1];
+            val[i] = val[i - 1];
+            i--;
+        }
+        id[i] = v;
+        val[i] = x;
+    }
+    return sample_candidates(id, val, n, g, rng);
+}
+
+extern "C" int qw_engine_par_step_sample(qw_engine *e, const int *sids, const int32_t *toks, int B, const qw_sample_params *g, unsigned long long *rng,
+                                         int32_t *out_ids, double *gpu_ms) {
+    if (!e || !g || !rng || !out_ids) return -1;
+    const double t0 = qw_now();
+    const uint32_t mc = begin_step(e, sids, toks, B, 1);
+    if (!mc) return -1;
+    qw_batch *b = qw_batch_begin(e->g, false);
+    encode_step(e, b, (uint32_t)B, mc, true, 3);
+    const double secs = qw_batch_end(b);
+    if (secs < 0) return e->fail("par_step_sample: device batch failed"), -1;
+    if (gpu_ms) *gpu_ms = secs * 1e3;
+    const int32_t *cid = (const int32_t *)e->cand_h.ptr;
+    const float *cval = (const float *)((const char *)e->cand_h.ptr + (size_t)QW_PAR_MAX * 256 * 4);
+    const int avail = std::min(256, e->V);
+    for (int j = 0; j < B; j++) {  // device row j is the caller's row perm[j]
+        const int i = e->perm[j];
+        out_ids[i] = sample_candidates(cid + (size_t)j * 256, cval + (size_t)j * 256, avail, &g[i], &rng[i]);
+    }
+    end_step(e, sids, B, 1, (qw_now() - t0) * 1e3);
+    return B;
 }
 
 extern "C" double qw_engine_par_cost(qw_engine *e, int B) { return e && B >= 1 && B <= QW_PAR_MAX ? e->cost[B] : 0; }

@@ -37,6 +37,8 @@ def _bind(L):
         "qw_engine_last_step_bytes": (None, [vp, C.POINTER(StepBytes)]),
         "qw_engine_tap": (C.c_size_t, [vp, C.c_char_p, C.c_int, vp, C.c_size_t]),
         "qw_ep_unique_id": (C.c_int, [vp]), "qw_engine_ep_init": (C.c_int, [vp, vp]),
+        "qw_engine_sample": (C.c_int32, [vp, C.c_int, vp, vp]),
+        "qw_engine_par_step_sample": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, vp, vp]),
         "qw_engine_ep_export": (C.c_int, [vp, vp]), "qw_engine_ep_connect": (C.c_int, [vp, vp, C.c_int]),
     }
     for name, (res, args) in sig.items():
@@ -60,6 +62,19 @@ def tiny_cfg(**over) -> ModelCfg:
                 max_slots=8, max_ctx=2048, kv_pages=0, seed=1)
     base.update(over)
     return default_cfg(**base)
+
+
+SAMPLE_DT = np.dtype([("temperature", np.float32), ("top_k", np.int32), ("top_p", np.float32)])
+
+
+def sample(logits: np.ndarray, temperature: float, top_k: int, top_p: float, rng: np.ndarray) -> int:
+    """qw_engine_sample through the C ABI (host only: works without a GPU); rng = uint64 array of one element."""
+    L = _lib.load()
+    _bind(L)
+    lg = np.ascontiguousarray(logits, np.float32)
+    g = np.zeros(1, SAMPLE_DT)
+    g[0] = (temperature, top_k, top_p)
+    return int(L.qw_engine_sample(lg.ctypes.data, lg.size, g.ctypes.data, rng.ctypes.data))
 
 
 def wide_cfg(**over) -> ModelCfg:
@@ -150,6 +165,20 @@ class Engine:
         if got != n:
             raise GpuError("tap(%s, %d) failed" % (name, index))
         return out
+
+    def step_sample(self, sids, toks, params, rng):
+        """One decode step with sampling: params = [(temperature, top_k, top_p)] per row, rng = uint64 state per row
+        (advanced in place for rows that draw).  Returns (ids int32 [B], gpu_ms)."""
+        B = len(sids)
+        s, t = np.ascontiguousarray(sids, np.int32), np.ascontiguousarray(toks, np.int32)
+        g = np.zeros(B, SAMPLE_DT)
+        for i, (T, k, p) in enumerate(params):
+            g[i] = (T, k, p)
+        out = np.empty(B, np.int32)
+        ms = C.c_double()
+        if self.L.qw_engine_par_step_sample(self.e, s.ctypes.data, t.ctypes.data, B, g.ctypes.data, rng.ctypes.data, out.ctypes.data, C.addressof(ms)) != B:
+            raise GpuError("step_sample: " + self.error())
+        return out, ms.value
 
     def ep_init(self, id128: bytes):
         buf = C.create_string_buffer(id128, 128)
