@@ -110,6 +110,10 @@ int qw_engine_ep_init(qw_engine *e, const void *id128);
  * means, then every rank calls qw_engine_ep_connect with the ep_size handles.  All ranks must then step in lockstep
  * with identical inputs.  0 on success, -1 with qw_engine_error set. */
 int qw_engine_ep_export(qw_engine *e, void *handle64);
+/* The row order the engine uses under slot sharding (host logic only, exposed for schedulers and tests): rows grouped by
+ * owning rank (slot mod nranks), stable within a rank; perm[j] = caller's index of device row j; [*lo, *hi) = this rank's
+ * rows in that order.  0 or -1. */
+int qw_ep_row_order(const int *sids, int B, int nranks, int rank, int *perm, int *lo, int *hi);
 int qw_engine_ep_connect(qw_engine *e, const void *handles, int n);
 
 #ifdef __cplusplus

@@ -418,6 +418,24 @@ extern "C" int qw_engine_par_seed(qw_engine *e, int sid, int ctx_len, unsigned l
     return 0;
 }
 
+// Row order of a step under slot sharding (slot s belongs to rank s mod nranks): rows grouped by owning rank, stable within
+// a rank, so that every rank's rows are one contiguous range [lo, hi) of the same order on every rank.  perm[j] = the
+// caller's index of device row j.  Pure host logic (no device needed).
+extern "C" int qw_ep_row_order(const int *sids, int B, int nranks, int rank, int *perm, int *lo, int *hi) {
+    if (!sids || !perm || B < 0 || nranks < 1 || rank < 0 || rank >= nranks) return -1;
+    for (int i = 0; i < B; i++) perm[i] = i;
+    std::stable_sort(perm, perm + B, [&](int a, int b) { return sids[a] % nranks < sids[b] % nranks; });
+    int l = 0, h = 0;
+    for (int j = 0; j < B; j++) {
+        const int own = sids[perm[j]] % nranks;
+        if (own < rank) l++;
+        if (own <= rank) h++;
+    }
+    if (lo) *lo = l;
+    if (hi) *hi = h;
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------------ the step
 namespace {
 
@@ -684,19 +702,10 @@ uint32_t begin_step(qw_engine *e, const int *sids, const int32_t *toks, int B, i
     }
     // device row order: the caller's, or (slot sharding) grouped by the rank that owns the slot, stable within a rank, so
     // that every rank's rows are one contiguous range -- the same order on every rank
-    for (int i = 0; i < B; i++) e->perm[i] = i;
-    e->row_lo = 0;
-    e->row_hi = (uint32_t)B;
-    if (e->slot_shard) {
-        const int n = e->c.ep_size;
-        std::stable_sort(e->perm, e->perm + B, [&](int a, int b2) { return sids[a] % n < sids[b2] % n; });
-        e->row_lo = e->row_hi = 0;
-        for (int j = 0; j < B; j++) {
-            const int own = sids[e->perm[j]] % n;
-            if (own < e->c.ep_rank) e->row_lo++;
-            if (own <= e->c.ep_rank) e->row_hi++;
-        }
-    }
+    int lo = 0, hi = B;
+    qw_ep_row_order(sids, B, e->slot_shard ? e->c.ep_size : 1, e->slot_shard ? e->c.ep_rank : 0, e->perm, &lo, &hi);
+    e->row_lo = (uint32_t)lo;
+    e->row_hi = (uint32_t)hi;
     int32_t *ctl = (int32_t *)e->ctl_h.ptr;
     for (int j = 0; j < B; j++) {
         const int i = e->perm[j];

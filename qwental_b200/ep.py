@@ -23,3 +23,19 @@ def owner_of(E: int, size: int, expert_ids: np.ndarray) -> np.ndarray:
 def scaling_bound(step_bytes_total: float, moe_bytes: float, n: int) -> float:
     """Upper bound on the speed-up from sharding only the expert weights over n GPUs (HBM bytes per GPU)."""
     return step_bytes_total / (step_bytes_total - moe_bytes + moe_bytes / n)
+
+
+def row_order(sids, nranks: int, rank: int):
+    """Device row order under slot sharding (slot s belongs to rank s mod nranks), through the C ABI (host logic, no device):
+    returns (perm, lo, hi) -- perm[j] = caller's index of device row j, [lo, hi) = this rank's rows."""
+    import ctypes as C
+    from . import lib
+    L = lib.load()
+    s = np.ascontiguousarray(sids, np.int32)
+    perm = np.empty(len(s), np.int32)
+    lo, hi = C.c_int(), C.c_int()
+    L.qw_ep_row_order.restype = C.c_int
+    L.qw_ep_row_order.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    if L.qw_ep_row_order(s.ctypes.data, len(s), nranks, rank, perm.ctypes.data, C.addressof(lo), C.addressof(hi)) != 0:
+        raise ValueError("bad rank / nranks")
+    return perm, lo.value, hi.value

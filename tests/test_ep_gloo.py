@@ -61,6 +61,60 @@ def worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def shard_worker(rank, world, port, q):
+    """Slot sharding: every rank produces the rows of the slots it owns (here a deterministic function of slot and token),
+    in the shared device order; summing zero-padded buffers stands in for the peer stores of the out-projection."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sids = np.array([5, 0, 2, 7, 4, 9, 1], np.int32)
+        toks = np.arange(len(sids), dtype=np.int64) * 3 + 1
+        perm, lo, hi = ep.row_order(sids, world, rank)
+        full = np.stack([np.full(8, float(sids[i] * 100 + toks[i]), np.float32) for i in perm])  # device order, all rows
+        mine = np.zeros_like(full)
+        assert all(sids[perm[j]] % world == rank for j in range(lo, hi))
+        mine[lo:hi] = full[lo:hi]
+        t = torch.from_numpy(mine.copy())
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        allperm = [torch.zeros(len(sids), dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(allperm, torch.from_numpy(perm.copy()))
+        same_order = all(np.array_equal(p.numpy(), perm) for p in allperm)
+        back = np.empty_like(full)
+        back[perm] = t.numpy()  # the caller's order
+        want = np.stack([np.full(8, float(sids[i] * 100 + toks[i]), np.float32) for i in range(len(sids))])
+        q.put((rank, bool(np.array_equal(back, want)), same_order, lo, hi))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_slot_sharded_rows_gather_to_the_full_batch_world2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=shard_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    assert all(r[1] and r[2] for r in res)
+    assert res[0][3] == 0 and res[0][4] == res[1][3] and res[1][4] == 7 and res[0][4] == 3  # slots 0, 2, 4 are rank 0's
+
+
+def test_row_order_edge_cases():
+    perm, lo, hi = ep.row_order([3, 1, 5], 2, 0)  # all slots odd: rank 0 owns no row
+    assert (lo, hi) == (0, 0) and perm.tolist() == [0, 1, 2]
+    perm, lo, hi = ep.row_order([3, 1, 5], 2, 1)
+    assert (lo, hi) == (0, 3)
+    perm, lo, hi = ep.row_order([6, 1, 4, 3], 1, 0)  # one rank: the caller's order
+    assert perm.tolist() == [0, 1, 2, 3] and (lo, hi) == (0, 4)
+    perm, lo, hi = ep.row_order([6, 1, 4, 3, 8], 4, 0)  # stable within a rank: slots 4 and 8 keep their order
+    assert perm.tolist() == [2, 4, 1, 0, 3] and (lo, hi) == (0, 2)
+    with pytest.raises(ValueError):
+        ep.row_order([1], 2, 2)
+
+
 def free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
