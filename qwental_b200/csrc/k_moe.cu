@@ -80,6 +80,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
     __shared__ uint32_t mlo[MOE_MAXE], mhi[MOE_MAXE], pos[MOE_MAXE], grp[MOE_MAXE];  // token bit masks per expert
     __shared__ uint16_t sid[MOE_MAXB * MOE_MAXK];
     __shared__ uint32_t wsum[2][32];
+    __shared__ uint64_t cand_s[NTH / 32][32 + MOE_MAXK];  // per warp: candidates of the fast top-k path, then the winners' keys
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t PER = E / 32;
     constexpr uint32_t NW = NTH / 32;
@@ -97,12 +98,56 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
         };
         uint32_t pkey = 0;
         if (PER == 16) {
-            // The lane sorts its 16 (key, ~id) pairs once with a 63-comparator odd-even merge network (descending key,
-            // ascending id); each of the topk rounds then only looks at the lanes' heads and the winning lane pops its
-            // head -- instead of rescanning 16 values per lane per round.
+            uint32_t kv[16];
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j++) kv[j] = key_of(j);
+            // Fast path.  T = the topk-th largest of the 32 lane maxima: at least topk values are >= T, so the winners are
+            // among the values >= T -- usually little more than topk of them.  If they fit one per lane, each lane takes
+            // one candidate and finds its rank by counting the candidates that beat it (larger key, or equal key and
+            // lower id); ranks are distinct because ids are.  Otherwise (many equal logits) the general path below runs.
+            uint32_t lm = kv[0];
+#pragma unroll
+            for (uint32_t j = 1; j < 16; j++) lm = max(lm, kv[j]);
+            uint32_t cur = lm, T = 0;
+            for (uint32_t k = 0; k < topk; k++) {
+                T = __reduce_max_sync(0xffffffffu, cur);
+                const uint32_t who = __ffs(__ballot_sync(0xffffffffu, cur == T)) - 1;
+                if (lane == who) cur = 0;  // (a real key is never 0: that would be the bit pattern of -NaN)
+            }
+            uint32_t cnt = 0;
+#pragma unroll
+            for (uint32_t j = 0; j < 16; j++) cnt += kv[j] >= T;
+            uint32_t pre = cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t n = __shfl_up_sync(0xffffffffu, pre, o);
+                if (lane >= (uint32_t)o) pre += n;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, pre, 31);
+            if (total <= 32) {
+                uint64_t *cs = cand_s[warp];
+                uint32_t at = pre - cnt;
+#pragma unroll
+                for (uint32_t j = 0; j < 16; j++)
+                    if (kv[j] >= T) cs[at++] = ((uint64_t)kv[j] << 32) | (0xffffffffu - (lane + 32 * j));
+                __syncwarp();
+                const uint64_t mine = lane < total ? cs[lane] : 0;
+                uint32_t rank = 0;
+                for (uint32_t j = 0; j < total; j++) rank += __shfl_sync(0xffffffffu, mine, j) > mine;
+                if (lane < total && rank < topk) {
+                    const uint32_t id = 0xffffffffu - (uint32_t)mine;
+                    ms->ids[t][rank] = (int32_t)id;
+                    sid[t * MOE_MAXK + rank] = (uint16_t)id;
+                    cs[32 + rank] = mine >> 32;  // key of rank r, for the softmax below
+                }
+                __syncwarp();
+                if (lane < topk) pkey = (uint32_t)cs[32 + lane];
+                __syncwarp();
+            } else {
+            // General path: the lane sorts its 16 (key, ~id) pairs once
             uint64_t s[16];
 #pragma unroll
-            for (uint32_t j = 0; j < 16; j++) s[j] = ((uint64_t)key_of(j) << 32) | (0xffffffffu - (lane + 32 * j));
+            for (uint32_t j = 0; j < 16; j++) s[j] = ((uint64_t)kv[j] << 32) | (0xffffffffu - (lane + 32 * j));
 #define CE(A, B)                          \
     {                                     \
         const uint64_t x_ = s[A], y_ = s[B]; \
@@ -128,6 +173,7 @@ __device__ __forceinline__ void moe_select_body(const float *logits, moe_sel *ms
                     s[15] = 0;
                 }
             }
+            }  // general path
         } else {
             uint32_t v[8];  // small expert counts (E <= 256): rescan the lane's few values every round
 #pragma unroll
