@@ -5,9 +5,10 @@
 // logits, src/engine.c:9410-9418); the host half that turns candidates into a token is qw_sample_candidates in engine.cpp.
 //
 // One block of 1024 threads per row.  Logits become order-preserving 32-bit keys; the k-th largest key is found by a
-// three-pass radix select (11 + 11 + 10 bits, shared-memory histograms), then every thread walks a contiguous range of the
-// row, so that keys above the threshold and the lowest-id keys equal to it are compacted in id order by block-wide prefix
-// sums; a bitonic sort of the <= 256 survivors gives the final order.
+// three-pass radix select (11 + 11 + 10 bits, shared-memory histograms with warp-aggregated updates).  Usually exactly the
+// wanted number of keys is >= the threshold and they are appended in one coalesced pass; when more keys equal the threshold
+// than are wanted, every thread walks a contiguous range of the row instead, so that the lowest ids are kept by block-wide
+// prefix sums.  A bitonic sort of the <= 256 survivors gives the final order.
 #include "common.cuh"
 #include "qw_kern.h"
 
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(1024) k_topk_k(const float *lg, int32_t *ids, 
     __shared__ uint32_t hist[2048];
     __shared__ uint32_t ws[2][32];
     __shared__ unsigned long long cand[TOPK_MAX];
-    __shared__ uint32_t sh_bin, sh_rem;
+    __shared__ uint32_t sh_bin, sh_rem, sh_cnt, sh_n;
     pdl_sync();
     const uint32_t tid = threadIdx.x;
     const float *row = lg + (size_t)blockIdx.x * V;
@@ -72,7 +73,11 @@ __global__ void __launch_bounds__(1024) k_topk_k(const float *lg, int32_t *ids, 
         __syncthreads();
         for (uint32_t i = tid; i < V; i += 1024) {
             const uint32_t k = key_of(__ldcg(row + i));
-            if (ps == 0 || (k >> (sh + widths[ps])) == prefix) atomicAdd(&hist[(k >> sh) & (nb - 1)], 1u);
+            const bool in = ps == 0 || (k >> (sh + widths[ps])) == prefix;
+            // logits crowd into a few bins: lanes with the same bin elect one to add their count (no serialised atomics)
+            const uint32_t bin = in ? (k >> sh) & (nb - 1) : 0xffffffffu;
+            const uint32_t peers = __match_any_sync(__activemask(), bin);
+            if (in && (threadIdx.x & 31) == (uint32_t)__ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
         }
         __syncthreads();
         // suffix sums over the bins (two bins per thread, highest bins first): bin b* = the highest bin whose suffix >= rem
@@ -80,32 +85,43 @@ __global__ void __launch_bounds__(1024) k_topk_k(const float *lg, int32_t *ids, 
         const uint32_t h1 = b1 < (uint32_t)nb ? hist[b1] : 0, h0 = b0 < (uint32_t)nb ? hist[b0] : 0;
         uint32_t e, dummy, tot, t2;
         block_scan2(h1 + h0, 0, e, dummy, tot, t2, ws);  // e = count in all bins above b1
-        if (e < rem && e + h1 >= rem) { sh_bin = b1; sh_rem = rem - e; }
-        else if (e + h1 < rem && e + h1 + h0 >= rem) { sh_bin = b0; sh_rem = rem - e - h1; }
+        if (e < rem && e + h1 >= rem) { sh_bin = b1; sh_rem = rem - e; sh_cnt = h1; }
+        else if (e + h1 < rem && e + h1 + h0 >= rem) { sh_bin = b0; sh_rem = rem - e - h1; sh_cnt = h0; }
         __syncthreads();
         prefix = (prefix << widths[ps]) | sh_bin;
         rem = sh_rem;
         __syncthreads();
     }
     const uint32_t T = prefix;  // rem = how many keys equal to T are wanted (the lowest ids)
-    // ---- compaction in id order: thread t owns ids [t*chunk, (t+1)*chunk)
-    const uint32_t chunk = (V + 1023) / 1024, i0 = tid * chunk, i1 = min(V, i0 + chunk);
-    uint32_t ngt = 0, neq = 0;
-    for (uint32_t i = i0; i < i1; i++) {
-        const uint32_t k = key_of(__ldcg(row + i));
-        ngt += k > T;
-        neq += k == T;
-    }
-    uint32_t egt, eeq, tgt, teq;
-    block_scan2(ngt, neq, egt, eeq, tgt, teq, ws);
+    const uint32_t n_eq = sh_cnt;  // keys equal to T in the whole row (the last pass's bin holds exactly those)
     for (uint32_t j = tid; j < TOPK_MAX; j += 1024) cand[j] = 0;
+    if (tid == 0) sh_n = 0;
     __syncthreads();
-    for (uint32_t i = i0; i < i1 && (ngt || neq); i++) {
-        const uint32_t k = key_of(__ldcg(row + i));
-        if (k > T) cand[egt++] = ((unsigned long long)k << 32) | (0xffffffffu - i);
-        else if (k == T) {
-            if (eeq < rem) cand[tgt + eeq] = ((unsigned long long)k << 32) | (0xffffffffu - i);
-            eeq++;
+    if (n_eq == rem) {
+        // ---- every key >= T is a winner (K of them): append in any order, the sort below orders them
+        for (uint32_t i = tid; i < V; i += 1024) {
+            const uint32_t k = key_of(__ldcg(row + i));
+            if (k >= T) cand[atomicAdd(&sh_n, 1u)] = ((unsigned long long)k << 32) | (0xffffffffu - i);
+        }
+    } else {
+        // ---- more keys equal T than are wanted: the lowest ids win.  Compaction in id order: thread t owns ids
+        // [t*chunk, (t+1)*chunk) and block-wide prefix sums give every thread its output offsets
+        const uint32_t chunk = (V + 1023) / 1024, i0 = tid * chunk, i1 = min(V, i0 + chunk);
+        uint32_t ngt = 0, neq = 0;
+        for (uint32_t i = i0; i < i1; i++) {
+            const uint32_t k = key_of(__ldcg(row + i));
+            ngt += k > T;
+            neq += k == T;
+        }
+        uint32_t egt, eeq, tgt, teq;
+        block_scan2(ngt, neq, egt, eeq, tgt, teq, ws);
+        for (uint32_t i = i0; i < i1 && (ngt || neq); i++) {
+            const uint32_t k = key_of(__ldcg(row + i));
+            if (k > T) cand[egt++] = ((unsigned long long)k << 32) | (0xffffffffu - i);
+            else if (k == T) {
+                if (eeq < rem) cand[tgt + eeq] = ((unsigned long long)k << 32) | (0xffffffffu - i);
+                eeq++;
+            }
         }
     }
     __syncthreads();

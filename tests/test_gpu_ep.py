@@ -28,7 +28,12 @@ def _steps(eng):
     l2, _ = eng.step(SIDS, list(l1.argmax(1).astype(np.int32)))
     l3, _ = eng.step([2, 0], [7, 8])  # even slots only: with two ranks and slot sharding rank 1 owns no row of this step
     ids, _ = eng.decode_greedy(SIDS, TOKS, 3)
-    return l1, l2, l3, ids
+    eng.gpu.L.qw_gpu_set_graphs(eng.gpu.g, True)  # the same chain replayed as CUDA graphs (flag waits inside the graph)
+    try:
+        ids_g, _ = eng.decode_greedy(SIDS, [1, 2, 3], 4)
+    finally:
+        eng.gpu.L.qw_gpu_set_graphs(eng.gpu.g, False)
+    return l1, l2, l3, ids, ids_g
 
 
 def _worker(rank, world, uid, q, up, down):
@@ -82,4 +87,4 @@ def test_expert_parallel_step_bit_identical_to_single_gpu(fused):
     for r in res:
         for got, want in zip(r[1:4], ref[:3]):
             assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r[0]
-        assert np.array_equal(r[4], ref[3]), r[0]
+        assert np.array_equal(r[4], ref[3]) and np.array_equal(r[5], ref[4]), r[0]

@@ -144,3 +144,31 @@ def test_fused_router_select_equals_two_launches(gpu, B):
         assert np.array_equal(ids, ref_ids)
         assert np.array_equal(got[n:n + 4 * U], sel[n:n + 4 * U]) and got[:4].view(np.uint32)[0] == sel[:4].view(np.uint32)[0]
         assert np.array_equal(out2.view(np.uint16), out.view(np.uint16))
+
+
+def test_selection_with_equal_logits_takes_lowest_ids(gpu):
+    """Ties in the router: equal logits resolve to the lower expert id (as the reference's stable selection,
+    kernels/moe_gg.metal:118-189).  Token 0 is all zeros (every logit equal: 512 candidates, the general path of the
+    selection); in the other tokens some router rows are duplicated, so winners and the cut-off come in equal pairs
+    (the fast path with a few candidates more than top-k)."""
+    D, I, topk, E = 2048, 512, 10, 512
+    layer, h, b = make_layer(gpu, E, D, I, topk, seed=33)
+    Wr = h["Wr"].copy()
+    rng = np.random.default_rng(8)
+    for _ in range(60):  # duplicated rows -> exactly equal logits for every token
+        a, c = rng.integers(0, E, 2)
+        Wr[c] = Wr[a]
+    b["Wr"].upload(Wr)
+    x = synth.acts_fp16(rng, 6, D)
+    x[0] = 0
+    for fused in (False, True):
+        layer.sel.zero()
+        run_layer(gpu, layer, x, fused_route=fused)
+        lg = layer.read_logits(6)
+        ref_lg = orc.router_canon(np.concatenate([Wr, h["wsg"][None]]), x)
+        assert np.array_equal(lg.view(np.uint32), ref_lg.view(np.uint32))
+        U, ids, w, ue, off, ent = layer.read_sel(6)
+        ref_ids, ref_w = orc.topk(ref_lg[:, :E], topk)
+        assert np.array_equal(ids[:6, :topk], ref_ids), fused
+        assert list(ids[0, :topk]) == list(range(topk))
+        assert np.abs(w[:6, :topk] - ref_w).max() < 1e-6
