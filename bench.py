@@ -169,8 +169,9 @@ def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
 def workload_config(layers, slots, ctx_sum, world, graphs, ep="nccl"):
     return {"workload": "full %d-layer Qwen3-Next-80B-A3B-shaped decode step, %d ragged slots (contexts log-uniform 1K-48K, sum %d tokens), "
                         "IQ3_S weights, Q8_0 lm_head, greedy" % (layers, slots, ctx_sum),
-            "parallelism": ("ep%d (experts sharded, attention and Gated DeltaNet sharded by slot, rest replicated; exchange: peer stores "
-                            "fused into the down and out projections)" % world if ep == "fused" else
+            "parallelism": ("ep%d (experts sharded, attention and Gated DeltaNet sharded by slot with conversations placed on the least "
+                            "loaded rank, rest replicated; exchange: peer stores fused into the down and out projections)" % world
+                            if ep == "fused" else
                             "ep%d (experts sharded, rest replicated; exchange: NCCL all-reduce)" % world) if world > 1 else "1 GPU",
             "l2": "inputs larger than L2 (weights 35 GB, KV and state several GB per step)", "cuda_graphs": bool(graphs)}
 
@@ -235,6 +236,15 @@ def main():
 
     B, K, W = args.slots, args.steps, max(3, args.warmup)
     ctx = synth.ragged_contexts(np.random.default_rng(0), B)
+    if world > 1:
+        # Placement, as a scheduler would do it when slot s is served by rank s mod N: the same conversations, each put into
+        # a free slot of the rank that holds the fewest context tokens so far (longest first).  With one GPU nothing changes.
+        placed, load, free = np.zeros(B, ctx.dtype), np.zeros(world), [list(range(r, B, world)) for r in range(world)]
+        for c in sorted(ctx.tolist(), reverse=True):
+            r = min((q for q in range(world) if free[q]), key=lambda q: load[q])
+            placed[free[r].pop(0)] = c
+            load[r] += c
+        ctx = placed
     nsteps_total = 3 * (K + W) + 8
     pages = int(sum((int(n) + nsteps_total + 256) // 256 + 1 for n in ctx))
     cfg = default_cfg(max_slots=B, max_ctx=int(ctx.max()) + nsteps_total + 512, kv_pages=pages, ep_rank=rank, ep_size=world, seed=0, layers=args.layers)
