@@ -441,14 +441,16 @@ QW_FAMILY(qsa_attn, launch_qsa_attn_mma, 128)
 
 // ------------------------------------------------------------------------------------------------ merge + output gate
 // binds: 0 = part, 1 = qkv fp16 (gate = qkv[t][qh*2*HD + HD + d]), 2 = y fp16 [nb][QH*HD], 3 = pos, 4 = qsa_args.
-// grid (QH, nb) x 256.  The chunk weights exp(m_c - M) are computed once per chunk (thread c), then thread d sums
-// dim d over the slot's chunks in chunk order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.
+// grid (QH, nb) x 1024.  The chunk weights exp(m_c - M) are computed once per chunk (thread c); then 8 groups of 128
+// threads (two dims per thread, 8-byte loads: a partial's 258 floats keep rows 8-byte aligned, not 16) each sum their chunks
+// in chunk order and the 8 partial sums are added in group order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.
 #define QSA_MAXCH 1024
 __global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
     constexpr uint32_t HD = 256;
-    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[32], accs[4][HD], ls[4];
+    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[32], ls[8];
+    __shared__ float2 accs[8][HD / 2];
     pdl_sync();
-    const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, d = tid & 255, grp = tid >> 8, lane = tid & 31, warp = tid >> 5;
+    const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, d = tid & 255, d2 = tid & 127, grp = tid >> 7, lane = tid & 31, warp = tid >> 5;
     const uint32_t ntok = (uint32_t)posv[t] + 1, nch = (ntok + QSA_PAGE - 1) / QSA_PAGE;
     const float *base = part + ((size_t)t * a.max_chunks * QH + qh) * (HD + 2);
     const size_t cstride = (size_t)QH * (HD + 2);
@@ -467,21 +469,29 @@ __global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __h
     for (int i = 1; i < 32; i++) M = fmaxf(M, tmp[i]);
     for (uint32_t c = tid; c < nch; c += 1024) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
     __syncthreads();
-    // four thread groups take the chunks c = grp, grp + 4, ... (each in increasing order); the four partial sums are
-    // then added in group order, so the result depends only on the slot's own chunk count
-    float l = 0.f, acc = 0.f;
-#pragma unroll 8
-    for (uint32_t c = grp; c < nch; c += 4) {
+    // eight thread groups take the chunks c = grp, grp + 8, ... (each in increasing order); the partial sums are then added
+    // in group order, so the result depends only on the slot's own chunk count
+    float l = 0.f;
+    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 4
+    for (uint32_t c = grp; c < nch; c += 8) {
         const float w = wc[c];
+        const float2 v = *(const float2 *)(base + c * cstride + 2 * d2);
         l = fmaf(lc[c], w, l);
-        acc = fmaf(base[c * cstride + d], w, acc);
+        acc.x = fmaf(v.x, w, acc.x);
+        acc.y = fmaf(v.y, w, acc.y);
     }
-    accs[grp][d] = acc;
-    if (d == 0) ls[grp] = l;
+    accs[grp][d2] = acc;
+    if (d2 == 0) ls[grp] = l;
     __syncthreads();
     if (tid < HD) {
-        const float at = ((accs[0][d] + accs[1][d]) + accs[2][d]) + accs[3][d];
-        const float lt = ((ls[0] + ls[1]) + ls[2]) + ls[3];
+        const float *col = (const float *)&accs[0][0] + d;
+        float at = col[0], lt = ls[0];
+#pragma unroll
+        for (int g2 = 1; g2 < 8; g2++) {
+            at += col[g2 * HD];
+            lt += ls[g2];
+        }
         const float g = __half2float(qkv[(size_t)t * a.qkv_stride + qh * 2 * HD + HD + d]);
         const float o = __half2float(__float2half_rn(at / lt));
         y[((size_t)t * QH + qh) * HD + d] = __float2half_rn(o * (1.0f / (1.0f + expf(-g))));

@@ -157,3 +157,29 @@ def test_full_batch_of_64_rows_matches_each_slot_alone(gpu):
             la, _ = e.step([sids[i]], [toks[i]])
             assert np.array_equal(la[0].view(np.uint32), lb[i].view(np.uint32)), (cfg.hidden, sids[i])
         e.close()
+
+
+def test_benchmark_layer_shapes_match_fp64_reference(gpu):
+    """Four layers of the benchmark model itself (hidden 2048, 512 experts with top-10, 151 936-token vocabulary; three
+    Gated DeltaNet layers and one attention layer) against the chained FP64 reference: logits within tolerance, top-1
+    equal, chosen experts taken from the device and checked to be the reference's own top-10 wherever its margin is clear."""
+    from oracle.model_ref import RefModel
+    from qwental_b200.engine import Engine, default_cfg
+    e = Engine(gpu, default_cfg(layers=4, max_slots=4, max_ctx=2048, kv_pages=0, seed=3))
+    try:
+        ctx = {0: 700, 2: 255, 3: 40}
+        for sid, n in ctx.items():
+            e.seed_slot(sid, n, 2000 + sid)
+        ref = RefModel(e.cfg, e)
+        sids, toks = [3, 0, 2], [11, 150000, 77]
+        states = {s: ref.read_slot(e, s) for s in sids}
+        logits, _ = e.step(sids, toks)
+        assert np.isfinite(logits).all()
+        for i, s in enumerate(sids):
+            dev_ids = [e.tap("sel", l, np.uint8)[16:16 + 64 * 16 * 4].view(np.int32).reshape(64, 16)[i, :e.cfg.topk] for l in range(e.cfg.layers)]
+            lg, hh, chosen = ref.step(states[s], toks[i], ids_by_layer=dev_ids)
+            scale = np.abs(lg).max()
+            assert np.abs(logits[i] - lg).max() < 2e-2 * scale, (s, np.abs(logits[i] - lg).max(), scale)
+            assert int(logits[i].argmax()) == int(lg.argmax())
+    finally:
+        e.close()
