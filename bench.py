@@ -176,11 +176,15 @@ def workload_config(layers, slots, ctx_sum, world, graphs, ep="nccl"):
             "l2": "inputs larger than L2 (weights 35 GB, KV and state several GB per step)", "cuda_graphs": bool(graphs)}
 
 
-def cpu_baseline_avg(nslots, ctx, reps=3):
-    vals, last = [], None
-    for i in range(reps):
+def cpu_baseline_avg(nslots, ctx, reps=3, min_seconds=10.0):
+    """Mean over at least `reps` samples and at least `min_seconds` of CPU work (bounded at 12 samples)."""
+    vals, last, t0 = [], None, time.time()
+    i = 0
+    while i < reps or (time.time() - t0 < min_seconds and i < 12):
         last = cpu_step_sample(nslots, ctx, seed=i)
         vals.append(last[0])
+        i += 1
+    reps = i
     v, cores, kind, sample, _ = last
     return float(np.mean(vals)), cores, kind, sample + " (mean of %d samples)" % reps
 
@@ -191,7 +195,7 @@ def run_reference(args):
         return
     from qwental_b200 import synth
     ctx = synth.ragged_contexts(np.random.default_rng(0), args.slots)
-    v, cores, kind, sample = cpu_baseline_avg(args.slots, ctx, reps=max(1, min(args.steps, 3)))
+    v, cores, kind, sample = cpu_baseline_avg(args.slots, ctx, reps=max(1, min(args.steps, 3)), min_seconds=0.0)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": args.slots / v * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
