@@ -3,7 +3,7 @@
     python -m qwental_b200.build [--force] [--verbose]
 
 nvcc cross-compiles without a GPU.  The IQ3_S codebook include is generated first from the installed `gguf`
-package (oracle/gen_tables.py).  Objects and the library go to qwental_b200/_build/ (git-ignored).
+package (qwental_b200/csrc/gen_tables.py).  Objects and the library go to qwental_b200/_build/ (git-ignored).
 """
 from __future__ import annotations
 
@@ -34,7 +34,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OUT, exist_ok=True)
     gen = os.path.join(CSRC, "_gen", "iq3s_grid.inc")
     if force or not os.path.exists(gen):
-        subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "gen_tables.py"), gen], check=True)
+        subprocess.run([sys.executable, os.path.join(CSRC, "gen_tables.py"), gen], check=True)
     srcs = sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     hdrs += [os.path.join(ROOT, "include", f) for f in os.listdir(os.path.join(ROOT, "include"))] + [gen]
