@@ -53,6 +53,10 @@ int qw_engine_par_pick(qw_engine *e, const int32_t *prompt, int np, unsigned lon
 /* Stands in for qw_engine_par_prefill (src/engine.h:81): gives slot sid a context of ctx_len tokens whose KV
  * pages, GDN state and conv state are seeded synthetic values (K, V ~ N(0,1); S ~ N(0, 0.01)).  0 or -1. */
 int qw_engine_par_seed(qw_engine *e, int sid, int ctx_len, unsigned long long seed);
+/* src/engine.h:81.  Processes a prompt into slot sid (released first if it was in use) and returns the logits of its last
+ * position ([vocab], valid until the next step), NULL on failure.  There is no prefill kernel family and no prefix cache in
+ * this library: the prompt runs through the decode step one token at a time (*cached = 0). */
+const float *qw_engine_par_prefill(qw_engine *e, int sid, const int32_t *prompt, int np, int *cached);
 /* src/engine.h:91.  One decode step for B slots (sids distinct, 1 <= B <= QW_PAR_MAX): returns [B][vocab] fp32
  * logits in host-visible memory, valid until the next step; NULL on failure.  *gpu_ms = device time. */
 const float *qw_engine_par_step(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms);

@@ -880,6 +880,43 @@ extern "C" int qw_engine_par_step_sample(qw_engine *e, const int *sids, const in
     return B;
 }
 
+// Prompt processing for one slot (src/engine.h:81) without a prefill kernel family: the prompt is fed through the decode step
+// one token at a time (B = 1), from an empty slot -- recurrent and conv state zero, no KV.  It is the decode path's own
+// arithmetic, so "prefill then step" equals stepping every token; it costs one step per prompt token and exists so that
+// a scheduler can run pick -> prefill -> step -> finish end to end (there is no prefix cache: *cached = 0).
+extern "C" const float *qw_engine_par_prefill(qw_engine *e, int sid, const int32_t *prompt, int np, int *cached) {
+    if (cached) *cached = 0;
+    if (!e || sid < 0 || sid >= (int)e->slots.size() || !prompt || np < 1 || np >= e->c.max_ctx) return e ? (e->fail("par_prefill: bad arguments"), nullptr) : nullptr;
+    for (int i = 0; i < np; i++)
+        if (prompt[i] < 0 || prompt[i] >= e->V) return e->fail("par_prefill: token %d out of range", prompt[i]), nullptr;
+    if (e->slots[sid].used) release_slot(e, sid);
+    Slot &s = e->slots[sid];
+    if (!reserve_pages(e, sid, np + 1)) return nullptr;
+    s.used = true;
+    s.pos = 0;
+    s.last_use = ++e->clock;
+    {   // empty recurrent state
+        const size_t sst = (size_t)std::max(1, e->n_gdn) * e->HV * 128 * 128 * 4, cst = (size_t)std::max(1, e->n_gdn) * 3 * e->C * 4;
+        qw_batch *b = qw_batch_begin(e->g, false);
+        enc_fill(e, b, &e->sstate, (size_t)sid * sst, {0, sst, 0, 0, 0.f, 0.f});
+        enc_fill(e, b, &e->cstate, (size_t)sid * cst, {0, cst, 0, 0, 0.f, 0.f});
+        if (qw_batch_end(b) < 0) return e->fail("par_prefill: state reset failed"), nullptr;
+    }
+    const float *lg = nullptr;
+    for (int i = 0; i < np; i++) {
+        if (i + 1 < np) {  // intermediate positions: the step runs, nothing is copied back
+            const double t0 = qw_now();
+            const uint32_t mc = begin_step(e, &sid, &prompt[i], 1, 1);
+            if (!mc) return nullptr;
+            qw_batch *b = qw_batch_begin(e->g, false);
+            encode_step(e, b, 1, mc, true, 0);
+            if (qw_batch_end(b) < 0) return e->fail("par_prefill: device batch failed at position %d", i), nullptr;
+            end_step(e, &sid, 1, 1, (qw_now() - t0) * 1e3);
+        } else lg = qw_engine_par_step(e, &sid, &prompt[i], 1, nullptr);
+    }
+    return lg;
+}
+
 extern "C" double qw_engine_par_cost(qw_engine *e, int B) { return e && B >= 1 && B <= QW_PAR_MAX ? e->cost[B] : 0; }
 
 extern "C" void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *o) {

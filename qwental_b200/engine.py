@@ -37,6 +37,7 @@ def _bind(L):
         "qw_engine_last_step_bytes": (None, [vp, C.POINTER(StepBytes)]),
         "qw_engine_tap": (C.c_size_t, [vp, C.c_char_p, C.c_int, vp, C.c_size_t]),
         "qw_ep_unique_id": (C.c_int, [vp]), "qw_engine_ep_init": (C.c_int, [vp, vp]),
+        "qw_engine_par_prefill": (C.c_void_p, [vp, C.c_int, vp, C.c_int, vp]),
         "qw_engine_sample": (C.c_int32, [vp, C.c_int, vp, vp]),
         "qw_engine_par_step_sample": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, vp, vp]),
         "qw_engine_ep_export": (C.c_int, [vp, vp]), "qw_engine_ep_connect": (C.c_int, [vp, vp, C.c_int]),
@@ -165,6 +166,14 @@ class Engine:
         if got != n:
             raise GpuError("tap(%s, %d) failed" % (name, index))
         return out
+
+    def prefill(self, sid: int, prompt) -> np.ndarray:
+        """Feeds a prompt into an empty slot (token by token through the decode step); returns the last position's logits."""
+        p = np.ascontiguousarray(prompt, np.int32)
+        ptr = self.L.qw_engine_par_prefill(self.e, sid, p.ctypes.data, len(p), None)
+        if not ptr:
+            raise GpuError("prefill: " + self.error())
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_float)), shape=(self.cfg.vocab,)).copy()
 
     def step_sample(self, sids, toks, params, rng):
         """One decode step with sampling: params = [(temperature, top_k, top_p)] per row, rng = uint64 state per row

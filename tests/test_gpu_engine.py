@@ -183,3 +183,33 @@ def test_benchmark_layer_shapes_match_fp64_reference(gpu):
             assert int(logits[i].argmax()) == int(lg.argmax())
     finally:
         e.close()
+
+
+def test_prefill_is_the_decode_path_token_by_token(gpu):
+    """qw_engine_par_prefill feeds a prompt through the decode step: prefill(p) equals prefill(p[:-1]) followed by one
+    step of p[-1], bit for bit; the result does not depend on the slot; a slot that was in use is emptied first; a
+    prefilled slot steps together with a seeded one exactly as it steps alone."""
+    from qwental_b200.engine import Engine, tiny_cfg
+    from qwental_b200.gpu import GpuError
+    e = Engine(gpu, tiny_cfg())
+    try:
+        prompt = [5, 17, 300, 4, 4, 511, 0, 260, 33]
+        full = e.prefill(1, prompt)
+        assert e.pos(1) == len(prompt) and np.isfinite(full).all()
+        part = e.prefill(4, prompt[:-1])
+        lg, _ = e.step([4], [prompt[-1]])
+        assert np.array_equal(lg[0].view(np.uint32), full.view(np.uint32))
+        e.seed_slot(2, 300, 77)  # slot 2 in use with other contents: prefill starts it over
+        again = e.prefill(2, prompt)
+        assert np.array_equal(again.view(np.uint32), full.view(np.uint32)) and e.pos(2) == len(prompt)
+        a, _ = e.step([1], [9])
+        e.prefill(1, prompt)
+        e.seed_slot(6, 500, 5)
+        b, _ = e.step([6, 1], [3, 9])
+        assert np.array_equal(b[1].view(np.uint32), a[0].view(np.uint32))
+        with pytest.raises(GpuError):
+            e.prefill(0, [e.cfg.vocab])
+        with pytest.raises(GpuError):
+            e.prefill(99, [1])
+    finally:
+        e.close()
