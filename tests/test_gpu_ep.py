@@ -88,3 +88,34 @@ def test_expert_parallel_step_bit_identical_to_single_gpu(fused):
         for got, want in zip(r[1:4], ref[:3]):
             assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), r[0]
         assert np.array_equal(r[4], ref[3]) and np.array_equal(r[5], ref[4]), r[0]
+
+
+def test_missing_peer_is_reported_not_waited_for_forever():
+    """Failure detection without a fault: the kernel that consumes exchanged rows waits for every rank's sequence flag for a
+    bounded time (about 2 s).  Here rank 1's flag never advances (nothing sets it -- the situation after a peer process has
+    died between steps): the wait runs out, the batch ends with an error that names the bounded wait, and the device and
+    the library stay usable.  One GPU is enough."""
+    import time
+    from qwental_b200.gpu import Gpu, GpuError
+    gpu = Gpu()
+    try:
+        D, nb = 2048, 4
+        rng = np.random.default_rng(0)
+        h = gpu.buf_from(rng.standard_normal((nb, D)).astype(np.float32))
+        delta = gpu.buf_from(rng.standard_normal((nb, D)).astype(np.float16))
+        w = gpu.buf_from(np.ones(D, np.float32))
+        x = gpu.buf(nb * D * 2).zero()
+        flags = gpu.buf_from(np.array([1, 0, 0, 0, 0, 0, 0, 0], np.uint32))  # rank 0 published step 1, rank 1 never does
+        seq = gpu.buf_from(np.array([1, 0], np.uint32))
+        k = gpu.compile("add_rmsnorm", "add_rmsnorm_epx_t", ADD=1, EPX=2)
+        args = np.array([nb, D], np.uint32)
+        t0 = time.time()
+        with pytest.raises(GpuError, match="bounded wait"):
+            gpu.batch().kernel(k).buf(0, h).buf(1, delta).buf(2, w).buf(3, x).bytes(4, args).buf(7, flags).buf(8, seq).dispatch((nb,), (256,)).end()
+        assert 1.0 < time.time() - t0 < 10.0
+        # the same kernel completes at once when both ranks have published, and the device is still fine
+        flags.upload(np.array([1, 1, 0, 0, 0, 0, 0, 0], np.uint32))
+        gpu.batch().kernel(k).buf(0, h).buf(1, delta).buf(2, w).buf(3, x).bytes(4, args).buf(7, flags).buf(8, seq).dispatch((nb,), (256,)).end()
+        assert np.isfinite(x.download(np.float16, nb * D).astype(np.float32)).all()
+    finally:
+        gpu.close()
