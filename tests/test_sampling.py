@@ -64,6 +64,19 @@ def test_host_sampler_matches_the_reference_code():
                 assert got == want and int(mine[0]) == theirs.value, (V, T, k, p)
 
 
+def test_host_sampler_matches_reference_golden_vectors():
+    """The committed vectors were drawn by the reference's own sampler (tests/golden/gen_sample_golden.py)."""
+    import os
+    from qwental_b200.engine import sample
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "sample_golden.npz"))
+    for pi, (T, k, p) in enumerate(g["params"]):
+        for r in range(g["logits"].shape[0]):
+            st = np.array([g["seeds"][pi, r]], np.uint64)
+            for d in range(g["toks"].shape[2]):
+                tok = sample(g["logits"][r], float(T), int(k), float(p), st)
+                assert tok == g["toks"][pi, r, d] and st[0] == g["states"][pi, r, d], (pi, r, d)
+
+
 def test_sampler_follows_the_distribution():
     from qwental_b200.engine import sample
     lg = np.log(np.array([0.5, 0.25, 0.125, 0.125], np.float32))
