@@ -76,7 +76,8 @@ struct gdn_args {
 
 // One block per (v-head, slot): 512 threads, thread (rq = tid / 32, c4 = tid % 32) holds rows 8 rq .. 8 rq + 7 of columns
 // 4 c4 .. 4 c4 + 3 of the head's [DK][DV] state in registers: every state access is a 16-byte load or store and a warp
-// moves one whole 512-byte row per instruction.  The 16 row groups meet in shared memory (summed in group order).
+// moves one whole 512-byte row per instruction.  The 16 row groups meet in shared memory (summed in group order); q and k
+// are normalised by every warp for itself, so the block has three barriers in all.
 // binds: 0 = cv fp16 [nb][C], 1 = la [nb][HV], 2 = beta [nb][HV], 3 = state pool fp32 [slot][nlayers][HV][DK][DV],
 // 4 = z fp16, 5 = norm weight fp32 [DV], 6 = gy out fp16 [nb][HV*DV], 7 = slot ids, 8 = gdn_args; with O_OUT
 // defined 1 also 9 = o out fp16 [nb][HV*DV] (the un-normalised output, for tests).  grid (HV, nb) x 512
@@ -84,8 +85,8 @@ template <bool TILED>
 __global__ void __launch_bounds__(512, 2) gdn_fstep_k(const __half *cv, const float *la, const float *beta, float *pool, const __half *z,
                                                   const float *nw, __half *gy, const int32_t *sids, __half *oo, gdn_args a, uint32_t HK, uint32_t HV) {
     constexpr int DK = 128, DV = 128;
-    __shared__ float ks[DK], qs[DK], red[8];
-    __shared__ float4 part[16][32];
+    __shared__ float red[8];
+    __shared__ float4 part[2][16][32];  // [S^T k | S^T q][row group][column quad]
     pdl_sync();
     const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c4 = tid & 31, rq = tid >> 5, lane = tid & 31, warp = tid >> 5;
     const uint32_t hk = TILED ? hv % HK : hv / (HV / HK);
@@ -98,57 +99,63 @@ __global__ void __launch_bounds__(512, 2) gdn_fstep_k(const __half *cv, const fl
 #pragma unroll
     for (int i = 0; i < 8; i++) s[i] = S[(size_t)(8 * rq + i) * (DV / 4)];
 
-    // q / k L2 normalisation (threads 0..127 take q, 128..255 take k)
-    float xv = 0.f;
-    if (tid < 128) xv = __half2float(row[hk * DK + tid]);
-    else if (tid < 256) xv = __half2float(row[HK * DK + hk * DK + (tid - 128)]);
-    const float ssq = warp_sum(xv * xv);
-    if (warp < 8 && lane == 0) red[warp] = ssq;
-    __syncthreads();
-    if (tid < 128) {
-        const float r = rsqrtf((((red[0] + red[1]) + red[2]) + red[3]) / DK + GDN_EPS);
-        qs[tid] = __half2float(__float2half_rn(xv * r / DK));
-    } else if (tid < 256) {
-        const float r = rsqrtf((((red[4] + red[5]) + red[6]) + red[7]) / DK + GDN_EPS);
-        ks[tid - 128] = __half2float(__float2half_rn(xv * r * rsqrtf((float)DK)));
+    // q / k L2 normalisation, by every warp for itself (no block barrier): lane l squares elements 4l .. 4l+3, one butterfly
+    // gives the head's sum of squares; then the warp's own eight rows 8 rq .. 8 rq + 7 are scaled
+    const __half *qh = row + hk * DK, *kh = row + HK * DK + hk * DK;
+    float qn[8], kn[8];
+    {
+        const uint2 q4 = *(const uint2 *)(qh + 4 * lane), k4 = *(const uint2 *)(kh + 4 * lane);
+        const float2 qa = __half22float2(*(const __half2 *)&q4.x), qb = __half22float2(*(const __half2 *)&q4.y);
+        const float2 ka = __half22float2(*(const __half2 *)&k4.x), kb = __half22float2(*(const __half2 *)&k4.y);
+        const float qss = warp_sum(fmaf(qa.x, qa.x, fmaf(qa.y, qa.y, fmaf(qb.x, qb.x, qb.y * qb.y))));
+        const float kss = warp_sum(fmaf(ka.x, ka.x, fmaf(ka.y, ka.y, fmaf(kb.x, kb.x, kb.y * kb.y))));
+        const float rq_ = rsqrtf(qss / DK + GDN_EPS), rk_ = rsqrtf(kss / DK + GDN_EPS);
+        const uint4 qr = *(const uint4 *)(qh + 8 * rq), kr = *(const uint4 *)(kh + 8 * rq);  // the warp's eight rows (same for all lanes)
+        const uint32_t qw[4] = {qr.x, qr.y, qr.z, qr.w}, kw[4] = {kr.x, kr.y, kr.z, kr.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 qf = __half22float2(*(const __half2 *)&qw[j]), kf = __half22float2(*(const __half2 *)&kw[j]);
+            qn[2 * j] = __half2float(__float2half_rn(qf.x * rq_ / DK));
+            qn[2 * j + 1] = __half2float(__float2half_rn(qf.y * rq_ / DK));
+            kn[2 * j] = __half2float(__float2half_rn(kf.x * rk_ * rsqrtf((float)DK)));
+            kn[2 * j + 1] = __half2float(__float2half_rn(kf.y * rk_ * rsqrtf((float)DK)));
+        }
     }
-    __syncthreads();
 
     const float gdec = expf(la[t * HV + hv]), b = beta[t * HV + hv];
     float4 mem = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const float kk = ks[8 * rq + i];
+        const float kk = kn[i];
         s[i].x *= gdec; s[i].y *= gdec; s[i].z *= gdec; s[i].w *= gdec;
         mem.x = fmaf(s[i].x, kk, mem.x); mem.y = fmaf(s[i].y, kk, mem.y); mem.z = fmaf(s[i].z, kk, mem.z); mem.w = fmaf(s[i].w, kk, mem.w);
     }
-    part[rq][c4] = mem;
+    part[0][rq][c4] = mem;
     __syncthreads();
-    mem = part[0][c4];
+    mem = part[0][0][c4];
 #pragma unroll
     for (int r = 1; r < 16; r++) {
-        const float4 pv = part[r][c4];
+        const float4 pv = part[0][r][c4];
         mem.x += pv.x; mem.y += pv.y; mem.z += pv.z; mem.w += pv.w;
     }
     const uint2 vraw = *(const uint2 *)(row + 2 * HK * DK + hv * DV + 4 * c4);
     const float2 v01 = __half22float2(*(const __half2 *)&vraw.x), v23 = __half22float2(*(const __half2 *)&vraw.y);
     const float4 d = make_float4(b * (v01.x - mem.x), b * (v01.y - mem.y), b * (v23.x - mem.z), b * (v23.y - mem.w));
-    __syncthreads();
     float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const float kk = ks[8 * rq + i], qq = qs[8 * rq + i];
+        const float kk = kn[i], qq = qn[i];
         s[i].x = fmaf(kk, d.x, s[i].x); s[i].y = fmaf(kk, d.y, s[i].y); s[i].z = fmaf(kk, d.z, s[i].z); s[i].w = fmaf(kk, d.w, s[i].w);
         out.x = fmaf(s[i].x, qq, out.x); out.y = fmaf(s[i].y, qq, out.y); out.z = fmaf(s[i].z, qq, out.z); out.w = fmaf(s[i].w, qq, out.w);
     }
-    part[rq][c4] = out;
+    part[1][rq][c4] = out;
 #pragma unroll
     for (int i = 0; i < 8; i++) S[(size_t)(8 * rq + i) * (DV / 4)] = s[i];
     __syncthreads();
     float o1 = 0.f;
     const uint32_t c = tid;  // threads 0..127: one output column each
     if (tid < 128) {
-        const float *pc = (const float *)&part[0][0] + c;
+        const float *pc = (const float *)&part[1][0][0] + c;
         o1 = pc[0];
 #pragma unroll
         for (int r = 1; r < 16; r++) o1 += pc[r * 128];
