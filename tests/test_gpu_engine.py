@@ -104,6 +104,15 @@ def test_slot_errors_and_accounting(eng):
         eng.step([1], [1])                  # slot never seeded
     with pytest.raises(GpuError):
         eng.step([0], [eng.cfg.vocab])      # token out of range
+    with pytest.raises(GpuError):
+        eng.step([], [])                    # an empty batch
+    with pytest.raises(GpuError):
+        eng.step(list(range(65)), [0] * 65) # more rows than QW_PAR_MAX
+    eng.seed_slot(7, eng.cfg.max_ctx - 1, 9)  # the last position that fits
+    eng.step([7], [1])
+    with pytest.raises(GpuError):
+        eng.step([7], [1])                  # one more would exceed max_ctx
+    eng.finish(7)
     lg, _ = eng.step([0, 3], [1, 2])        # the engine is still usable
     b = eng.step_bytes()
     c = eng.cfg
