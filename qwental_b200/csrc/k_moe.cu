@@ -3,7 +3,7 @@
 // Replaces the reference's moe_pre_gg / gg_select / moe_gu_gg / moe_dn_gg / moe_cmb_gg
 // (kernels/moe_gg.metal:118-189, 534-663; host src/engine.c:568-646).  What is kept from the reference:
 //   - router logits in fp32 with one fixed summation order (so the chosen experts are reproducible),
-//   - top-k by repeated arg-max, equal logits -> lowest expert id; weights = softmax over the picked logits
+//   - top-k with equal logits -> lowest expert id; weights = softmax over the picked logits
 //     with the exponentials summed in rank order; shared-expert gate = sigmoid of an extra router row,
 //   - every distinct expert's weights are read and decoded once per step and applied to each token that chose
 //     it; a token's arithmetic does not depend on which other tokens are in the batch,

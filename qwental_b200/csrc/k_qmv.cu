@@ -405,7 +405,8 @@ static cudaError_t qmv_mma2_go(const QmvMmaP &p, int sm_count, cudaStream_t st) 
     return cudaGetLastError();
 }
 
-// The grid given by the host is ignored (the kernel is persistent: one block per SM); block size must be 256.
+// The grid and block given by the host are ignored (the kernels are persistent and size themselves).  Defines: GF (21 = IQ3_S,
+// 8 = Q8_0), KD, YT_F32; EPX = ranks of a slot-sharded projection whose rows go to every rank (see below).
 static cudaError_t launch_qmv_mma(const QwLaunch &L) {
     qmv_args a;
     int gf;
