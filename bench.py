@@ -9,9 +9,12 @@ One "step" advances every slot by one token.  Prints ONE JSON line (rank 0):
             engine's stream, max over ranks)
   e2e       the same metric through the public C-ABI call qw_engine_par_step_greedy with host token ids in and
             host sampled ids out every step
-  roofline  the dominant kernel (MoE gate/up, an IQ3_S batched matvec over the gathered experts): algorithmic
+  roofline  the dominant kernel (the MoE expert FFN: IQ3_S gate/up/down matvecs over the gathered experts): algorithmic
             bytes per launch / mean launch duration (CUDA events around every dispatch, qw_profile_*), against the
-            measured HBM copy bandwidth of MEASURED_PEAKS.json
+            measured HBM copy bandwidth of MEASURED_PEAKS.json; copy_ceiling_gbs = the same launch with the decode taken
+            out (the staged copies only), timed the same way
+  sustained the same chained steps repeated for a few seconds, with the SM clock seen meanwhile
+  slots64   the same step at 64 active slots (1 GPU)
   cpu_baseline  the CPU oracle (block decode + fp32 dot on all host cores, numpy attention / GDN) timed on a
             bounded sample of the same step and scaled to a whole step
 With --gpus N > 1 (launched by torchrun) the experts are sharded over the ranks (expert parallel) and the
@@ -45,7 +48,7 @@ def measured_peak_gbs():
             return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
         except Exception:
             pass
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s)"
 
 
 class ClockSampler:
@@ -87,6 +90,13 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------------------- CPU arm
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
     """Times the CPU implementation of one decode step on a bounded sample and scales it to the whole step.
 
@@ -103,11 +113,11 @@ def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
     rng = np.random.default_rng(seed)
     x = synth.acts_fp16(rng, nslots, D)
     xf = x.astype(np.float32)
-    cores = orc.max_threads()
+    cores = host_threads()  # asked for explicitly: a launcher may have set OMP_NUM_THREADS=1 for its ranks
     t = {}
 
     def mv(W, K, xin):
-        return orc.qmv_cpu(21, W, K, xin, 0)[0]
+        return orc.qmv_cpu(21, W, K, xin, cores)[0]
 
     # ---- MoE block (same for both layer types)
     Wr = (rng.standard_normal((E, D)) * 0.02).astype(np.float16)
@@ -158,7 +168,7 @@ def cpu_step_sample(nslots: int, ctx: np.ndarray, seed: int = 0):
     if os.path.exists(orc.REF_LIB):
         orc.ref_dq_q8_0_rows(Wl[:2048], D)  # the reference's own decoder on a slice (single thread, its only CPU code on this path)
         kind = "port (+ reference ggml_dq.c for a Q8_0 slice)"
-    orc.qmv_cpu(8, Wl, D, xf, 0)
+    orc.qmv_cpu(8, Wl, D, xf, cores)
     t["lm_head_eighth"] = time.perf_counter() - t0
     step = 36 * (t["gdn_layer"] + t["moe"]) + 12 * (t["attn_layer"] + t["moe"]) + 8 * t["lm_head_eighth"]
     sample = ("1 GDN layer + 1 attention layer + MoE block (%d distinct experts) + 1/8 of lm_head, %d slots; "
@@ -190,17 +200,31 @@ def cpu_baseline_avg(nslots, ctx, reps=3, min_seconds=10.0):
 
 
 def run_reference(args):
+    """The CPU implementation alone: W untimed and K timed steps, each step one bounded sample of the workload (see
+    cpu_step_sample) scaled to a whole decode step; value = slots / mean scaled step time over the K timed samples."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from qwental_b200 import synth
     ctx = synth.ragged_contexts(np.random.default_rng(0), args.slots)
-    v, cores, kind, sample = cpu_baseline_avg(args.slots, ctx, reps=max(1, min(args.steps, 3)), min_seconds=0.0)
+    K, W = max(1, args.steps), max(0, args.warmup)
+    for i in range(W):
+        cpu_step_sample(args.slots, ctx, seed=1000 + i)
+    vals, spent, last = [], 0.0, None
+    t0 = time.time()
+    for i in range(K):
+        last = cpu_step_sample(args.slots, ctx, seed=i)
+        vals.append(args.slots / last[0])  # scaled seconds per step
+        spent += sum(last[4].values())
+    _, cores, kind, sample, _ = last
+    step_s = float(np.mean(vals))
+    v = args.slots / step_s
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": args.slots / v * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(48, args.slots, int(ctx.sum()), 1, False),
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": K, "warmup": W,
+        "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(48, args.slots, int(ctx.sum()), 1, True),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": sample + " (each of the %d timed steps is one such sample; %.1f s of CPU work measured, %.1f s wall)" % (K, spent, time.time() - t0)},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))

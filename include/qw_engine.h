@@ -63,19 +63,40 @@ const float *qw_engine_par_step(qw_engine *e, const int *sids, const int32_t *to
 /* The same step with the arg-max fused on the device (ties -> lowest id, as src/engine.c:6144-6148):
  * returns B token ids in host-visible memory; logits are not copied to the host. */
 const int32_t *qw_engine_par_step_greedy(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms);
-/* Sampling.  qw_sample_params = the sampling fields of the reference's qw_gen (src/engine.h:40-42): temperature <= 0 is
- * greedy; top_k <= 0 or > 256 means 256; top_p >= 1 (or <= 0) means no nucleus cut.  qw_engine_sample is the reference's
- * function of that name (src/engine.h:125, src/engine.c:9410-9418; the vocabulary size is a parameter here): candidates =
- * the top_k logits (ties -> lower id first), softmax(logit / T) over them, top-p cut, renormalise, one splitmix64 draw
- * from *rng.  qw_engine_par_step_sample runs the decode step, selects the 256 best (id, logit) pairs of every row on the
- * device and finishes on the host from those -- the same tokens as qw_engine_sample on the full logits, without copying or
- * scanning the [B][vocab] logits on the host.  g and rng have one entry per row; out_ids [B].  Returns B or -1. */
+/* Sampling.  qw_gen is the reference's generation request (src/engine.h:39-52), field for field, so that a host compiled
+ * against the reference's header passes the same bytes; the sampler reads only temperature (<= 0: greedy), top_k (<= 0 or
+ * > 256 means 256) and top_p (>= 1 or <= 0: no nucleus cut).  qw_sample_params = those first three fields.
+ *
+ * qw_engine_sample is the reference's function of that name with its signature (src/engine.h:125, src/engine.c:9410-9418):
+ * candidates = the top_k logits (ties -> lower id first), softmax(logit / T) over them, top-p cut, renormalise, one
+ * splitmix64 draw from *rng.  The reference compiles the vocabulary size in; here it is the vocabulary of the engine opened
+ * last in this process (or what qw_engine_sample_set_vocab set); -1 if neither happened.  qw_engine_sample_v is the same
+ * sampler with the vocabulary size as a parameter.  qw_engine_par_step_sample runs the decode step, selects the 256 best
+ * (id, logit) pairs of every row on the device and finishes on the host from those -- the same tokens as qw_engine_sample on
+ * the full logits, without copying or scanning the [B][vocab] logits on the host.  g and rng have one entry per row;
+ * out_ids [B].  Returns B or -1. */
+typedef struct {
+    float temperature;
+    int top_k;
+    float top_p;
+    unsigned long long seed;
+    int max_tokens;
+    const int32_t *stop;
+    int nstop;
+    bool spec;
+    const int *persist;
+    int npersist;
+    volatile bool *yield;
+    bool (*pf_yield)(void *ctx);
+} qw_gen;
 typedef struct {
     float temperature;
     int top_k;
     float top_p;
 } qw_sample_params;
-int32_t qw_engine_sample(const float *logits, int vocab, const qw_sample_params *g, unsigned long long *rng);
+int32_t qw_engine_sample(const float *logits, const qw_gen *g, unsigned long long *rng);
+int32_t qw_engine_sample_v(const float *logits, int vocab, const qw_sample_params *g, unsigned long long *rng);
+void qw_engine_sample_set_vocab(int vocab);
 int qw_engine_par_step_sample(qw_engine *e, const int *sids, const int32_t *toks, int B, const qw_sample_params *g, unsigned long long *rng,
                               int32_t *out_ids, double *gpu_ms);
 /* nsteps greedy steps back to back with no host round trip between them (each step's ids feed the next);
@@ -94,6 +115,12 @@ typedef struct {
     long long ctx_tokens;   /* sum of context lengths attended in the last step */
 } qw_step_bytes;
 void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *out);
+
+/* Measurement aid (no counterpart in the reference's engine; its benches time pure-read kernels, bench/moe_bw.c:1-3): while
+ * on, steps run the copy-only twin of the fused expert FFN kernel -- the same staged copies of the chosen experts' weights,
+ * no decode, no output -- so a profiled step shows what the copy pipeline alone sustains.  Steps taken while it is on
+ * produce meaningless tokens.  0, or -1 if this engine does not use the fused kernel. */
+int qw_engine_set_moe_probe(qw_engine *e, int on);
 
 /* Debug taps for the parity tests (role of the reference's QW_MOE_TEST / QW_DN_TAP dumps, src/engine.c:7942-7999):
  * copy a named internal buffer to the host; dst == NULL returns the size.  Last step: "h" fp32 [B][D],

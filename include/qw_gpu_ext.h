@@ -52,9 +52,11 @@ void qw_gpu_set_pdl(qw_gpu *g, bool on);
  * Inputs are what qsa_attn + qsa_merge take through a batch: q fp16 [nb][16][256] (already normalised and rotated),
  * the paged KV pool and its size in bytes, the page table int32 [slots][max_pages], pos / slot_ids int32 [nb],
  * qkv fp16 rows (for the output gate), y fp16 [nb][4096] out; `stream` is a cudaStream_t.  All pointers are device
- * pointers.  The first call on a device looks up the array's address: make it outside any stream capture.  Calls
- * that overlap on the GPU share the array and race: serialise them.  Returns 0, or a negative code with a message
- * in err (-2: the request exceeds the static scratch). */
+ * pointers; every row must satisfy pos[t] + 1 <= max_chunks * 256 (the entry point cannot read device memory to check:
+ * a longer row is attended over its first max_chunks pages only).  The first call on a device looks up the array's
+ * address: make it outside any stream capture.  Calls that overlap on the GPU share the array and race: serialise
+ * them.  Returns 0, or a negative code with a message in err (-1: bad argument, -2: the request exceeds the static
+ * scratch, -3: CUDA error). */
 int qw_attn_decode_static(const void *q, const void *kv_pool, size_t kv_pool_bytes, const int32_t *page_table, const int32_t *pos,
                           const int32_t *slot_ids, const void *qkv, void *y, uint32_t nb, uint32_t layer, uint32_t nlayers, uint32_t qkv_stride,
                           uint32_t max_pages, uint32_t max_chunks, void *stream, char *err, size_t errlen);

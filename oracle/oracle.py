@@ -11,8 +11,11 @@ Two layers:
       decode attention bench/qsa.c:181-200 + output gate kernels/qsa_dec.metal:643-644
       GDN step         bench/gdn_decode.c:74-85 and tools/dn_ref.py:63-80 (norms, decay, gated RMSNorm,
                        fp16 rounding points)
-Parity pin: see tests/test_oracle_pins.py (gguf.quants 0.19.0 on golden blocks; reference src/ggml_dq.c
-compiled into oracle/_ref for Q8_0).
+Parity pin: see tests/test_oracle_pins.py -- block decode against gguf.quants 0.19.0 on golden blocks and the
+reference's src/ggml_dq.c compiled into oracle/_ref (Q8_0); the three FP64 layer references against the reference's own
+CPU double-precision checks (bench/gdn_decode.c:74-84, bench/qsa.c:184-201, bench/moe_decode.c:133-177) compiled into
+oracle/_ref/liblayer_ref.so by oracle/gen_layer_ref.py, live where the reference tree is present and through the
+committed vectors tests/golden/layer_ref_golden.npz everywhere.
 """
 from __future__ import annotations
 
@@ -26,6 +29,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "_build", "libqw_oracle.so")
 REF_LIB = os.path.join(HERE, "_ref", "libggml_dq_ref.so")
 REF_DQCPU = os.path.join(HERE, "_ref", "dqcpu")
+REF_LAYERS = os.path.join(HERE, "_ref", "liblayer_ref.so")  # the reference's CPU layer checks (oracle/gen_layer_ref.py)
 
 IQ3_S, Q8_0 = 21, 8
 _u8p, _u16p, _f32p, _f64p, _i32p = (C.POINTER(t) for t in (C.c_uint8, C.c_uint16, C.c_float, C.c_double, C.c_int32))
@@ -152,10 +156,13 @@ def h16(a):
     return np.asarray(a).astype(np.float16).astype(np.float64)
 
 
-def moe_ref(x16, Wr16, wsg16, gate, up, down, sh_gate, sh_up, sh_down, D, I, topk_n=10, ids=None):
+def moe_ref(x16, Wr16, wsg16, gate, up, down, sh_gate, sh_up, sh_down, D, I, topk_n=10, ids=None, ref_arith=False):
     """FP64 MoE layer (tools/moe_ref.py:60,72-82).  gate/up: raw IQ3_S [E][I][rb(D)], down: [E][D][rb(I)];
     shared expert the same shapes without the E axis.  `ids` (optional [B][topk]) overrides the FP64
     selection so the output can be compared for the experts a device actually chose.
+    ref_arith=True reproduces the arithmetic of the reference's C check (bench/moe_decode.c:133-177) instead of
+    pure FP64: expert products weight * activation are formed in fp32 before they are summed in double, and H is
+    rounded to fp16 (:170) -- the mode tests/test_oracle_pins.py holds against that code.
     Returns (out [B][D] float64, ids64 [B][topk], gap [B] = 10th minus 11th FP64 logit)."""
     x = np.asarray(x16, np.float16).astype(np.float64)
     Wr = np.asarray(Wr16, np.float16).astype(np.float64)
@@ -165,23 +172,33 @@ def moe_ref(x16, Wr16, wsg16, gate, up, down, sh_gate, sh_up, sh_down, D, I, top
     srt = -np.sort(-lg, axis=1)
     gap = srt[:, topk_n - 1] - srt[:, topk_n]
     use = ids64 if ids is None else np.asarray(ids)
-    SG, SU, SD = (dq_rows(IQ3_S, sh_gate, D).astype(np.float64), dq_rows(IQ3_S, sh_up, D).astype(np.float64),
-                  dq_rows(IQ3_S, sh_down, I).astype(np.float64))
+
+    def mv(M, v):
+        if not ref_arith:
+            return M.astype(np.float64) @ v
+        return (M.astype(np.float32) * np.asarray(v, np.float32)[None, :]).astype(np.float64).sum(1)
+
+    def expert(G, U, Dn, xt):
+        h = silu(mv(G, xt)) * mv(U, xt)
+        if ref_arith:
+            h = h.astype(np.float32).astype(np.float16).astype(np.float32)
+        return mv(Dn, h)
+
+    SG, SU, SD = dq_rows(IQ3_S, sh_gate, D), dq_rows(IQ3_S, sh_up, D), dq_rows(IQ3_S, sh_down, I)
     out = np.zeros((B, D))
     cache = {}
     for t in range(B):
         l = lg[t, use[t]]
-        w = np.exp(l - l.max())
+        w = np.exp(l - l[0] if ref_arith else l - l.max())
         w /= w.sum()
         for e, we in zip(use[t], w):
             e = int(e)
             if e not in cache:
-                cache[e] = (dq_rows(IQ3_S, gate[e], D).astype(np.float64), dq_rows(IQ3_S, up[e], D).astype(np.float64),
-                            dq_rows(IQ3_S, down[e], I).astype(np.float64))
+                cache[e] = (dq_rows(IQ3_S, gate[e], D), dq_rows(IQ3_S, up[e], D), dq_rows(IQ3_S, down[e], I))
             G, U, Dn = cache[e]
-            out[t] += we * (Dn @ (silu(G @ x[t]) * (U @ x[t])))
+            out[t] += we * expert(G, U, Dn, x[t])
         sgl = float(np.asarray(wsg16, np.float16).astype(np.float64) @ x[t])
-        out[t] += sigmoid(sgl) * (SD @ (silu(SG @ x[t]) * (SU @ x[t])))
+        out[t] += sigmoid(sgl) * expert(SG, SU, SD, x[t])
     return out, ids64, gap
 
 
@@ -189,20 +206,8 @@ def attn_ref(q16, K16, V16, gate16):
     """FP64 decode attention of one slot (bench/qsa.c:181-200) with the output gate of
     kernels/qsa_dec.metal:643-644.  q16 [QH][HD], K16/V16 [L][KVH][HD], gate16 [QH][HD] (pre-sigmoid).
     Returns y [QH][HD] float64 = fp16(o) * sigmoid(gate)."""
-    q = np.asarray(q16, np.float16).astype(np.float64)
-    K = np.asarray(K16, np.float16).astype(np.float64)
-    V = np.asarray(V16, np.float16).astype(np.float64)
     g = np.asarray(gate16, np.float16).astype(np.float64)
-    QH, HD = q.shape
-    KVH = K.shape[1]
-    y = np.empty((QH, HD))
-    for h in range(QH):
-        kv = h // (QH // KVH)
-        s = K[:, kv, :] @ q[h] / np.sqrt(HD)
-        p = np.exp(s - s.max())
-        o = (p / p.sum()) @ V[:, kv, :]
-        y[h] = h16(o) * sigmoid(g[h])
-    return y
+    return h16(attn_core_ref(q16, K16, V16)) * sigmoid(g)
 
 
 def rope_ref(v, pos, rd=64, theta=1e7):
@@ -222,27 +227,92 @@ def rmsnorm_ref(x, w, eps=1e-6):
     return x / np.sqrt((x * x).mean(-1, keepdims=True) + eps) * np.asarray(w, np.float64)
 
 
+def gdn_core_ref(S, qn, kn, v, la, beta, hk_of):
+    """The recurrence alone (bench/gdn_decode.c:74-84) on already normalised q / k [HK][DK]: S [HV][DK][DV] is decayed,
+    mem = S^T k, delta = beta (v - mem), S += k delta^T, o = S^T q.  Returns (S_new, o [HV][DV]) in float64."""
+    S = np.array(S, np.float64)
+    kk, qq = np.asarray(kn, np.float64)[hk_of], np.asarray(qn, np.float64)[hk_of]
+    S *= np.exp(np.asarray(la, np.float64))[:, None, None]
+    mem = np.einsum("hkd,hk->hd", S, kk)
+    d = np.asarray(beta, np.float64)[:, None] * (np.asarray(v, np.float64) - mem)
+    S += kk[:, :, None] * d[:, None, :]
+    return S, np.einsum("hkd,hk->hd", S, qq)
+
+
 def gdn_step_ref(S, q16, k16, v16, la, beta, z16, nw, hk_of, eps=1e-6):
     """FP64 Gated DeltaNet step of one slot (bench/gdn_decode.c:74-85, tools/dn_ref.py:63-80).
     S [HV][DK][DV] (updated copy returned), q16/k16 [HK][DK] raw conv outputs (normalised here: q also
     times DK^-1/2, both rounded to fp16 as dn_ref.py:63-64), v16 [HV][DV], la/beta [HV],
     z16 [HV][DV], nw [DV].  Returns (S_new, o16 [HV][DV] (fp16-rounded), y [HV][DV] gated RMSNorm)."""
-    S = np.array(S, np.float64)
     q = np.asarray(q16, np.float16).astype(np.float64)
     k = np.asarray(k16, np.float16).astype(np.float64)
     v = np.asarray(v16, np.float16).astype(np.float64)
     DK = q.shape[-1]
     qn = h16(q / np.sqrt((q * q).mean(-1, keepdims=True) + eps) / DK)
     kn = h16(k / np.sqrt((k * k).mean(-1, keepdims=True) + eps) / np.sqrt(DK))
-    kk, qq = kn[hk_of], qn[hk_of]
-    S *= np.exp(np.asarray(la, np.float64))[:, None, None]
-    mem = np.einsum("hkd,hk->hd", S, kk)
-    d = np.asarray(beta, np.float64)[:, None] * (v - mem)
-    S += kk[:, :, None] * d[:, None, :]
-    o = h16(np.einsum("hkd,hk->hd", S, qq))
+    S, o = gdn_core_ref(S, qn, kn, v, la, beta, hk_of)
+    o = h16(o)
     r = 1.0 / np.sqrt((o * o).mean(-1, keepdims=True) + eps)
     y = o * r * np.asarray(nw, np.float64) * sigmoid(np.asarray(z16, np.float16).astype(np.float64))
     return S, o, y
+
+
+def attn_core_ref(q16, K16, V16):
+    """softmax(q . K / sqrt(HD)) . V per head in float64, before the fp16 rounding and the gate (bench/qsa.c:184-201)."""
+    q = np.asarray(q16, np.float16).astype(np.float64)
+    K = np.asarray(K16, np.float16).astype(np.float64)
+    V = np.asarray(V16, np.float16).astype(np.float64)
+    QH, HD = q.shape
+    KVH = K.shape[1]
+    o = np.empty((QH, HD))
+    for h in range(QH):
+        kv = h // (QH // KVH)
+        s = K[:, kv, :] @ q[h] / np.sqrt(HD)
+        p = np.exp(s - s.max())
+        o[h] = (p / p.sum()) @ V[:, kv, :]
+    return o
+
+
+# ---- the reference's own CPU checks of these layers, compiled from its bench sources into oracle/_ref/liblayer_ref.so
+def _layer_ref():
+    r = C.CDLL(REF_LAYERS)
+    return r
+
+
+def ref_gdn_core(S, qn16, kn16, v16, la, beta):
+    """bench/gdn_decode.c:74-84 on fp16 q / k / v: (S_new, o) in float64; v-head h reads k-head h // (HV / HK)."""
+    S0 = np.array(S, np.float64)
+    HV, DK, DV = S0.shape
+    qn16, kn16, v16 = (np.ascontiguousarray(a, np.float16) for a in (qn16, kn16, v16))
+    pa, pb = np.ascontiguousarray(la, np.float32), np.ascontiguousarray(beta, np.float32)
+    out = np.zeros((HV, DV))
+    _layer_ref().ref_gdn_core(HV, qn16.shape[0], DK, DV, _p(pa, _f32p), _p(pb, _f32p), _p(qn16.view(np.uint16), _u16p),
+                              _p(kn16.view(np.uint16), _u16p), _p(v16.view(np.uint16), _u16p), _p(S0, _f64p), _p(out, _f64p))
+    return S0, out
+
+
+def ref_attn_core(q16, K16, V16):
+    """bench/qsa.c:184-201 for 16 query heads, 2 kv heads, head dim 256: o [16][256] float64."""
+    q16, K16, V16 = (np.ascontiguousarray(a, np.float16) for a in (q16, K16, V16))
+    assert q16.shape == (16, 256) and K16.shape[1:] == (2, 256)
+    out = np.zeros((16, 256))
+    _layer_ref().ref_attn_core(K16.shape[0], _p(q16.view(np.uint16), _u16p), _p(K16.view(np.uint16), _u16p), _p(V16.view(np.uint16), _u16p),
+                               _p(out, _f64p))
+    return out
+
+
+def ref_moe_check(x16, wsg16, Wr, G, U, Dn, SG, SU, SD):
+    """bench/moe_decode.c:133-177 for one token at E 32, TOPK 4, D 256, I 256; all matrices dequantised fp32
+    (Wr [E][D], G/U [E*I][D], Dn [E*D][I], shared SG/SU [I][D], SD [D][I]).  Returns (ids [4], out [256] float64)."""
+    f = lambda a: np.ascontiguousarray(a, np.float32)
+    x16, wsg16 = np.ascontiguousarray(x16, np.float16), np.ascontiguousarray(wsg16, np.float16)
+    Wr, G, U, Dn, SG, SU, SD = map(f, (Wr, G, U, Dn, SG, SU, SD))
+    assert Wr.shape == (32, 256) and G.shape == (32 * 256, 256) and Dn.shape == (32 * 256, 256)
+    ids, out, gpu = np.zeros(4, np.int32), np.zeros(256), np.zeros(4, np.uint32)
+    _layer_ref().ref_moe_check(_p(x16.view(np.uint16), _u16p), _p(wsg16.view(np.uint16), _u16p), _p(Wr, _f32p), _p(G, _f32p), _p(U, _f32p),
+                               _p(Dn, _f32p), _p(SG, _f32p), _p(SU, _f32p), _p(SD, _f32p), gpu.ctypes.data_as(C.POINTER(C.c_uint32)),
+                               _p(ids, _i32p), _p(out, _f64p))
+    return ids, out
 
 
 # ---- sampling: make_dist + dist_draw + splitmix64 of the reference host (src/engine.c:6085-6143, 9410-9418), with its

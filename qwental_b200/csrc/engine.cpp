@@ -98,6 +98,10 @@ struct qw_engine {
     qw_buf epx{};            // [2][Pg] (double-buffered by layer parity) + flag array, exported to the other ranks
     qw_buf ep_peer[8]{};     // the other ranks' epx (ep_peer[own rank] aliases epx)
     qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr, *k_topk = nullptr;
+    // gate/up + down of the expert FFN in one launch (moe_ffn), where the shapes allow it; QW_MOE_FFN=split keeps the two launches
+    bool ffn_fused = false;
+    qw_kernel *k_ffn = nullptr, *k_ffn_x = nullptr, *k_ffn_probe = nullptr;
+    bool moe_probe = false;  // measurement only: the copy-only twin of moe_ffn runs in its place (outputs are not produced)
     // slot sharding on top of the fused exchange: attention / GDN (their projections included) run only for the rows whose
     // slot this rank owns (slot % ep_size == ep_rank); the out-projection stores its rows into every rank's `ob` and publishes
     bool slot_shard = false;
@@ -294,6 +298,15 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          compile(e, "moe_gu", "moe_gu", md, &e->k_gu) && compile(e, "moe_dn", "moe_dn", md, &e->k_dn) && compile(e, "moe_cmb", "moe_cmb", md, &e->k_cmb) &&
          compile(e, "moe_route", "moe_route", md, &e->k_route) &&
          compile(e, "add_rmsnorm", "cmb_add_rmsnorm", {{"CMB", 1}, {"TOPK", e->TOPK}}, &e->k_norm_cmb);
+    {
+        const char *fm = getenv("QW_MOE_FFN");
+        e->ffn_fused = e->D % 2048 == 0 && e->D <= 2048 && e->I == 512 && !(fm && !strcmp(fm, "split"));
+        if (ok && e->ffn_fused) {
+            auto mp = md;
+            mp.push_back({"PROBE", 1});
+            ok = compile(e, "moe_ffn", "moe_ffn", md, &e->k_ffn) && compile(e, "moe_ffn", "moe_ffn_copy_probe", mp, &e->k_ffn_probe);
+        }
+    }
     ok = ok && compile(e, "k_topk", "k_topk", {}, &e->k_topk);
     e->k_ar = nullptr;
     if (ok && c.ep_size > 1) ok = compile(e, "ep_allreduce", "ep_allreduce", {}, &e->k_ar);
@@ -336,6 +349,7 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     }
     e->slots.resize(c.max_slots);
     for (int p = kvp - 1; p >= 0; p--) e->free_pages.push_back(p);
+    qw_engine_sample_set_vocab(e->V);
     return e;
 }
 
@@ -614,36 +628,58 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
         qw_batch_bytes(b, 14, &sa, sizeof sa);
         qw_batch_dispatch(b, (e->E + 1 + 7) / 8, 1, 1, 1024, 1, 1);
         const uint32_t ebase = (uint32_t)e->e_lo;
-        qw_batch_kernel(b, e->k_gu);
-        qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
-        qw_batch_buf(b, 1, &e->exu, (size_t)l * ex_bytes);
-        qw_batch_buf(b, 2, &e->shg, (size_t)l * gu_bytes);
-        qw_batch_buf(b, 3, &e->shu, (size_t)l * gu_bytes);
-        qw_batch_buf(b, 4, &e->x, 0);
-        qw_batch_buf(b, 5, &e->msel, selo);
-        qw_batch_buf(b, 6, &e->Hhi, 0);
-        qw_batch_buf(b, 7, &e->Hlo, 0);
-        qw_batch_bytes(b, 10, &ebase, 4);
-        qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
-        if (e->c.ep_size > 1 && !e->ep_fused) {  // rows of experts held elsewhere must read as zero before the exchange
-            const fill_args z = {0, (uint64_t)nb * (e->TOPK + 1) * D * 4, 0, 0, 0.f, 0.f};
-            enc_fill(e, b, &e->Pg, 0, z);
+        const bool zero_first = e->c.ep_size > 1 && !e->ep_fused;  // rows of experts held elsewhere must read as zero before the NCCL exchange
+        // the down projection's output: Pg, or (fused exchange) Pg[layer parity] of every rank -- two buffers suffice because a rank
+        // can run at most one down projection ahead of the slowest rank (its next norm waits for everybody's flags)
+        auto bind_pg = [&]() {
+            if (e->ep_fused) {
+                const size_t po = (size_t)(l & 1) * e->pg_bytes;
+                qw_batch_buf(b, 9, &e->epx, po);
+                bind_peers(po, true);
+            } else qw_batch_buf(b, 9, &e->Pg, 0);
+            qw_batch_bytes(b, 10, &ebase, 4);
+        };
+        if (e->ffn_fused) {
+            if (zero_first) {
+                const fill_args z = {0, (uint64_t)nb * (e->TOPK + 1) * D * 4, 0, 0, 0.f, 0.f};
+                enc_fill(e, b, &e->Pg, 0, z);
+            }
+            qw_batch_kernel(b, e->ep_fused ? e->k_ffn_x : e->moe_probe ? e->k_ffn_probe : e->k_ffn);  // gate/up, SiLU * up and down of every chosen expert in one launch
+            qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 1, &e->exu, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 2, &e->shg, (size_t)l * gu_bytes);
+            qw_batch_buf(b, 3, &e->shu, (size_t)l * gu_bytes);
+            qw_batch_buf(b, 4, &e->x, 0);
+            qw_batch_buf(b, 5, &e->msel, selo);
+            qw_batch_buf(b, 6, &e->exd, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 7, &e->shd, (size_t)l * gu_bytes);
+            bind_pg();
+            qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
+        } else {
+            qw_batch_kernel(b, e->k_gu);
+            qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 1, &e->exu, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 2, &e->shg, (size_t)l * gu_bytes);
+            qw_batch_buf(b, 3, &e->shu, (size_t)l * gu_bytes);
+            qw_batch_buf(b, 4, &e->x, 0);
+            qw_batch_buf(b, 5, &e->msel, selo);
+            qw_batch_buf(b, 6, &e->Hhi, 0);
+            qw_batch_buf(b, 7, &e->Hlo, 0);
+            qw_batch_bytes(b, 10, &ebase, 4);
+            qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
+            if (zero_first) {
+                const fill_args z = {0, (uint64_t)nb * (e->TOPK + 1) * D * 4, 0, 0, 0.f, 0.f};
+                enc_fill(e, b, &e->Pg, 0, z);
+            }
+            qw_batch_kernel(b, e->ep_fused ? e->k_dn_x : e->k_dn);
+            qw_batch_buf(b, 0, &e->exd, (size_t)l * ex_bytes);
+            qw_batch_buf(b, 2, &e->shd, (size_t)l * gu_bytes);
+            qw_batch_buf(b, 5, &e->msel, selo);
+            qw_batch_buf(b, 6, &e->Hhi, 0);
+            qw_batch_buf(b, 7, &e->Hlo, 0);
+            bind_pg();
+            qw_batch_dispatch(b, D / 64, nb * e->TOPK + 1, 1, 256, 1, 1);
         }
-        qw_batch_kernel(b, e->ep_fused ? e->k_dn_x : e->k_dn);
-        qw_batch_buf(b, 0, &e->exd, (size_t)l * ex_bytes);
-        qw_batch_buf(b, 2, &e->shd, (size_t)l * gu_bytes);
-        qw_batch_buf(b, 5, &e->msel, selo);
-        qw_batch_buf(b, 6, &e->Hhi, 0);
-        qw_batch_buf(b, 7, &e->Hlo, 0);
-        if (e->ep_fused) {
-            // every row goes into Pg[layer parity] of every rank; two buffers suffice because a rank can run at most one
-            // down projection ahead of the slowest rank (its next norm waits for everybody's flags)
-            const size_t po = (size_t)(l & 1) * e->pg_bytes;
-            qw_batch_buf(b, 9, &e->epx, po);
-            bind_peers(po, true);
-        } else qw_batch_buf(b, 9, &e->Pg, 0);
-        qw_batch_bytes(b, 10, &ebase, 4);
-        qw_batch_dispatch(b, D / 64, nb * e->TOPK + 1, 1, 256, 1, 1);
         if (e->c.ep_size > 1 && !e->ep_fused) {
             // every (token, rank) row has exactly one non-zero contributor (a routed expert's owner, or rank 0 for
             // the shared expert), so the sum reproduces the one-GPU rows bit for bit
@@ -835,7 +871,15 @@ int32_t sample_candidates(const int32_t *id, const float *lg, int avail, const q
 }
 }  // namespace
 
-extern "C" int32_t qw_engine_sample(const float *lg, int vocab, const qw_sample_params *g, unsigned long long *rng) {
+static int g_sample_vocab = 0;  // the reference compiles its vocabulary size in; here: the engine opened last, or set explicitly
+extern "C" void qw_engine_sample_set_vocab(int vocab) { g_sample_vocab = vocab > 0 ? vocab : 0; }
+extern "C" int32_t qw_engine_sample(const float *lg, const qw_gen *g, unsigned long long *rng) {
+    if (!g || g_sample_vocab < 1) return -1;
+    const qw_sample_params sp = {g->temperature, g->top_k, g->top_p};
+    return qw_engine_sample_v(lg, g_sample_vocab, &sp, rng);
+}
+
+extern "C" int32_t qw_engine_sample_v(const float *lg, int vocab, const qw_sample_params *g, unsigned long long *rng) {
     if (!lg || vocab < 1 || !g || !rng) return -1;
     // the top candidates of the whole row in the reference's order: insertion into a list kept sorted by value, an equal
     // value goes behind the ones already there (they have lower ids)
@@ -915,6 +959,12 @@ extern "C" const float *qw_engine_par_prefill(qw_engine *e, int sid, const int32
         } else lg = qw_engine_par_step(e, &sid, &prompt[i], 1, nullptr);
     }
     return lg;
+}
+
+extern "C" int qw_engine_set_moe_probe(qw_engine *e, int on) {
+    if (!e || !e->k_ffn_probe) return -1;
+    e->moe_probe = on != 0;
+    return 0;
 }
 
 extern "C" double qw_engine_par_cost(qw_engine *e, int B) { return e && B >= 1 && B <= QW_PAR_MAX ? e->cost[B] : 0; }
@@ -1020,7 +1070,7 @@ extern "C" int qw_engine_ep_connect(qw_engine *e, const void *handles, int n) {
     }
     std::vector<std::pair<const char *, long>> md = {{"E", e->E}, {"EL", e->EL}, {"D", (long)e->D}, {"I", e->I}, {"TOPK", e->TOPK},
                                                       {"SHARED", e->c.ep_rank == 0 ? 1 : 0}, {"RESID", 0}, {"EPX", n}};
-    if (!compile(e, "moe_dn", "moe_dn_epx", md, &e->k_dn_x) ||
+    if ((e->ffn_fused && !compile(e, "moe_ffn", "moe_ffn_epx", md, &e->k_ffn_x)) || !compile(e, "moe_dn", "moe_dn_epx", md, &e->k_dn_x) ||
         !compile(e, "add_rmsnorm", "cmb_add_rmsnorm_epx", {{"CMB", 1}, {"TOPK", e->TOPK}, {"EPX", n}}, &e->k_norm_cmb_x))
         return -1;
     if (!qw_buf_zero(e->g, &e->rcnt, 64, 8)) return -1;

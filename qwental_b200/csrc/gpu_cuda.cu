@@ -33,7 +33,11 @@ bool qw_pdl_enabled() {
     return true;
 }
 void qw_set_pdl(bool on) { g_pdl = on ? 1 : 0; }
-extern "C" void qw_gpu_set_pdl(qw_gpu *, bool on) { qw_set_pdl(on); }
+static void graph_cache_clear(qw_gpu *g);
+extern "C" void qw_gpu_set_pdl(qw_gpu *g, bool on) {
+    if (g) graph_cache_clear(g);  // recorded graphs carry the launch attributes of the mode they were captured in
+    qw_set_pdl(on);
+}
 
 // ------------------------------------------------------------------------------------------------ registry
 static QwFamily *g_families = nullptr;
@@ -96,8 +100,14 @@ struct qw_gpu {
     std::string err;
     unsigned long long launches;
     bool graphs;
-    std::unordered_map<uint64_t, cudaGraphExec_t> graph_cache;
-    std::unordered_map<uint64_t, unsigned> graph_nodes;
+    // CUDA graphs of recorded batches, keyed by a hash of everything a replay depends on (kernel, its specialisation, grid,
+    // threadgroup memory, bound addresses, inline bytes, stream, dependent-launch mode); the key bytes are kept and compared
+    // on a hit.  Cleared whenever a kernel is re-specialised or the launch mode changes; capped in size.
+    struct GraphEnt {
+        cudaGraphExec_t exec;
+        std::vector<uint8_t> key;
+    };
+    std::unordered_map<uint64_t, GraphEnt> graph_cache;
     void *tables;
     unsigned *status_host, *status_dev;
 };
@@ -114,6 +124,11 @@ struct qw_batch {
     std::vector<cudaEvent_t> pev;  // profiling: 2 per dispatch
     bool submitted, failed;
 };
+
+static void graph_cache_clear(qw_gpu *g) {
+    for (auto &kv : g->graph_cache) cudaGraphExecDestroy(kv.second.exec);
+    g->graph_cache.clear();
+}
 
 static void set_err(qw_gpu *g, const char *what, cudaError_t e) {
     char buf[512];
@@ -168,7 +183,7 @@ extern "C" void qw_gpu_close(qw_gpu *g) {
     if (!g) return;
     cudaSetDevice(g->dev);
     cudaDeviceSynchronize();
-    for (auto &kv : g->graph_cache) cudaGraphExecDestroy(kv.second);
+    graph_cache_clear(g);
     for (auto &kv : g->kernels) delete kv.second;
     if (g->tables) cudaFree(g->tables);
     if (g->status_host) cudaFreeHost(g->status_host);
@@ -288,10 +303,12 @@ extern "C" bool qw_gpu_compile(qw_gpu *g, const char *src, size_t len, char *err
     k->defs = defs;
     auto it = g->kernels.find(entry);
     if (it != g->kernels.end()) {
-        // Replace in place: handles already given out keep working and see the new specialisation.
+        // Replace in place: handles already given out keep working and see the new specialisation; graphs recorded with
+        // the old one must not be replayed.
         it->second->fam = f;
         it->second->defs = defs;
         delete k;
+        graph_cache_clear(g);
     } else g->kernels[entry] = k;
     if (err && errlen) err[0] = 0;
     return true;
@@ -569,19 +586,37 @@ extern "C" void qw_batch_submit(qw_batch *b) {
     }
     cudaEventRecord(b->e0, b->stream);
     if (g->graphs && !g->profile && b->recs.size() > 1) {
-        uint64_t h = 0xcbf29ce484222325ull;
+        std::vector<uint8_t> key;
+        key.reserve(b->recs.size() * 320);
+        auto put = [&](const void *p, size_t n) { key.insert(key.end(), (const uint8_t *)p, (const uint8_t *)p + n); };
         for (const Rec &r : b->recs) {
-            h = hash_bytes(h, &r.k, sizeof r.k);
-            h = hash_bytes(h, &r.gx, 6 * sizeof(unsigned));
-            for (int i = 0; i < 32; i++) {
-                h = hash_bytes(h, &r.b[i].ptr, sizeof(void *));
-                h = hash_bytes(h, &r.b[i].blen, 4);
-                if (r.b[i].blen) h = hash_bytes(h, b->arena.data() + r.b[i].boff, r.b[i].blen);
+            put(&r.k, sizeof r.k);
+            put(&r.k->fam, sizeof r.k->fam);
+            for (auto &kv : r.k->defs.v) {
+                put(kv.first.data(), kv.first.size());
+                put(&kv.second, sizeof kv.second);
             }
+            put(&r.gx, 6 * sizeof(unsigned));
+            put(&r.tgmem, sizeof r.tgmem);
+            for (int i = 0; i < 32; i++) {
+                put(&r.b[i].ptr, sizeof(void *));
+                put(&r.b[i].blen, 4);
+                if (r.b[i].blen) put(b->arena.data() + r.b[i].boff, r.b[i].blen);
+            }
+            qw_pdl_current_family(r.k->fam->name);
+            const uint8_t pdl = qw_pdl_enabled() ? 1 : 0;
+            put(&pdl, 1);
         }
-        h = hash_bytes(h, &b->stream, sizeof b->stream);
+        put(&b->stream, sizeof b->stream);
+        const uint64_t h = hash_bytes(0xcbf29ce484222325ull, key.data(), key.size());
         auto it = g->graph_cache.find(h);
+        if (it != g->graph_cache.end() && it->second.key != key) {  // a hash collision: the stored graph is another batch's
+            cudaGraphExecDestroy(it->second.exec);
+            g->graph_cache.erase(it);
+            it = g->graph_cache.end();
+        }
         if (it == g->graph_cache.end()) {
+            if (g->graph_cache.size() >= 256) graph_cache_clear(g);  // e.g. one entry per (rows, chunk count) a long run went through
             cudaGraph_t graph = nullptr;
             cudaGraphExec_t exec = nullptr;
             cudaError_t e = cudaStreamBeginCapture(b->stream, cudaStreamCaptureModeThreadLocal);
@@ -603,11 +638,9 @@ extern "C" void qw_batch_submit(qw_batch *b) {
                 b->failed = true;
                 return;
             }
-            g->graph_cache[h] = exec;
-            g->graph_nodes[h] = (unsigned)b->recs.size();
-            it = g->graph_cache.find(h);
+            it = g->graph_cache.emplace(h, qw_gpu::GraphEnt{exec, std::move(key)}).first;
         }
-        cudaError_t e = cudaGraphLaunch(it->second, b->stream);
+        cudaError_t e = cudaGraphLaunch(it->second.exec, b->stream);
         if (e != cudaSuccess) {
             set_err(g, "graph launch", e);
             b->failed = true;

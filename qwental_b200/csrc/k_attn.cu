@@ -451,7 +451,9 @@ __global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __h
     __shared__ float2 accs[8][HD / 2];
     pdl_sync();
     const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, d = tid & 255, d2 = tid & 127, grp = tid >> 7, lane = tid & 31, warp = tid >> 5;
-    const uint32_t ntok = (uint32_t)posv[t] + 1, nch = (ntok + QSA_PAGE - 1) / QSA_PAGE;
+    // the core wrote max_chunks partials per slot at most: a position beyond that (only a caller that passes its own device
+    // positions can produce one) must not make the merge read another slot's partials or run off the buffer
+    const uint32_t ntok = (uint32_t)posv[t] + 1, nch = min((ntok + QSA_PAGE - 1) / QSA_PAGE, min(a.max_chunks, (uint32_t)QSA_MAXCH));
     const float *base = part + ((size_t)t * a.max_chunks * QH + qh) * (HD + 2);
     const size_t cstride = (size_t)QH * (HD + 2);
     float mx = -INFINITY;
@@ -522,6 +524,8 @@ QW_FAMILY(qsa_merge, launch_qsa_merge, 256)
 //             8192 tokens, or 2 slots of 65536); QH = 16, KVH = 2, HD = 256 only.  Larger requests are rejected.
 //   set-up    the first call on a device resolves the array's device address (cudaGetSymbolAddress, with that
 //             device current) and remembers it; make that first call outside any stream capture.
+//   contract  pos[t] + 1 <= max_chunks * 256 for every row: the core covers max_chunks pages per slot and the merge never
+//             looks past them (a longer position is cut to the first max_chunks pages, not read out of bounds).
 //   contents  nothing has to start at zero: the core writes every partial (accumulator, max, sum) that the merge
 //             of the same call reads, so what an earlier call left behind is never looked at.
 //   sharing   all calls on a device use the same array: two calls whose kernels overlap on the GPU (different

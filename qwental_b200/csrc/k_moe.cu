@@ -410,14 +410,16 @@ constexpr int MOE_TAB_BYTES = 512 * 16 * 8;
 constexpr int MOE_RED_BYTES = 2 * 2 * 16 * 32 * 16;  // gate/up: per team two buffers (alternating by unit) of 16 x 32 float4
 constexpr int MOE_DN_ROWS = 128;                       // rows of a down-projection tile: 16 per consumer warp
 
-__device__ __forceinline__ void team_sync(int team) { asm volatile("bar.sync %0, 256;" ::"r"(team + 1) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
-    return v;
+// Barrier among the 8 warps of a team, built on an mbarrier (one arrival per warp) so that the wait is bounded like every other
+// wait of these kernels: a warp that gave up elsewhere and left cannot strand its team in a hardware barrier.  ph counts
+// the team's barriers so far (its parity selects the phase).  False after about two seconds without the others.
+__device__ __forceinline__ bool team_sync(uint64_t *bar, uint32_t &ph, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+    const bool ok = mbar_wait(bar, ph & 1);
+    ph++;
+    __syncwarp();
+    return ok;
 }
 
 // Work units = (group, pass of 8 token columns, row tile), enumerated group-major, then pass, then tile, so that a team's
@@ -490,10 +492,13 @@ __global__ void __launch_bounds__(512, 1) moe_gu_k(const MoeP p) {
     const bool active = ks < KS;
     // independent of earlier kernels: barriers and the codebook table (thread 0 both initialises and uses the table's
     // barrier here; the other threads see the initialised barriers after the __syncthreads in moe_sched)
-    uint64_t *tab_bar = bars + 2 * MOE_STG;
+    uint64_t *tab_bar = bars + 2 * MOE_STG, *team_bar = tab_bar + 1 + team;
+    uint32_t team_ph = 0;
     pdl_launch();
     if (tid == 0) {
         for (int s = 0; s < 2 * MOE_STG + 1; s++) mbar_init(&bars[s], 1);
+        mbar_init(tab_bar + 1, 8);
+        mbar_init(tab_bar + 2, 8);
         mbar_init_fence();
         mbar_expect_tx(tab_bar, MOE_TAB_BYTES);
         bulk_g2s(tab, p.tab->grid_h4, MOE_TAB_BYTES, tab_bar);
@@ -568,7 +573,10 @@ __global__ void __launch_bounds__(512, 1) moe_gu_k(const MoeP p) {
         }
         red[(warp * 2 + 0) * 32 + lane] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
         red[(warp * 2 + 1) * 32 + lane] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
-        team_sync(team);
+        if (!team_sync(team_bar, team_ph, lane)) {
+            ok = false;
+            break;
+        }
         if (tt < 128) {
             const int jj = tt & 3, ln = tt >> 2;
             float gs = 0.f, us = 0.f;
@@ -616,7 +624,8 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
     uint8_t *hs = smem + 128 + MOE_TAB_BYTES + (size_t)team * hs_bytes;
     const uint32_t tile_bytes = MOE_DN_ROWS * rb, stage_stride = (tile_bytes + 127) & ~127u;
     uint8_t *stage0 = smem + 128 + MOE_TAB_BYTES + 2 * hs_bytes + (size_t)team * MOE_STG * stage_stride;
-    uint64_t *full = bars + team * MOE_STG, *empty = bars + 2 * MOE_STG + team * MOE_STG, *tab_bar = bars + 4 * MOE_STG;
+    uint64_t *full = bars + team * MOE_STG, *empty = bars + 2 * MOE_STG + team * MOE_STG, *tab_bar = bars + 4 * MOE_STG, *team_bar = tab_bar + 1 + team;
+    uint32_t team_ph = 0;
     pdl_launch();
     if (tid == 0) {
         for (int s = 0; s < 2 * MOE_STG; s++) {
@@ -624,6 +633,8 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
             mbar_init(&bars[2 * MOE_STG + s], 8);  // one arrival per consumer warp
         }
         mbar_init(tab_bar, 1);
+        mbar_init(tab_bar + 1, 8);
+        mbar_init(tab_bar + 2, 8);
         mbar_init_fence();
         mbar_expect_tx(tab_bar, MOE_TAB_BYTES);
         bulk_g2s(tab, p.tab->grid_b4, MOE_TAB_BYTES, tab_bar);
@@ -676,7 +687,10 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
             if (u != cur_u || c0 != cur_c0) {  // new (group, pass): uniform over the team's consumers
                 cur_u = u;
                 cur_c0 = c0;
-                team_sync(team);  // every consumer warp is done with the previous pass's H rows
+                if (!team_sync(team_bar, team_ph, lane)) {  // every consumer warp is done with the previous pass's H rows
+                    ok = false;
+                    break;
+                }
                 const uint32_t i8 = p.I / 8;  // 16-byte pieces per row
                 for (uint32_t idx = tt; idx < 16 * i8; idx += 256) {
                     const uint32_t pc = idx / i8, kk = idx - pc * i8, col = pc & 7;
@@ -689,7 +703,10 @@ __global__ void __launch_bounds__(MOE_DN_THREADS, 1) moe_dn_k(const MoeP p) {
                 uint32_t tok = 0, rank = 0;
                 oo[0] = moe_entry(ms, u, U, e0, c0, cnt, topk, 2 * t, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
                 oo[1] = moe_entry(ms, u, U, e0, c0, cnt, topk, 2 * t + 1, tok, rank) ? (tok * (topk + 1) + rank) * p.D : 0xffffffffu;
-                team_sync(team);
+                if (!team_sync(team_bar, team_ph, lane)) {
+                    ok = false;
+                    break;
+                }
             }
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t r0 = smem_u32(stage0) + s * stage_stride + (16 * warp + 2 * g) * rb;

@@ -151,6 +151,12 @@ __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
     return v;
 }
 
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
 struct Iq3sHdr {
     float d, d2;        // block scale and twice it: sub-block scale = d + d2 * s
     uint32_t qa0, qa1;  // bytes = this thread's codebook high bit for word 0 of sub-blocks 0..3 / 4..7 (0 or 1)
@@ -220,6 +226,26 @@ __device__ __forceinline__ void sub_mma1(uint32_t u0, uint32_t u1, int t, const 
         mma_f16(p, a0, xv.x, xv.y, zr.z);
         mma_f16(p, a1, xv.z, xv.w, p);
     }
+    acc[0] = fmaf(dba, p[0], acc[0]);
+    acc[1] = fmaf(dba, p[1], acc[1]);
+    acc[2] = fmaf(dbb, p[2], acc[2]);
+    acc[3] = fmaf(dbb, p[3], acc[3]);
+}
+
+// The same sub-block against an activation kept as two fp16 planes (value = high + low): four MMAs on one accumulator.
+template <int IB, int TS>
+__device__ __forceinline__ void sub_mma1_h2(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr,
+                                            const uint4 &xv, const uint4 &xl, float (&acc)[4]) {
+    uint32_t wa[4], wb[4];
+    const float dba = iq3s_sub_h<IB, TS>(u0 + 2 * t, u0 + t, h0, tabc, wa);
+    const float dbb = iq3s_sub_h<IB, TS>(u1 + 2 * t, u1 + t, h1, tabc, wb);
+    const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+    const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+    float p[4];
+    mma_f16(p, a0, xv.x, xv.y, zr.z);
+    mma_f16(p, a1, xv.z, xv.w, p);
+    mma_f16(p, a0, xl.x, xl.y, p);
+    mma_f16(p, a1, xl.z, xl.w, p);
     acc[0] = fmaf(dba, p[0], acc[0]);
     acc[1] = fmaf(dba, p[1], acc[1]);
     acc[2] = fmaf(dbb, p[2], acc[2]);

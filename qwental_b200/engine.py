@@ -38,7 +38,8 @@ def _bind(L):
         "qw_engine_tap": (C.c_size_t, [vp, C.c_char_p, C.c_int, vp, C.c_size_t]),
         "qw_ep_unique_id": (C.c_int, [vp]), "qw_engine_ep_init": (C.c_int, [vp, vp]),
         "qw_engine_par_prefill": (C.c_void_p, [vp, C.c_int, vp, C.c_int, vp]),
-        "qw_engine_sample": (C.c_int32, [vp, C.c_int, vp, vp]),
+        "qw_engine_sample_v": (C.c_int32, [vp, C.c_int, vp, vp]), "qw_engine_sample": (C.c_int32, [vp, vp, vp]),
+        "qw_engine_sample_set_vocab": (None, [C.c_int]), "qw_engine_set_moe_probe": (C.c_int, [vp, C.c_int]),
         "qw_engine_par_step_sample": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, vp, vp]),
         "qw_engine_ep_export": (C.c_int, [vp, vp]), "qw_engine_ep_connect": (C.c_int, [vp, vp, C.c_int]),
     }
@@ -69,13 +70,13 @@ SAMPLE_DT = np.dtype([("temperature", np.float32), ("top_k", np.int32), ("top_p"
 
 
 def sample(logits: np.ndarray, temperature: float, top_k: int, top_p: float, rng: np.ndarray) -> int:
-    """qw_engine_sample through the C ABI (host only: works without a GPU); rng = uint64 array of one element."""
+    """qw_engine_sample_v through the C ABI (host only: works without a GPU); rng = uint64 array of one element."""
     L = _lib.load()
     _bind(L)
     lg = np.ascontiguousarray(logits, np.float32)
     g = np.zeros(1, SAMPLE_DT)
     g[0] = (temperature, top_k, top_p)
-    return int(L.qw_engine_sample(lg.ctypes.data, lg.size, g.ctypes.data, rng.ctypes.data))
+    return int(L.qw_engine_sample_v(lg.ctypes.data, lg.size, g.ctypes.data, rng.ctypes.data))
 
 
 def wide_cfg(**over) -> ModelCfg:

@@ -43,8 +43,12 @@ class MoeLayer:
     """Router + top-k/grouping + gathered expert FFN + shared expert + combine for up to 64 tokens."""
 
     def __init__(self, gpu: Gpu, E: int, D: int, I: int, topk: int, Wr: Buf, Wsg: Buf, Wg: Buf, Wu: Buf, Wd: Buf,
-                 Sg: Buf | None, Su: Buf | None, Sd: Buf | None, e_lo: int = 0, e_hi: int | None = None):
+                 Sg: Buf | None, Su: Buf | None, Sd: Buf | None, e_lo: int = 0, e_hi: int | None = None, ffn: str = "auto"):
         self.gpu, self.E, self.D, self.I, self.topk = gpu, E, D, I, topk
+        # expert FFN: "fused" = gate/up + down in one launch (moe_ffn; D a multiple of 2048, I = 512), "split" = moe_gu then
+        # moe_dn; "auto" takes the fused kernel where its shapes allow, as the engine does
+        assert ffn in ("auto", "fused", "split")
+        self.fused_ffn = ffn == "fused" or (ffn == "auto" and D % 2048 == 0 and I == 512)
         self.Wr, self.Wsg, self.Wg, self.Wu, self.Wd, self.Sg, self.Su, self.Sd = Wr, Wsg, Wg, Wu, Wd, Sg, Su, Sd
         self.e_lo, self.e_hi = e_lo, E if e_hi is None else e_hi
         tag = "_e%d_d%d_i%d_k%d" % (E, D, I, topk)
@@ -56,6 +60,7 @@ class MoeLayer:
         self.route_cnt = gpu.buf(256).zero()
         self.k_gu = gpu.compile("moe_gu", "moe_gu" + tag, **d)
         self.k_dn = gpu.compile("moe_dn", "moe_dn" + tag, **d)
+        self.k_ffn = gpu.compile("moe_ffn", "moe_ffn" + tag, **d) if self.fused_ffn else None
         self.k_cmb = gpu.compile("moe_cmb", "moe_cmb" + tag, RESID=0, **d)
         self.k_cmb_res = gpu.compile("moe_cmb", "moe_cmb_res" + tag, RESID=1, **d)
         self.logits = gpu.buf(MOE_MAXB * (E + 1) * 4)
@@ -77,14 +82,20 @@ class MoeLayer:
 
     def _encode_ffn(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None):
         D, I = self.D, self.I
-        b.kernel(self.k_gu).buf(0, self.Wg).buf(1, self.Wu)
-        if self.Sg is not None:
-            b.buf(2, self.Sg).buf(3, self.Su)
-        b.buf(4, x).buf(5, self.sel).buf(6, self.Hhi).buf(7, self.Hlo).dispatch((I // 16, nb * self.topk + 1), (256,))
-        b.kernel(self.k_dn).buf(0, self.Wd)
-        if self.Sd is not None:
-            b.buf(2, self.Sd)
-        b.buf(5, self.sel).buf(6, self.Hhi).buf(7, self.Hlo).buf(9, self.Pg).dispatch((D // 64, nb * self.topk + 1), (256,))
+        if self.fused_ffn:
+            b.kernel(self.k_ffn).buf(0, self.Wg).buf(1, self.Wu)
+            if self.Sg is not None:
+                b.buf(2, self.Sg).buf(3, self.Su).buf(7, self.Sd)
+            b.buf(4, x).buf(5, self.sel).buf(6, self.Wd).buf(9, self.Pg).dispatch((I // 16, nb * self.topk + 1), (256,))
+        else:
+            b.kernel(self.k_gu).buf(0, self.Wg).buf(1, self.Wu)
+            if self.Sg is not None:
+                b.buf(2, self.Sg).buf(3, self.Su)
+            b.buf(4, x).buf(5, self.sel).buf(6, self.Hhi).buf(7, self.Hlo).dispatch((I // 16, nb * self.topk + 1), (256,))
+            b.kernel(self.k_dn).buf(0, self.Wd)
+            if self.Sd is not None:
+                b.buf(2, self.Sd)
+            b.buf(5, self.sel).buf(6, self.Hhi).buf(7, self.Hlo).buf(9, self.Pg).dispatch((D // 64, nb * self.topk + 1), (256,))
         b.kernel(self.k_cmb if resid is None else self.k_cmb_res).buf(3, self.sel).buf(4, out).buf(9, self.Pg).bytes(8, u32(nb))
         if resid is not None:
             b.buf(5, resid)

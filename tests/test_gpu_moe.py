@@ -21,7 +21,7 @@ def gpu():
     g.close()
 
 
-def make_layer(gpu, E, D, I, topk, seed, shared=True, e_lo=0, e_hi=None):
+def make_layer(gpu, E, D, I, topk, seed, shared=True, e_lo=0, e_hi=None, ffn="auto"):
     from qwental_b200.layers import MoeLayer
     rng = np.random.default_rng(seed)
     h = {}
@@ -38,7 +38,7 @@ def make_layer(gpu, E, D, I, topk, seed, shared=True, e_lo=0, e_hi=None):
     h["sd"] = synth.iq3s_rows(rng, D, I, sI)
     b = {k: gpu.buf_from(v) for k, v in h.items()}
     layer = MoeLayer(gpu, E, D, I, topk, b["Wr"], b["wsg"], b["gate"], b["up"], b["down"],
-                     b["sg"] if shared else None, b["su"] if shared else None, b["sd"] if shared else None, e_lo, e_hi)
+                     b["sg"] if shared else None, b["su"] if shared else None, b["sd"] if shared else None, e_lo, e_hi, ffn)
     return layer, h, b
 
 
@@ -51,10 +51,13 @@ def run_layer(gpu, layer, x, fused_route=False):
     return ob.download(np.float16, nb * layer.D).reshape(nb, layer.D)
 
 
+@pytest.mark.parametrize("ffn", ["fused", "split"])
 @pytest.mark.parametrize("E,B", [(64, 16), (64, 1), (64, 64), (512, 16)])
-def test_moe_layer_parity(gpu, E, B):
+def test_moe_layer_parity(gpu, E, B, ffn):
+    """ffn = "fused": gate/up + down in one launch with H in shared memory (what the engine runs at these shapes);
+    "split": the two-launch family that serves every other shape."""
     D, I, topk = 2048, 512, 10
-    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=10 + E)
+    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=10 + E, ffn=ffn)
     x = synth.acts_fp16(np.random.default_rng(B), B, D)
     out = run_layer(gpu, layer, x)
 
@@ -86,9 +89,10 @@ def test_moe_layer_parity(gpu, E, B):
             assert set(ids64[t]) == set(ids[t])
 
 
-def test_moe_batched_equals_alone(gpu):
+@pytest.mark.parametrize("ffn", ["fused", "split"])
+def test_moe_batched_equals_alone(gpu, ffn):
     D, I, topk, E, B = 2048, 512, 10, 64, 24
-    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=3)
+    layer, h, _ = make_layer(gpu, E, D, I, topk, seed=3, ffn=ffn)
     x = synth.acts_fp16(np.random.default_rng(9), B, D)
     out = run_layer(gpu, layer, x)
     for t in (0, 7, 23):
@@ -100,11 +104,12 @@ def test_moe_batched_equals_alone(gpu):
     assert all(np.array_equal(outs[i].view(np.uint16), out[0].view(np.uint16)) for i in range(20))
 
 
-def test_moe_expert_range_partitions_the_work(gpu):
+@pytest.mark.parametrize("ffn", ["fused", "split"])
+def test_moe_expert_range_partitions_the_work(gpu, ffn):
     """Expert-parallel building block: with experts restricted to [lo, hi) each part writes only its own
     (token, rank) rows; the union over a partition equals the full layer's rows bit for bit."""
     D, I, topk, E, B = 2048, 512, 10, 64, 16
-    full, h, b = make_layer(gpu, E, D, I, topk, seed=5)
+    full, h, b = make_layer(gpu, E, D, I, topk, seed=5, ffn=ffn)
     x = synth.acts_fp16(np.random.default_rng(2), B, D)
     run_layer(gpu, full, x)
     pg_full = full.Pg.download(np.float32, B * (topk + 1) * D).reshape(B, topk + 1, D)
@@ -112,7 +117,7 @@ def test_moe_expert_range_partitions_the_work(gpu):
     from qwental_b200.layers import MoeLayer
     acc = np.zeros_like(pg_full)
     for lo, hi in ((0, 32), (32, 64)):
-        part = MoeLayer(gpu, E, D, I, topk, b["Wr"], b["wsg"], b["gate"], b["up"], b["down"], b["sg"], b["su"], b["sd"], lo, hi)
+        part = MoeLayer(gpu, E, D, I, topk, b["Wr"], b["wsg"], b["gate"], b["up"], b["down"], b["sg"], b["su"], b["sd"], lo, hi, ffn)
         run_layer(gpu, part, x)
         pg = part.Pg.download(np.float32, B * (topk + 1) * D).reshape(B, topk + 1, D)
         mine = (ids >= lo) & (ids < hi)

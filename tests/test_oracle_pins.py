@@ -101,3 +101,60 @@ def test_counter_fill_blocks_have_valid_fields():
     Q = synth.fill_quant_rows(99, 8, 4, 2048)
     q = Q.reshape(4, 64, 34)[:, :, 2:].view(np.int8)
     assert q.min() >= -127
+
+
+# ---- the floating-point layer references against the reference's own CPU checks
+def _layer_cases():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("gen_layer_golden", os.path.join(os.path.dirname(__file__), "golden", "gen_layer_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _numpy_layer_outputs(d):
+    g, a, m = d["gdn"], d["attn"], d["moe"]
+    S1, o1 = orc.gdn_core_ref(g["S"], g["qn"].astype(np.float64), g["kn"].astype(np.float64), g["v"].astype(np.float64), g["la"], g["beta"], g["hk_of"])
+    out, ids, _ = orc.moe_ref(m["x"], m["Wr"], m["wsg"], m["gate"], m["up"], m["down"], m["sg"], m["su"], m["sd"], m["D"], m["I"], m["T"], ref_arith=True)
+    return dict(gdn_o=o1, gdn_S_sample=S1.reshape(-1)[::97], attn_o=orc.attn_core_ref(a["q"], a["K"], a["V"]), moe_ids=ids, moe_out=out)
+
+
+def _close(got, want, tol=1e-12):
+    return np.abs(np.asarray(got, np.float64) - want).max() <= tol * np.abs(want).max()
+
+
+def test_fp_layer_references_match_reference_golden_vectors():
+    """gdn_core_ref, attn_core_ref and moe_ref (the references every GPU parity test compares against) reproduce, to 1e-12
+    relative, what the reference's own CPU checks computed on the same seeded inputs (tests/golden/layer_ref_golden.npz,
+    written by tests/golden/gen_layer_golden.py from bench/gdn_decode.c:74-84, bench/qsa.c:184-201,
+    bench/moe_decode.c:133-177)."""
+    want = np.load(os.path.join(os.path.dirname(__file__), "golden", "layer_ref_golden.npz"))
+    got = _numpy_layer_outputs(_layer_cases().layer_inputs())
+    assert np.array_equal(got["moe_ids"], want["moe_ids"])
+    for k in ("gdn_o", "gdn_S_sample", "attn_o", "moe_out"):
+        assert _close(got[k], want[k]), k
+
+
+@pytest.mark.skipif(not os.path.exists(orc.REF_LAYERS), reason="oracle/_ref/liblayer_ref.so not built (reference tree absent)")
+def test_fp_layer_references_match_live_reference_code():
+    mod = _layer_cases()
+    d = mod.layer_inputs()
+    want, got = mod.reference_outputs(d), _numpy_layer_outputs(d)
+    assert np.array_equal(got["moe_ids"], want["moe_ids"])
+    for k in ("gdn_o", "gdn_S_sample", "attn_o", "moe_out"):
+        assert _close(got[k], want[k]), k
+    # other shapes than the committed ones: the benchmark's 32 / 16 heads, a longer context
+    rng = np.random.default_rng(77)
+    HV, HK, DK, DV = 32, 16, 128, 128
+    q, k = rng.standard_normal((HK, DK)), rng.standard_normal((HK, DK))
+    qn = (q / np.linalg.norm(q, axis=1, keepdims=True) / np.sqrt(DK)).astype(np.float16)
+    kn = (k / np.linalg.norm(k, axis=1, keepdims=True)).astype(np.float16)
+    S = (rng.standard_normal((HV, DK, DV)) * 0.1).astype(np.float32).astype(np.float64)
+    v = rng.standard_normal((HV, DV)).astype(np.float16)
+    la, be = np.log(0.9 + 0.1 * rng.random(HV)).astype(np.float32), (0.1 + 0.8 * rng.random(HV)).astype(np.float32)
+    S1, o1 = orc.ref_gdn_core(S, qn, kn, v, la, be)
+    S2, o2 = orc.gdn_core_ref(S, qn.astype(np.float64), kn.astype(np.float64), v.astype(np.float64), la, be, np.arange(HV) // (HV // HK))
+    assert _close(S2, S1) and _close(o2, o1)
+    L = 2500
+    qq, K, V = (rng.standard_normal(s).astype(np.float16) for s in ((16, 256), (L, 2, 256), (L, 2, 256)))
+    assert _close(orc.attn_core_ref(qq, K, V), orc.ref_attn_core(qq, K, V))

@@ -62,6 +62,16 @@ def test_host_sampler_matches_the_reference_code():
                 want = ref.qw_engine_sample(lg.ctypes.data, C.byref(g), C.byref(theirs))
                 got = sample(lg, T, k, p, mine)
                 assert got == want and int(mine[0]) == theirs.value, (V, T, k, p)
+            # the entry point with the reference's own signature, given the very same qw_gen bytes
+            from qwental_b200 import lib
+            L = lib.load()
+            L.qw_engine_sample.restype = C.c_int32
+            L.qw_engine_sample.argtypes = [C.c_void_p, C.POINTER(QwGen), C.POINTER(C.c_ulonglong)]
+            L.qw_engine_sample_set_vocab(V)
+            a, b = C.c_ulonglong(12345), C.c_ulonglong(12345)
+            for _ in range(3):
+                assert L.qw_engine_sample(lg.ctypes.data, C.byref(g), C.byref(a)) == ref.qw_engine_sample(lg.ctypes.data, C.byref(g), C.byref(b))
+                assert a.value == b.value
 
 
 def test_host_sampler_matches_reference_golden_vectors():
@@ -136,3 +146,32 @@ def test_sampled_step_equals_sampler_on_full_logits():
     finally:
         eng.close()
         gpu.close()
+
+
+def test_reference_signature_entry_point_equals_the_explicit_one():
+    """qw_engine_sample(logits, const qw_gen *, rng) -- the reference's signature (src/engine.h:125) -- reads the first
+    three fields of qw_gen and the vocabulary set for the process; it must draw what qw_engine_sample_v draws."""
+    import ctypes as C
+    from qwental_b200 import lib
+    from qwental_b200.engine import sample
+
+    class QwGen(C.Structure):  # src/engine.h:39-52
+        _fields_ = [("temperature", C.c_float), ("top_k", C.c_int), ("top_p", C.c_float), ("seed", C.c_ulonglong), ("max_tokens", C.c_int),
+                    ("stop", C.c_void_p), ("nstop", C.c_int), ("spec", C.c_bool), ("persist", C.c_void_p), ("npersist", C.c_int),
+                    ("yield_", C.c_void_p), ("pf_yield", C.c_void_p)]
+    L = lib.load()
+    L.qw_engine_sample.restype = C.c_int32
+    L.qw_engine_sample.argtypes = [C.c_void_p, C.POINTER(QwGen), C.POINTER(C.c_ulonglong)]
+    rng = np.random.default_rng(11)
+    V = 4096
+    lg = _logits(rng, V)
+    L.qw_engine_sample_set_vocab(0)
+    assert L.qw_engine_sample(lg.ctypes.data, C.byref(QwGen(temperature=1.0)), C.byref(C.c_ulonglong(1))) == -1  # no vocabulary known yet
+    L.qw_engine_sample_set_vocab(V)
+    for T, k, p in CASES:
+        st = np.array([rng.integers(0, 2**63)], np.uint64)
+        theirs = C.c_ulonglong(int(st[0]))
+        g = QwGen(temperature=T, top_k=k, top_p=p, seed=99, max_tokens=7)
+        for _ in range(4):
+            assert L.qw_engine_sample(lg.ctypes.data, C.byref(g), C.byref(theirs)) == sample(lg, T, k, p, st)
+            assert theirs.value == int(st[0])
