@@ -231,6 +231,51 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------------------- GPU arm
+CHAIN_FIXTURE = os.path.join(ROOT, "tests", "golden", "greedy_chain_16slots.npz")
+CHAIN_STEPS = 64  # steps of the seeded greedy chain kept in the fixture
+
+
+def place_contexts(ctx, world):
+    """Placement as a scheduler would do it when slot s is served by rank s mod N: the same conversations, each put into a free
+    slot of the rank that holds the fewest context tokens so far (longest first).  With one rank nothing changes."""
+    if world <= 1:
+        return ctx
+    B = len(ctx)
+    placed, load, free = np.zeros(B, ctx.dtype), np.zeros(world), [list(range(r, B, world)) for r in range(world)]
+    for c in sorted(ctx.tolist(), reverse=True):
+        r = min((q for q in range(world) if free[q]), key=lambda q: load[q])
+        placed[free[r].pop(0)] = c
+        load[r] += c
+    return placed
+
+
+def profile_step(gpu, eng, sids, cur):
+    """One step with CUDA events around every dispatch (graphs off): {kernel name: [durations in us]}."""
+    import ctypes as C
+    gpu.L.qw_gpu_set_graphs(gpu.g, False)
+    gpu.L.qw_profile_enable(gpu.g, True)
+    nxt, _ = eng.step_greedy(sids, cur)
+    per = {}
+    for i in range(gpu.L.qw_profile_count(gpu.g)):
+        us = C.c_double()
+        nm = gpu.L.qw_profile_get(gpu.g, i, C.byref(us)).decode()
+        per.setdefault(nm, []).append(us.value)
+    gpu.L.qw_profile_enable(gpu.g, False)
+    return per, nxt
+
+
+def ncu_traffic_ratio():
+    """dram bytes / algorithmic bytes of one launch of the expert FFN kernel, from the tracked ncu summary (a line
+    'dram_bytes_per_launch: X  algorithmic_bytes_per_launch: Y'); None when no such capture is recorded."""
+    import re
+    try:
+        txt = open(os.path.join(ROOT, "profiles", "moe_ffn_16slots_ncu.md")).read()
+        m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)\s+algorithmic_bytes_per_launch:\s*([0-9.eE+]+)", txt)
+        return float(m.group(1)) / float(m.group(2)) if m else None
+    except Exception:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -243,6 +288,10 @@ def main():
     ap.add_argument("--graphs", type=int, default=1)
     ap.add_argument("--ep", default="fused", choices=["nccl", "fused"],
                     help="expert-parallel exchange at N > 1: one NCCL all-reduce per layer, or peer stores fused into the down projection")
+    ap.add_argument("--sustain", type=float, default=3.0, help="seconds of back-to-back chained steps for the sustained figure (0: skip)")
+    ap.add_argument("--slots-big", type=int, default=64, help="second leg at this many slots on 1 GPU (0: skip)")
+    ap.add_argument("--place-as", type=int, default=0, help="(1 GPU) lay the conversations out as the N-GPU run does: the chain then equals that run's")
+    ap.add_argument("--write-chain", default="", help="(1 GPU) record the first %d steps of the seeded greedy chain under this key of the fixture and exit" % CHAIN_STEPS)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -263,19 +312,16 @@ def main():
     from qwental_b200.gpu import Gpu
 
     B, K, W = args.slots, args.steps, max(3, args.warmup)
-    ctx = synth.ragged_contexts(np.random.default_rng(0), B)
-    if world > 1:
-        # Placement, as a scheduler would do it when slot s is served by rank s mod N: the same conversations, each put into
-        # a free slot of the rank that holds the fewest context tokens so far (longest first).  With one GPU nothing changes.
-        placed, load, free = np.zeros(B, ctx.dtype), np.zeros(world), [list(range(r, B, world)) for r in range(world)]
-        for c in sorted(ctx.tolist(), reverse=True):
-            r = min((q for q in range(world) if free[q]), key=lambda q: load[q])
-            placed[free[r].pop(0)] = c
-            load[r] += c
-        ctx = placed
-    nsteps_total = 3 * (K + W) + 8
-    pages = int(sum((int(n) + nsteps_total + 256) // 256 + 1 for n in ctx))
-    cfg = default_cfg(max_slots=B, max_ctx=int(ctx.max()) + nsteps_total + 512, kv_pages=pages, ep_rank=rank, ep_size=world, seed=0, layers=args.layers)
+    place = world if world > 1 else max(1, args.place_as)
+    ctx = place_contexts(synth.ragged_contexts(np.random.default_rng(0), B), place)
+    BB = args.slots_big if (world == 1 and args.slots_big > B and not args.write_chain) else 0
+    ctx_big = np.concatenate([ctx, synth.ragged_contexts(np.random.default_rng(1), BB)[B:]]) if BB else ctx
+    peak, peak_src = measured_peak_gbs()
+    est_ms = 8.0  # only to size the KV reservation of the sustained leg
+    sustain_steps = int(args.sustain * 1e3 / est_ms * 2) if args.sustain > 0 else 0
+    nsteps_total = 3 * (K + W) + 16 + sustain_steps + CHAIN_STEPS
+    pages = int(sum((int(n) + nsteps_total + 256) // 256 + 1 for n in ctx_big))
+    cfg = default_cfg(max_slots=max(B, BB), max_ctx=int(ctx_big.max()) + nsteps_total + 512, kv_pages=pages, ep_rank=rank, ep_size=world, seed=0, layers=args.layers)
     gpu = Gpu()
     eng = Engine(gpu, cfg)
     if world > 1:
@@ -300,8 +346,8 @@ def main():
             else:
                 args.ep = "nccl"
             dist.barrier()
-    for s in range(B):
-        eng.seed_slot(s, int(ctx[s]), 100 + s)
+    for s in range(len(ctx_big)):
+        eng.seed_slot(s, int(ctx_big[s]), 100 + s)
     gpu.L.qw_gpu_set_graphs(gpu.g, bool(args.graphs))
     sids = np.arange(B, dtype=np.int32)
     toks = (np.arange(B, dtype=np.int32) * 7919) % cfg.vocab
@@ -313,11 +359,24 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    if args.write_chain:  # fixture generation: the first CHAIN_STEPS steps of the chain every run below walks
+        ids, _ = eng.decode_greedy(sids, toks, CHAIN_STEPS)
+        old = dict(np.load(CHAIN_FIXTURE)) if os.path.exists(CHAIN_FIXTURE) else {}
+        old[args.write_chain] = ids.astype(np.int32)
+        np.savez_compressed(CHAIN_FIXTURE, **old)
+        print(json.dumps({"wrote": CHAIN_FIXTURE, "key": args.write_chain, "steps": CHAIN_STEPS, "layers": cfg.layers}))
+        eng.close()
+        gpu.close()
+        return
+
     # ---- warm-up (also builds the CUDA graphs of both step forms)
+    chain = []
     ids, _ = eng.decode_greedy(sids, toks, W)
+    chain.append(ids)
     cur = ids[-1]
     for _ in range(W):
         cur, _ = eng.step_greedy(sids, cur)
+        chain.append(cur[None])
 
     # ---- timed region 1: K chained steps, inputs resident in HBM (weights 35 GB + KV: far larger than L2)
     sampler = ClockSampler(local)
@@ -331,15 +390,14 @@ def main():
     sync_all()
     launches = gpu.launches() - l0
     dev_ms = e0.elapsed_time(e1)
+    chain.append(ids)
     cur = ids[-1]
     # ---- timed region 2: K steps through the public call, host ids in / host ids out each step
     sync_all()
     t0 = time.perf_counter()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record(stream)
     for _ in range(K):
         cur, _ = eng.step_greedy(sids, cur)
-    e3.record(stream)
+        chain.append(cur[None])
     sync_all()
     e2e_wall_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
@@ -348,32 +406,99 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         dev_ms, e2e_wall_ms = float(tt[0]), float(tt[1])
 
+    # ---- the chain so far against the committed single-GPU chain of the same seed and placement; all ranks must agree
+    chain = np.concatenate(chain)
+    ids_match = None
+    if os.path.exists(CHAIN_FIXTURE) and cfg.layers == 48 and B == 16:
+        fx = np.load(CHAIN_FIXTURE)
+        key = "place%d" % place
+        if key in fx.files:
+            n = min(len(chain), fx[key].shape[0])
+            ids_match = bool(np.array_equal(chain[:n], fx[key][:n]))
+    if dist is not None:
+        mine = torch.from_numpy(chain.astype(np.int32)).cuda()
+        alls = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(alls, mine)
+        same = all(bool(torch.equal(alls[0], a)) for a in alls)
+        ids_match = (ids_match and same) if ids_match is not None else (None if same else False)
+
+    # ---- sustained: the same chained steps back to back for a few seconds, SM clock sampled meanwhile
+    sustained = None
+    if sustain_steps > 0:
+        smp = ClockSampler(local)
+        smp.start()
+        sync_all()
+        done, t0s = 0, time.perf_counter()
+        es, ee = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        es.record(stream)
+        while time.perf_counter() - t0s < args.sustain and done + K <= sustain_steps:
+            ids, _ = eng.decode_greedy(sids, cur, K)
+            cur = ids[-1]
+            done += K
+        ee.record(stream)
+        sync_all()
+        sms = es.elapsed_time(ee)
+        ck = smp.stop()
+        if dist is not None:
+            tt = torch.tensor([sms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            sms = float(tt[0])
+        if done:
+            sustained = {"value": B * done / (sms * 1e-3), "unit": UNIT, "steps": done, "seconds": sms * 1e-3, "ms_per_step": sms / done,
+                         "sm_mhz": ck.get("sm_mhz"), "reasons": ck.get("reasons"), "clock_samples": ck.get("samples"),
+                         "ms_per_step_x_sm_ghz": (sms / done) * (ck["sm_mhz"] / 1e3) if ck.get("sm_mhz") else None}
+
     # ---- per-kernel durations (CUDA events around every dispatch) and algorithmic bytes of the last step
-    gpu.L.qw_gpu_set_graphs(gpu.g, False)
-    gpu.L.qw_profile_enable(gpu.g, True)
-    eng.step_greedy(sids, cur)
-    import ctypes as C
-    per = {}
-    for i in range(gpu.L.qw_profile_count(gpu.g)):
-        us = C.c_double()
-        nm = gpu.L.qw_profile_get(gpu.g, i, C.byref(us)).decode()
-        per.setdefault(nm, []).append(us.value)
-    gpu.L.qw_profile_enable(gpu.g, False)
+    per, cur = profile_step(gpu, eng, sids, cur)
     sb = eng.step_bytes()
-    peak, peak_src = measured_peak_gbs()
-    gu_bytes = (sb.unique_experts_sum / cfg.layers + (1 if rank == 0 else 0)) * 2 * cfg.expert_inter * (cfg.hidden // 256 * 110)
-    gu_us = float(np.mean(per.get("moe_gu", [float("nan")])))
+    fused = "moe_ffn" in per or "moe_ffn_epx" in per
+    kname = "moe_ffn" if "moe_ffn" in per else "moe_ffn_epx" if fused else "moe_gu"
+    experts_per_launch = sb.unique_experts_sum / cfg.layers + (1 if rank == 0 else 0)
+    gu_bytes = experts_per_launch * (3 if fused else 2) * cfg.expert_inter * (cfg.hidden // 256 * 110)
+    gu_us = float(np.mean(per.get(kname, [float("nan")])))
     achieved = gu_bytes / (gu_us * 1e-6) / 1e9
-    # DRAM traffic of a gate/up launch: ncu measured 124.4 MB read + written for 117.1 MB of weights on a launch of the
-    # same shape (profiles/moe_gu_dn_route_qmv_16slots_ncu_full.md); the ratio is applied to this run's own bytes
-    gu_traffic = gu_bytes * (124.4 / 117.1)
+    ratio = ncu_traffic_ratio() if fused else None
     tot_us = sum(sum(v) for v in per.values())
     shares = {k: round(sum(v) / tot_us, 4) for k, v in sorted(per.items(), key=lambda kv: -sum(kv[1]))}
+    kernel_us = {k: [len(v), round(float(np.mean(v)), 2)] for k, v in sorted(per.items(), key=lambda kv: -sum(kv[1]))}
+    # the copy-only twin of the expert FFN kernel in its place: what the staging pipeline alone sustains on the same experts
+    copy_gbs = None
+    if fused and world == 1 and eng.L.qw_engine_set_moe_probe(eng.e, 1) == 0:
+        perp, cur = profile_step(gpu, eng, sids, cur)
+        eng.L.qw_engine_set_moe_probe(eng.e, 0)
+        sbp = eng.step_bytes()
+        pb = (sbp.unique_experts_sum / cfg.layers + 1) * 3 * cfg.expert_inter * (cfg.hidden // 256 * 110)
+        pu = float(np.mean(perp.get("moe_ffn_copy_probe", [float("nan")])))
+        copy_gbs = pb / (pu * 1e-6) / 1e9
+    gpu.L.qw_gpu_set_graphs(gpu.g, bool(args.graphs))
+    step_bytes_max = sb.total
+    if dist is not None:  # every rank moves its own experts, KV pages and recurrent state: the slowest rank bounds the step
+        tt = torch.tensor([sb.total], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        step_bytes_max = float(tt[0])
+
+    # ---- 64 active slots (1 GPU): the first 16 are the same conversations
+    big = None
+    if BB:
+        sb_ids = np.arange(BB, dtype=np.int32)
+        tb = np.concatenate([cur, (np.arange(B, BB, dtype=np.int32) * 7919) % cfg.vocab]).astype(np.int32)
+        ids, _ = eng.decode_greedy(sb_ids, tb, W)
+        sync_all()
+        eb0, eb1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        eb0.record(stream)
+        ids, _ = eng.decode_greedy(sb_ids, ids[-1], K)
+        eb1.record(stream)
+        sync_all()
+        bms = eb0.elapsed_time(eb1)
+        sbb = eng.step_bytes()
+        big = {"slots": BB, "value": BB * K / (bms * 1e-3), "unit": UNIT, "ms_per_step": bms / K, "ctx_tokens": int(sbb.ctx_tokens),
+               "unique_experts_per_layer": sbb.unique_experts_sum / cfg.layers, "step_bytes": sbb.total,
+               "step_frac_of_hbm_roofline": sbb.total / (peak * 1e9) * 1e3 / (bms / K)}
 
     if rank == 0:
         value = B * K / (dev_ms * 1e-3)
         e2e = B * K / (e2e_wall_ms * 1e-3)
-        step_roof_ms = sb.total / (peak * 1e9) * 1e3
+        step_roof_ms = step_bytes_max / (peak * 1e9) * 1e3
         out = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x int (IQ3_S / Q8_0 weights), f32 accumulate",
@@ -382,16 +507,25 @@ def main():
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 3 * 64 * 4, "d2h_bytes_per_step": B * 4, "ms_per_step": e2e_wall_ms / K},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "moe_gu (IQ3_S gate/up matvec over gathered experts)", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": gu_traffic, "traffic_source": "ncu dram bytes of one launch, scaled by algorithmic bytes",
-                         "peak_source": peak_src,
-                         "bytes_per_launch": gu_bytes, "us_per_launch": gu_us},
-            "step_bytes": {"total": sb.total, "moe": sb.moe, "dense": sb.dense, "lm_head": sb.lm_head, "kv": sb.kv, "gdn_state": sb.gdn_state,
+            "roofline": {"bound": "hbm", "kernel": kname + (" (IQ3_S gate/up + down matvecs over the gathered experts, one launch per layer)" if fused
+                                                               else " (IQ3_S gate/up matvec over gathered experts)"),
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": gu_bytes * ratio if ratio else None,
+                         "traffic_source": "ncu dram bytes of one launch (tracked summary under profiles/), scaled by algorithmic bytes" if ratio
+                                           else "no ncu capture of this kernel recorded",
+                         "peak_source": peak_src, "bytes_per_launch": gu_bytes, "us_per_launch": gu_us, "copy_ceiling_gbs": copy_gbs},
+            "step_bytes": {"total": step_bytes_max, "moe": sb.moe, "dense": sb.dense, "lm_head": sb.lm_head, "kv": sb.kv, "gdn_state": sb.gdn_state,
+                           "scope": "one rank (the largest over ranks in total)" if world > 1 else "the GPU",
                            "unique_experts_per_layer": sb.unique_experts_sum / cfg.layers, "ctx_tokens": int(sb.ctx_tokens),
                            "step_roofline_ms": step_roof_ms, "step_frac_of_hbm_roofline": step_roof_ms / (dev_ms / K),
-                           "frac_of_nominal_8TBs": sb.total / 8e12 * 1e3 / (dev_ms / K)},
-            "kernel_time_shares": shares,
+                           "frac_of_nominal_8TBs": step_bytes_max / 8e12 * 1e3 / (dev_ms / K)},
+            "kernel_time_shares": shares, "kernel_us": kernel_us,
+            "ids_match_single_gpu": ids_match,
         }
+        if sustained:
+            out["sustained"] = sustained
+        if big:
+            out["slots64" if BB == 64 else "slots_big"] = big
         if world == 1 and not args.no_cpu:
             v, cores, kind, sample = cpu_baseline_avg(B, ctx)
             out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample}

@@ -107,8 +107,9 @@ double qw_engine_par_cost(qw_engine *e, int B);      /* src/engine.h:95: EMA of 
 size_t qw_engine_par_mem(qw_engine *e);              /* src/engine.h:96: bytes of slot state in use */
 int qw_engine_par_pos(qw_engine *e, int sid);        /* tokens in slot sid's context, -1 if unused */
 
-/* Algorithmic bytes one step over these slots must move (weights of the distinct experts the last step chose,
- * dense weights, KV of the contexts, GDN state read + write): the numerator of the HBM roofline. */
+/* Algorithmic bytes one step over these slots must move on THIS rank (weights of the distinct experts the last step chose
+ * among the experts held here, the shared expert on rank 0, dense weights, KV of the contexts and GDN state read + write of
+ * the slots whose token mixers ran here): the numerator of the HBM roofline. */
 typedef struct {
     double moe, dense, lm_head, kv, gdn_state, other, total;
     int unique_experts_sum; /* sum over layers of distinct experts chosen in the last step */

@@ -45,18 +45,22 @@ struct EpPeers {
     unsigned *seq, *done;  // local: this rank's sequence counter, finished-block counter (both start at zero)
     uint32_t nranks, rank;
 };
-// Every thread of every block calls this after its last peer store: the stores are made visible system-wide, the block
-// counts itself done, the last block advances this rank's sequence number and writes it into slot [rank] of every rank.
+// Every thread of every block calls this after its last peer store.  The block barrier makes the block's stores visible to
+// its first thread, whose one system-scope fence then orders them (fences are cumulative) before the counter update; the
+// last block advances this rank's sequence number, fences once more and writes the number into slot [rank] of every rank
+// with plain (relaxed) stores issued back to back -- together with the fence they are release stores, but none of them
+// waits for the previous peer's store to be performed, so the publish costs one NVLink round trip, not one per rank.
+__device__ __forceinline__ void st_relaxed_sys(unsigned *p, unsigned v) { asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void ep_publish(const EpPeers &ep) {
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) {
+        __threadfence_system();
         if (atomicAdd(ep.done, 1u) == gridDim.x * gridDim.y * gridDim.z - 1) {
             *ep.done = 0;
             const unsigned sv = *ep.seq + 1;
             *ep.seq = sv;
-            __threadfence_system();
-            for (uint32_t r = 0; r < ep.nranks; r++) st_release_sys(ep.flagR[r] + ep.rank, sv);
+            __threadfence_system();  // every block's stores (observed through the counter) before the flags
+            for (uint32_t r = 0; r < ep.nranks; r++) st_relaxed_sys(ep.flagR[r] + ep.rank, sv);
         }
     }
 }

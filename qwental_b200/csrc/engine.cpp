@@ -116,6 +116,7 @@ struct qw_engine {
     int lastB = 0;
     std::vector<int> last_sids;
     long long last_ctx = 0;
+    int last_own = 0;  // rows of the last step whose token mixers ran on this rank
 
     bool fail(const char *fmt, ...) {
         char buf[512];
@@ -759,11 +760,16 @@ void end_step(qw_engine *e, const int *sids, int B, int nsteps, double wall_ms) 
     e->last_sids.assign(sids, sids + B);
     e->lastB = B;
     e->last_ctx = 0;
+    e->last_own = 0;
     for (int i = 0; i < B; i++) {
         Slot &s = e->slots[sids[i]];
         s.pos += nsteps;
         s.last_use = ++e->clock;
-        e->last_ctx += s.pos;  // tokens attended by the last of the steps
+        // tokens attended by the last of the steps -- under slot sharding only the slots this rank owns are its traffic
+        if (!e->slot_shard || sids[i] % e->c.ep_size == e->c.ep_rank) {
+            e->last_ctx += s.pos;
+            e->last_own++;
+        }
     }
     const double per = wall_ms / nsteps;
     e->cost[B] = e->cost[B] == 0 ? per : 0.8 * e->cost[B] + 0.2 * per;
@@ -979,7 +985,7 @@ extern "C" void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *o) {
         uint32_t U = 0;
         qw_buf_download(e->g, &e->msel, (size_t)l * e->sel_bytes, &U, 4);
         usum += (int)U;
-        o->moe += ((double)U + 1) * 3 * gu + (double)(e->E + 1) * e->D * 2;
+        o->moe += ((double)U + (e->c.ep_rank == 0 ? 1 : 0)) * 3 * gu + (double)(e->E + 1) * e->D * 2;  // the shared expert runs on rank 0
         const LayerW &w = e->layers[l];
         o->dense += (double)w.n_in * e->rbD + (double)e->D * (w.attn ? e->rbKA : e->rbKG);
     }
@@ -987,7 +993,7 @@ extern "C" void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *o) {
     o->lm_head = (double)e->V * e->rbV;
     o->ctx_tokens = e->last_ctx;
     o->kv = (double)e->last_ctx * 2 * e->KVH * e->HD * 2 * e->n_attn;
-    o->gdn_state = (double)e->lastB * e->n_gdn * e->HV * 128 * 128 * 4 * 2;
+    o->gdn_state = (double)e->last_own * e->n_gdn * e->HV * 128 * 128 * 4 * 2;
     o->other = (double)e->lastB * e->V * 4 * 2;
     o->total = o->moe + o->dense + o->lm_head + o->kv + o->gdn_state + o->other;
 }

@@ -147,6 +147,10 @@ class Engine:
             raise GpuError("par_decode_greedy: " + self.error())
         return out, ms.value
 
+    def set_moe_probe(self, on: bool) -> bool:
+        """Measurement aid: run the copy-only twin of the fused expert FFN kernel in its place (see qw_engine.h)."""
+        return self.L.qw_engine_set_moe_probe(self.e, int(on)) == 0
+
     def cost(self, B: int) -> float:
         return self.L.qw_engine_par_cost(self.e, B)
 

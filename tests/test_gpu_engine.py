@@ -222,3 +222,41 @@ def test_prefill_is_the_decode_path_token_by_token(gpu):
             e.prefill(99, [1])
     finally:
         e.close()
+
+
+def test_benchmark_engine_full_depth_batched_equals_alone_and_graph_replay(gpu):
+    """The benchmark engine itself -- all 48 layers, the 16 ragged conversations bench.py steps (contexts log-uniform in
+    1K..48K, the same seeds) -- needs no oracle for the reference's own guarantee (src/engine.c:7977-7986,
+    tools/run.c:217-229): three rows of the 16-row step are bit-identical to the same slots stepped alone, and the step
+    replayed as a CUDA graph gives the bytes of the plain launches."""
+    from qwental_b200 import synth
+    from qwental_b200.engine import Engine, default_cfg
+    B = 16
+    ctx = synth.ragged_contexts(np.random.default_rng(0), B)
+    pages = int(sum((int(n) + 64 + 256) // 256 + 1 for n in ctx))
+    e = Engine(gpu, default_cfg(max_slots=B, max_ctx=int(ctx.max()) + 1024, kv_pages=pages, seed=0))
+    try:
+        def seed(rows):
+            for s in rows:
+                e.seed_slot(s, int(ctx[s]), 100 + s)
+        sids = np.arange(B, dtype=np.int32)
+        toks = (np.arange(B, dtype=np.int32) * 7919) % e.cfg.vocab
+        seed(range(B))
+        lb, _ = e.step(sids, toks)
+        assert np.isfinite(lb).all()
+        longest, shortest = int(np.argmax(ctx)), int(np.argmin(ctx))
+        for r in sorted({longest, shortest, 7}):
+            seed([r])
+            la, _ = e.step([r], [toks[r]])
+            assert np.array_equal(la[0].view(np.uint32), lb[r].view(np.uint32)), (r, int(ctx[r]))
+        gpu.L.qw_gpu_set_graphs(gpu.g, True)
+        try:
+            seed(range(B))
+            e.step(sids, toks)        # records the graph
+            seed(range(B))
+            lg, _ = e.step(sids, toks)  # replays it
+        finally:
+            gpu.L.qw_gpu_set_graphs(gpu.g, False)
+        assert np.array_equal(lg.view(np.uint32), lb.view(np.uint32))
+    finally:
+        e.close()
