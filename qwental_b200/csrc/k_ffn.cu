@@ -22,6 +22,7 @@
 #include "qmv_core.cuh"
 #include "qw_kern.h"
 #include <cuda.h>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -33,22 +34,26 @@ namespace {
 constexpr int FFN_CW = 16;                       // consumer warps
 constexpr int FFN_THREADS = (FFN_CW + 1) * 32;   // + the producer warp
 constexpr int FFN_STG = 3;
+constexpr int FFN_PF = 2;                        // whole tiles (56 - 112 KB) the L2 prefetch cursor runs ahead of the copies (QW_FFN_PF overrides)
 constexpr int FFN_PITCH = 240;                   // bytes between staged gate/up rows
 constexpr int FFN_SLOT = 128 * FFN_PITCH;        // 30720: also holds a down tile of 128 x 220 bytes
 constexpr int FFN_TAB = 65536;
 constexpr int FFN_OFF_TAB = 128;
-constexpr int FFN_OFF_PRE = FFN_OFF_TAB + FFN_TAB;          // uint32 pre[MOE_MAXE + 2], padded to 4224 bytes
-constexpr int FFN_OFF_RED = FFN_OFF_PRE + 4224;             // [2][8 row groups][32 lanes] float4
+constexpr int FFN_MAXG = 520;                               // groups kept in shared memory: E <= 512 experts (+ end markers)
+constexpr int FFN_OFF_PRE = FFN_OFF_TAB + FFN_TAB;          // uint32 pre[FFN_MAXG], off[FFN_MAXG], ue[FFN_MAXG] of the selection record
+constexpr int FFN_OFF_RED = FFN_OFF_PRE + 3 * FFN_MAXG * 4 + 32;  // [2][8 row groups][32 lanes] float4  (6272 = 49 * 128)
 constexpr int FFN_OFF_XS = FFN_OFF_RED + 2 * 8 * 32 * 16;   // tokens of the pass, then H planes, then the stages
 
 struct FfnP {
     const uint8_t *Wd, *Sd;   // routed down [E][D][rbI], shared expert's down [D][rbI] (nullptr: no shared expert)
+    const uint8_t *Wg, *Wu, *Sg, *Su;  // gate / up matrices (the copies go through the tensor maps; these are for the L2 prefetch)
     const __half *x;          // tokens fp16 [nb][D]
     float *Pg;                // [nb][topk+1][D]
     const moe_sel *ms;
     const QwTables *tab;
     unsigned *status;
-    uint32_t D, I, rbD, rbI, ebase;
+    uint32_t D, I, rbD, rbI, ebase, pf, probe1d, hint;
+    unsigned long long *dbg;  // optional (define DBG 1, bind 13): cycle counters of the consumer warps, for tuning
     float *PgR[8];            // expert-parallel exchange: Pg of every rank (see moe_dn in k_moe.cu)
     EpPeers ep;
 };
@@ -65,7 +70,8 @@ struct FfnItem {
     bool shared;
 };
 // item number w -> (group, pass): routed groups first (pre[] = passes before each group), then the shared expert's passes
-__device__ __forceinline__ FfnItem ffn_item(const moe_sel *ms, const uint32_t *pre, uint32_t U, uint32_t nb, uint32_t w) {
+__device__ __forceinline__ FfnItem ffn_item(const uint32_t *pre, uint32_t U, uint32_t nb, uint32_t w) {
+    const uint32_t *off = pre + FFN_MAXG;
     FfnItem it;
     const uint32_t routed = pre[U];
     if (w >= routed) {
@@ -83,8 +89,8 @@ __device__ __forceinline__ FfnItem ffn_item(const moe_sel *ms, const uint32_t *p
         }
         it.shared = false;
         it.u = lo;
-        it.e0 = ms->off[lo];
-        it.cnt = ms->off[lo + 1] - it.e0;
+        it.e0 = off[lo];
+        it.cnt = off[lo + 1] - it.e0;
         it.c0 = (w - pre[lo]) * 8;
     }
     it.ncols = it.cnt - it.c0 < 8 ? it.cnt - it.c0 : 8;
@@ -102,28 +108,110 @@ __device__ __forceinline__ void ffn_entry(const moe_sel *ms, const FfnItem &it, 
     }
 }
 
-template <int IB>
-__device__ __forceinline__ void ffn_sub_gu(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr, uint32_t bx,
-                                           bool have, float (&acc)[4]) {
-    uint4 xv = make_uint4(0, 0, 0, 0);
-    if (have) xv = lds_v4(bx + IB * 64);
-    sub_mma1<false, IB, 128>(u0, u1, t, h0, h1, tabc, zr, xv, xv, acc);
+// ---- decode of this kernel.  The codebook sits in shared memory as its raw 4 bytes per entry in 32 interleaved copies (64 KB:
+// lane l reads copy l, so a warp's 32 lookups hit 32 different banks in one wavefront).  A byte b becomes the fp16 subnormal
+// with bit pattern 0x00bb = b * 2^-24 -- exact, and the tensor core multiplies subnormals like any other value -- so one byte
+// permute builds two weights from two table bytes and two sign bytes (0x80 / 0x00 in the halves' upper bytes); the factor
+// 2^24 is folded into the block scale d, a power of two that changes no rounding.  The four sign bytes of a codebook word come
+// from the sign byte of the sub-block by one multiply (four non-overlapping shifted copies) and one AND.
+struct RowHdr {
+    float d, d2;        // block scale * 2^24 and twice it: sub-block scale = d + d2 * s
+    uint32_t qa0, qa1;  // bytes = this thread's codebook high bit for word 0 of sub-blocks 0..3 / 4..7 (0 or 1)
+    uint32_t qb0, qb1;  // the same for word 1
+    uint32_t sclo, schi;  // the 4-bit scales of sub-blocks 0,2,4,6 / 1,3,5,7, one per byte
+};
+__device__ __forceinline__ RowHdr row_hdr(uint32_t blk, int t) {
+    RowHdr h;
+    h.d = h2f((uint16_t)lds_u16<0>(blk)) * 16777216.0f;
+    h.d2 = h.d + h.d;
+    const uint32_t q0 = (lds_u16<66>(blk) | (lds_u16<68>(blk) << 16)) >> (2 * t);
+    const uint32_t q1 = (lds_u16<70>(blk) | (lds_u16<72>(blk) << 16)) >> (2 * t);
+    h.qa0 = q0 & 0x01010101u;
+    h.qb0 = (q0 >> 1) & 0x01010101u;
+    h.qa1 = q1 & 0x01010101u;
+    h.qb1 = (q1 >> 1) & 0x01010101u;
+    const uint32_t sc = lds_u16<106>(blk) | (lds_u16<108>(blk) << 16);
+    h.sclo = sc & 0x0f0f0f0fu;
+    h.schi = (sc >> 4) & 0x0f0f0f0fu;
+    return h;
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+// 16-byte load of a B fragment into registers that keep their value (zero) in lanes whose column is absent
+template <int OFF>
+__device__ __forceinline__ void lds_v4_if(uint4 &v, uint32_t a, uint32_t have) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %5, 0;\n\t@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%6];\n\t}"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+                 : "r"(a), "r"(have), "n"(OFF));
+}
+// this thread's 8 weights of sub-block IB of one row as four packed pairs; returns the sub-block scale d * (1 + 2 s) * 2^24
 template <int IB>
-__device__ __forceinline__ void ffn_sub_dn(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, const ZeroRegs &zr, uint32_t bh,
-                                           uint32_t bl, bool have, float (&acc)[4]) {
-    uint4 xv = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
-    if (have) {
+__device__ __forceinline__ float row_sub(uint32_t blk_t, uint32_t blk_s, const RowHdr &h, uint32_t tabl, uint32_t (&w)[4]) {
+    constexpr uint32_t k = IB & 3;
+    constexpr uint32_t selA = (3u << 12) | (2u << 8) | ((4 + k) << 4) | 0, selB = (3u << 12) | (2u << 8) | ((4 + k) << 4) | 1;
+    const uint32_t qs = lds_u16<2 + 8 * IB>(blk_t);
+    const uint32_t sg = lds_u8<74 + 4 * IB>(blk_s);
+    const uint32_t v0 = lds_u32(tabl + __byte_perm(qs, IB < 4 ? h.qa0 : h.qa1, selA) * 128);
+    const uint32_t v1 = lds_u32(tabl + __byte_perm(qs, IB < 4 ? h.qb0 : h.qb1, selB) * 128);
+    // sign bit j of the low / high nibble -> bit 7 of byte 3 - j
+    const uint32_t s0 = (sg * 0x80402010u) & 0x80808080u, s1 = (sg * 0x08040201u) & 0x80808080u;
+    w[0] = __byte_perm(v0, s0, 0x6170);
+    w[1] = __byte_perm(v0, s0, 0x4352);
+    w[2] = __byte_perm(v1, s1, 0x6170);
+    w[3] = __byte_perm(v1, s1, 0x4352);
+    const uint32_t n = __byte_perm(IB & 1 ? h.schi : h.sclo, 0, 0x4440 | (IB >> 1));
+    return fmaf(h.d2, (float)n, h.d);
+}
+// one sub-block of rows g (at u0) and g + 8 (at u1): PLANES = 1 for fp16 tokens, 2 for H as fp16 high + low
+template <int IB, int PLANES, int VAR>
+__device__ __forceinline__ void ffn_sub(uint32_t u0, uint32_t u1, int t, const RowHdr &h0, const RowHdr &h1, uint32_t tabl, const ZeroRegs &zr, uint32_t bh,
+                                        uint32_t bl, uint32_t have, uint4 &xv, uint4 &xl, float (&acc)[4]) {
+    if (VAR == 1) {  // every lane loads: a lane whose column is absent reads its own (stale) row -- that column's results are never stored
         xv = lds_v4(bh + IB * 64);
-        xl = lds_v4(bl + IB * 64);
+        if (PLANES == 2) xl = lds_v4(bl + IB * 64);
+    } else {
+        lds_v4_if<IB * 64>(xv, bh, have);
+        if (PLANES == 2) lds_v4_if<IB * 64>(xl, bl, have);
     }
-    sub_mma1_h2<IB, 128>(u0, u1, t, h0, h1, tabc, zr, xv, xl, acc);
+    uint32_t wa[4], wb[4];
+    const float dba = row_sub<IB>(u0 + 2 * t, u0 + t, h0, tabl, wa);
+    const float dbb = row_sub<IB>(u1 + 2 * t, u1 + t, h1, tabl, wb);
+    const uint32_t a0[4] = {wa[0], wb[0], wa[1], wb[1]};
+    const uint32_t a1[4] = {wa[2], wb[2], wa[3], wb[3]};
+    float p[4];
+    mma_f16(p, a0, xv.x, xv.y, zr.z);
+    mma_f16(p, a1, xv.z, xv.w, p);
+    if (PLANES == 2) {
+        mma_f16(p, a0, xl.x, xl.y, p);
+        mma_f16(p, a1, xl.z, xl.w, p);
+    }
+    acc[0] = fmaf(dba, p[0], acc[0]);
+    acc[1] = fmaf(dba, p[1], acc[1]);
+    acc[2] = fmaf(dbb, p[2], acc[2]);
+    acc[3] = fmaf(dbb, p[3], acc[3]);
+}
+template <int PLANES, int VAR>
+__device__ __forceinline__ void ffn_unit(uint32_t u0, uint32_t u1, int t, uint32_t tabl, const ZeroRegs &zr, uint32_t bh, uint32_t bl, uint32_t have,
+                                         float (&acc)[4]) {
+    const RowHdr h0 = row_hdr(u0, t), h1 = row_hdr(u1, t);
+    uint4 xv = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
+    ffn_sub<0, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<1, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<2, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<3, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<4, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<5, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<6, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<7, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
 }
 
 // PROBE = true is the copy-only twin used to measure what the staging pipeline alone can deliver: the same items, the same
 // TMA boxes and bulk copies through the same ring, but the consumers only read every staged byte once (16-byte loads) and
 // compute nothing -- the role of the reference's pure-read probes (bench/moe_bw.c:1-3, bench/qmv.c:357-382).
-template <bool PROBE>
+template <bool PROBE, int VAR>
 __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
                                                            const __grid_constant__ CUtensorMap mSG, const __grid_constant__ CUtensorMap mSU, const FfnP p) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -147,11 +235,15 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
         mbar_init(xfree, FFN_CW);
         mbar_init_fence();
         mbar_expect_tx(tab_bar, FFN_TAB);
-        bulk_g2s(smem + FFN_OFF_TAB, p.tab->grid_h4, FFN_TAB, tab_bar);
+        bulk_g2s(smem + FFN_OFF_TAB, p.tab->grid_u32x32, FFN_TAB, tab_bar);
     }
     pdl_wait();  // the selection record, the tokens and Pg belong to earlier kernels
     const moe_sel *ms = p.ms;
-    for (uint32_t i = tid; i <= MOE_MAXE + 1; i += FFN_THREADS) pre[i] = ms->pre[i];
+    // groups, their first entries, passes and experts: independent loads, so the whole record is in shared memory after one latency
+    for (uint32_t i = tid; i < 3 * FFN_MAXG; i += FFN_THREADS) {
+        const uint32_t a = i / FFN_MAXG, e = i - a * FFN_MAXG;
+        pre[i] = a == 0 ? ms->pre[e] : a == 1 ? ms->off[e] : ms->ue[e];
+    }
     const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
     __syncthreads();
     const uint32_t items = pre[U] + (p.Sd ? (nb + 7) / 8 : 0);
@@ -172,8 +264,50 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 mbar_expect_tx(&full[s], bytes);
                 return slot0 + s * FFN_SLOT;
             };
+            // The gate/up stages read 240 bytes of every 880-byte row at a time: left to the copies alone, DRAM would see small
+            // scattered pieces.  A second cursor therefore runs ahead of the copies and asks for whole tiles -- 64 contiguous
+            // rows of gate and of up (56 KB each), pairs of down tiles (56 KB) -- to be brought into L2 (prefetches hold no shared
+            // memory), so DRAM streams contiguous ranges and the strided boxes are served from L2.
+            const uint32_t PU = GT + DT / 2;  // prefetch units per item
+            struct Src {
+                const CUtensorMap *tg, *tu;
+                const uint8_t *wg, *wu, *wd;
+                uint32_t erow;
+            };
+            auto src_of = [&](uint32_t w) {
+                const FfnItem it = ffn_item(pre, U, nb, w);
+                Src c;
+                c.erow = it.shared ? 0 : (pre[2 * FFN_MAXG + it.u] - p.ebase);
+                c.tg = it.shared ? &mSG : &mG;
+                c.tu = it.shared ? &mSU : &mU;
+                c.wg = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * p.I * p.rbD;
+                c.wu = (it.shared ? p.Su : p.Wu) + (size_t)c.erow * p.I * p.rbD;
+                c.wd = it.shared ? p.Sd : p.Wd + (size_t)c.erow * p.D * p.rbI;
+                return c;
+            };
+            auto l2_prefetch = [](const uint8_t *ptr, uint32_t bytes) {
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
+            };
+            uint32_t pw = blockIdx.x, pu = 0;
+            Src pc{};
+            if (pw < items) pc = src_of(pw);
+            auto prefetch_next = [&]() {
+                if (pw >= items) return;
+                if (pu < GT) {
+                    l2_prefetch(pc.wg + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
+                    l2_prefetch(pc.wu + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
+                } else {
+                    l2_prefetch(pc.wd + (size_t)(pu - GT) * 256 * p.rbI, 256 * p.rbI);
+                }
+                if (++pu == PU) {
+                    pu = 0;
+                    pw += gridDim.x;
+                    if (pw < items) pc = src_of(pw);
+                }
+            };
+            for (uint32_t i = 0; i < p.pf; i++) prefetch_next();
             for (uint32_t w = blockIdx.x; w < items; w += gridDim.x, n++) {
-                const FfnItem it = ffn_item(ms, pre, U, nb, w);
+                const FfnItem it = ffn_item(pre, U, nb, w);
                 if (n > 0 && ok && !mbar_wait(xfree, (n - 1) & 1)) {  // every consumer warp is done with the previous item's tokens
                     ok = false;
                     set_status(p.status, ST_MBAR_TIMEOUT | 7);
@@ -185,20 +319,29 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                     ffn_entry(ms, it, topk, c, tok, rank);
                     bulk_g2s(xs + c * xpitch, p.x + (size_t)tok * p.D, p.D * 2, xfull);
                 }
-                const uint32_t erow = it.shared ? 0 : (ms->ue[it.u] - p.ebase);
-                const CUtensorMap *tg = it.shared ? &mSG : &mG, *tu = it.shared ? &mSU : &mU;
-                for (uint32_t gt = 0; gt < GT; gt++)
+                const Src sc = src_of(w);
+                for (uint32_t gt = 0; gt < GT; gt++) {
+                    if (p.pf) prefetch_next();
                     for (uint32_t kp = 0; kp < KP; kp++, j++) {
                         const uint32_t dst = slot_for(2 * 64 * FFN_PITCH);
-                        const int xc = (int)((220 * kp) & ~15u), yr = (int)(erow * p.I + gt * 64);
-                        tma_box_2d(dst, tg, xc, yr, &full[j % FFN_STG]);
-                        tma_box_2d(dst + 64 * FFN_PITCH, tu, xc, yr, &full[j % FFN_STG]);
+                        const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * p.I + gt * 64);
+                        if (PROBE && p.probe1d) {  // measurement only: the same bytes per stage as two contiguous runs instead of two boxes
+                            const size_t o = ((size_t)gt * KP + kp) * 64 * FFN_PITCH;
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                                         "l"(sc.wg + o), "r"(64 * FFN_PITCH), "r"(smem_u32(&full[j % FFN_STG])) : "memory");
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + 64 * FFN_PITCH),
+                                         "l"(sc.wu + o), "r"(64 * FFN_PITCH), "r"(smem_u32(&full[j % FFN_STG])) : "memory");
+                            continue;
+                        }
+                        tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
+                        tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
                     }
-                const uint8_t *wd = it.shared ? p.Sd : p.Wd + (size_t)erow * p.D * p.rbI;
+                }
                 for (uint32_t dt = 0; dt < DT; dt++, j++) {
+                    if (p.pf && !(dt & 1)) prefetch_next();
                     const uint32_t dst = slot_for(128 * p.rbI);
                     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                                 "l"(wd + (size_t)dt * 128 * p.rbI), "r"(128 * p.rbI), "r"(smem_u32(&full[j % FFN_STG]))
+                                 "l"(sc.wd + (size_t)dt * 128 * p.rbI), "r"(128 * p.rbI), "r"(smem_u32(&full[j % FFN_STG]))
                                  : "memory");
                 }
             }
@@ -208,16 +351,20 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
         const int r = warp & 7, kh = warp >> 3;
         bool ok = mbar_wait(tab_bar, 0);
         if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 8);
-        const uint32_t tabc = smem_u32(smem + FFN_OFF_TAB) + (lane & 15) * 8;  // this lane's copy of the interleaved codebook
+        const uint32_t tabl = smem_u32(smem + FFN_OFF_TAB) + lane * 4;  // this lane's copy of the interleaved codebook
         const ZeroRegs zr = zero_regs();
         const uint32_t xb0 = smem_u32(xs) + g * xpitch + t * 16;
         const uint32_t hb0 = smem_u32(hs) + g * hpitch + t * 16;
         uint32_t j = 0, n = 0, rc = 0;
+        long long c_wait = 0, c_bar = 0, c_x = 0;
+        const long long c_begin = clock64();
         auto wait_full = [&]() {
-            if (ok && !mbar_wait(&full[j % FFN_STG], (j / FFN_STG) & 1)) {
+            const long long c0 = p.dbg ? clock64() : 0;
+            if (ok && !(p.hint ? mbar_wait_hint(&full[j % FFN_STG], (j / FFN_STG) & 1, p.hint) : mbar_wait(&full[j % FFN_STG], (j / FFN_STG) & 1))) {
                 ok = false;
                 if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 9);
             }
+            if (p.dbg) c_wait += clock64() - c0;
             return slot0 + (j % FFN_STG) * FFN_SLOT;
         };
         auto release = [&]() {
@@ -230,7 +377,9 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             float4 *rd = red + ((rc & 1) * 8 + r) * 32 + lane;
             rc++;
             if (kh) *rd = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            const long long c0 = p.dbg ? clock64() : 0;
             bar_sync_n(1 + r, 64);
+            if (p.dbg) c_bar += clock64() - c0;
             if (!kh) {
                 const float4 v = *rd;
                 acc[0] += v.x;
@@ -240,9 +389,9 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             }
         };
         for (uint32_t w = blockIdx.x; w < items; w += gridDim.x, n++) {
-            const FfnItem it = ffn_item(ms, pre, U, nb, w);
+            const FfnItem it = ffn_item(pre, U, nb, w);
             if (n > 0) bar_sync_n(9, FFN_CW * 32);  // nobody still reads the previous item's H rows
-            const bool have = (uint32_t)g < it.ncols;
+            const uint32_t have = (uint32_t)g < it.ncols ? 1u : 0u;
             uint32_t oo[2] = {0xffffffffu, 0xffffffffu};  // element offsets of the output rows of columns 2t and 2t + 1
 #pragma unroll
             for (int c = 0; c < 2; c++)
@@ -251,9 +400,13 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                     ffn_entry(ms, it, topk, 2 * t + c, tok, rank);
                     oo[c] = (tok * (topk + 1) + rank) * p.D;
                 }
-            if (ok && !mbar_wait(xfull, n & 1)) {
-                ok = false;
-                if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 10);
+            {
+                const long long c0 = p.dbg ? clock64() : 0;
+                if (ok && !mbar_wait(xfull, n & 1)) {
+                    ok = false;
+                    if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 10);
+                }
+                if (p.dbg) c_x += clock64() - c0;
             }
             if (PROBE) {
                 uint32_t sink = 0;
@@ -277,15 +430,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                     const uint32_t st = wait_full();
                     const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
                     const uint32_t bx = xb0 + (2 * kp + kh) * 512;
-                    const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
-                    ffn_sub_gu<0>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<1>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<2>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<3>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<4>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<5>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<6>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
-                    ffn_sub_gu<7>(u0, u1, t, h0, h1, tabc, zr, bx, have, acc);
+                    ffn_unit<1, VAR>(u0, u1, t, tabl, zr, bx, bx, have, acc);
                     release();
                 }
                 pair_sum(acc);
@@ -316,15 +461,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 for (uint32_t ks = kh; ks < KU; ks += 2) {
                     const uint32_t u0 = st + (16 * r + 2 * g) * p.rbI + ks * 110, u1 = u0 + p.rbI;
                     const uint32_t bh = hb0 + ks * 512, bl = bh + 8 * hpitch;
-                    const Iq3sHdr h0 = iq3s_hdr(u0, t), h1 = iq3s_hdr(u1, t);
-                    ffn_sub_dn<0>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<1>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<2>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<3>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<4>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<5>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<6>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
-                    ffn_sub_dn<7>(u0, u1, t, h0, h1, tabc, zr, bh, bl, have, acc);
+                    ffn_unit<2, VAR>(u0, u1, t, tabl, zr, bh, bl, have, acc);
                 }
                 release();
                 pair_sum(acc);
@@ -342,6 +479,13 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                     }
                 }
             }
+        }
+        if (p.dbg && lane == 0 && n > 0) {
+            atomicAdd(p.dbg + 0, (unsigned long long)(clock64() - c_begin));
+            atomicAdd(p.dbg + 1, (unsigned long long)c_wait);
+            atomicAdd(p.dbg + 2, (unsigned long long)c_bar);
+            atomicAdd(p.dbg + 3, (unsigned long long)c_x);
+            atomicAdd(p.dbg + 4, 1ull);
         }
     }
     if (p.ep.nranks > 1) ep_publish(p.ep);
@@ -389,7 +533,7 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
     p.D = (uint32_t)L.def("D", 2048);
     p.I = (uint32_t)L.def("I", 512);
-    QW_CHECK_ARG(p.D % 2048 == 0 && p.I == 512 && topk < MOE_MAXK);
+    QW_CHECK_ARG(p.D % 2048 == 0 && p.I == 512 && topk < MOE_MAXK && E <= 512);
     p.rbD = p.D / 256 * 110;
     p.rbI = p.I / 256 * 110;
     const size_t smem = FFN_OFF_XS + (size_t)8 * (p.D * 2 + 64) + (size_t)16 * (p.I * 2 + 64) + (size_t)FFN_STG * FFN_SLOT;
@@ -400,6 +544,7 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     QW_CHECK_ARG(EL >= 1 && p.ebase + EL <= E);
     const uint8_t *Wg = L.buf<uint8_t>(0), *Wu = L.buf<uint8_t>(1), *Sg = shared ? L.buf<uint8_t>(2) : nullptr, *Su = shared ? L.buf<uint8_t>(3) : nullptr;
     p.Wd = L.buf<uint8_t>(6);
+    p.Wg = Wg; p.Wu = Wu; p.Sg = Sg; p.Su = Su;
     p.Sd = shared ? L.buf<uint8_t>(7) : nullptr;
     p.x = L.buf<__half>(4);
     p.ms = L.buf<moe_sel>(5);
@@ -429,7 +574,15 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     const CUtensorMap *mG = ffn_tensor_map(Wg, p.rbD, (uint64_t)EL * p.I), *mU = ffn_tensor_map(Wu, p.rbD, (uint64_t)EL * p.I);
     const CUtensorMap *mSG = shared ? ffn_tensor_map(Sg, p.rbD, p.I) : mG, *mSU = shared ? ffn_tensor_map(Su, p.rbD, p.I) : mU;
     QW_CHECK_ARG(mG && mU && mSG && mSU);
-    auto kern = L.def("PROBE", 0) ? moe_ffn_k<true> : moe_ffn_k<false>;  // PROBE defined 1: the copy-only twin (outputs are not written)
+    static const int pf_env = getenv("QW_FFN_PF") ? atoi(getenv("QW_FFN_PF")) : FFN_PF;
+    p.pf = (uint32_t)(pf_env < 0 ? 0 : pf_env > 64 ? 64 : pf_env);
+    p.probe1d = getenv("QW_FFN_PROBE_1D") ? 1 : 0;
+    static const int hint_env = getenv("QW_FFN_HINT") ? atoi(getenv("QW_FFN_HINT")) : 0;
+    p.hint = (uint32_t)(hint_env < 0 ? 0 : hint_env);
+    p.dbg = L.def("DBG", 0) ? L.buf<unsigned long long>(13) : nullptr;
+    if (L.def("DBG", 0)) QW_CHECK_ARG(p.dbg && L.avail(13) >= 64);
+    static const int var_env = getenv("QW_FFN_VAR") ? atoi(getenv("QW_FFN_VAR")) : 0;
+    auto kern = L.def("PROBE", 0) ? moe_ffn_k<true, 0> : var_env == 1 ? moe_ffn_k<false, 1> : moe_ffn_k<false, 0>;  // PROBE defined 1: the copy-only twin (outputs are not written)
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     qw_launch(kern, L.sm_count, FFN_THREADS, smem, L.stream, *mG, *mU, *mSG, *mSU, p);

@@ -23,6 +23,7 @@ cudaError_t qw_tables_create(void **out, cudaStream_t s) {
             memcpy(&h[j], &hh, 2);
             memcpy(&b[j], &bb, 2);
         }
+        for (int c = 0; c < 32; c++) t.grid_u32x32[e * 32 + c] = w;
         for (int c = 0; c < 16; c++) {
             t.grid_h4[e * 16 + c] = make_uint2(h[0] | ((uint32_t)h[1] << 16), h[2] | ((uint32_t)h[3] << 16));
             t.grid_b4[e * 16 + c] = make_uint2(b[0] | ((uint32_t)b[1] << 16), b[2] | ((uint32_t)b[3] << 16));

@@ -60,6 +60,7 @@ struct QwTables {
     uint32_t grid_u32[512];          // IQ3_S codebook, 4 unsigned bytes per entry
     uint2 grid_h4[512 * 16];         // the same as 4 fp16 values, 16 interleaved copies (entry e, copy c at e*16+c)
     uint2 grid_b4[512 * 16];         // the same as 4 bf16 values, 16 interleaved copies
+    uint32_t grid_u32x32[512 * 32];  // grid_u32 in 32 interleaved copies (entry e, copy c at e*32+c): a warp's 32 lanes read 32 different banks
 };
 cudaError_t qw_tables_create(void **out, cudaStream_t s);
 
