@@ -454,7 +454,9 @@ def main():
     fused = "moe_ffn" in per or "moe_ffn_epx" in per
     kname = "moe_ffn" if "moe_ffn" in per else "moe_ffn_epx" if fused else "moe_gu"
     experts_per_launch = sb.unique_experts_sum / cfg.layers + (1 if rank == 0 else 0)
-    gu_bytes = experts_per_launch * (3 if fused else 2) * cfg.expert_inter * (cfg.hidden // 256 * 110)
+    iq3x = fused and sb.moe_iq3s > 0 and abs(sb.moe - sb.moe_iq3s) > 1  # experts re-coded into the kernel's own layout (136 B / 256 weights)
+    iq3s_bytes = experts_per_launch * (3 if fused else 2) * cfg.expert_inter * (cfg.hidden // 256 * 110)
+    gu_bytes = experts_per_launch * ((cfg.expert_inter // 64) * (cfg.hidden // 512) + (cfg.hidden // 128) * (cfg.expert_inter // 512)) * 128 * 272 if iq3x else iq3s_bytes
     gu_us = float(np.mean(per.get(kname, [float("nan")])))
     achieved = gu_bytes / (gu_us * 1e-6) / 1e9
     ratio = ncu_traffic_ratio() if fused else None
@@ -467,7 +469,7 @@ def main():
         perp, cur = profile_step(gpu, eng, sids, cur)
         eng.L.qw_engine_set_moe_probe(eng.e, 0)
         sbp = eng.step_bytes()
-        pb = (sbp.unique_experts_sum / cfg.layers + 1) * 3 * cfg.expert_inter * (cfg.hidden // 256 * 110)
+        pb = gu_bytes / experts_per_launch * (sbp.unique_experts_sum / cfg.layers + 1)
         pu = float(np.mean(perp.get("moe_ffn_copy_probe", [float("nan")])))
         copy_gbs = pb / (pu * 1e-6) / 1e9
     gpu.L.qw_gpu_set_graphs(gpu.g, bool(args.graphs))
@@ -513,8 +515,10 @@ def main():
                          "traffic": gu_bytes * ratio if ratio else None,
                          "traffic_source": "ncu dram bytes of one launch (tracked summary under profiles/), scaled by algorithmic bytes" if ratio
                                            else "no ncu capture of this kernel recorded",
-                         "peak_source": peak_src, "bytes_per_launch": gu_bytes, "us_per_launch": gu_us, "copy_ceiling_gbs": copy_gbs},
-            "step_bytes": {"total": step_bytes_max, "moe": sb.moe, "dense": sb.dense, "lm_head": sb.lm_head, "kv": sb.kv, "gdn_state": sb.gdn_state,
+                         "peak_source": peak_src, "bytes_per_launch": gu_bytes, "us_per_launch": gu_us, "copy_ceiling_gbs": copy_gbs,
+                         "weight_format": "IQ3X (the IQ3_S experts re-coded losslessly at load time, 136 bytes per 256 weights)" if iq3x else "IQ3_S (110 bytes per 256 weights)",
+                         "iq3s_equivalent_gbs": iq3s_bytes / (gu_us * 1e-6) / 1e9},
+            "step_bytes": {"total": step_bytes_max, "moe": sb.moe, "moe_in_iq3s_bytes": sb.moe_iq3s, "dense": sb.dense, "lm_head": sb.lm_head, "kv": sb.kv, "gdn_state": sb.gdn_state,
                            "scope": "one rank (the largest over ranks in total)" if world > 1 else "the GPU",
                            "unique_experts_per_layer": sb.unique_experts_sum / cfg.layers, "ctx_tokens": int(sb.ctx_tokens),
                            "step_roofline_ms": step_roof_ms, "step_frac_of_hbm_roofline": step_roof_ms / (dev_ms / K),

@@ -114,6 +114,8 @@ typedef struct {
     double moe, dense, lm_head, kv, gdn_state, other, total;
     int unique_experts_sum; /* sum over layers of distinct experts chosen in the last step */
     long long ctx_tokens;   /* sum of context lengths attended in the last step */
+    double moe_iq3s;        /* the MoE term counted in IQ3_S bytes (110 per 256 weights): equals `moe` unless the experts run from
+                             * their re-coded IQ3X form (136 per 256), in which case `moe` and `total` count the bytes actually read */
 } qw_step_bytes;
 void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *out);
 

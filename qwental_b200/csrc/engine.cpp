@@ -100,7 +100,12 @@ struct qw_engine {
     qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr, *k_topk = nullptr;
     // gate/up + down of the expert FFN in one launch (moe_ffn), where the shapes allow it; QW_MOE_FFN=split keeps the two launches
     bool ffn_fused = false;
-    qw_kernel *k_ffn = nullptr, *k_ffn_x = nullptr, *k_ffn_probe = nullptr;
+    // ... on expert weights re-coded once into the kernel's own stage order and bit layout (IQ3X, csrc/iq3x.cuh): lossless, 136
+    // instead of 110 bytes per 256 weights; QW_MOE_FFN=fused keeps the fused kernel on the raw IQ3_S blocks
+    bool ffn_iq3x = false;
+    qw_buf xq_gu{}, xq_d{}, xs_gu{}, xs_d{};  // routed gate+up / down and the shared expert's, per layer
+    size_t x_gus = 0, x_dns = 0;              // IQ3X bytes of one expert's gate+up / down
+    qw_kernel *k_ffn = nullptr, *k_ffn_x = nullptr, *k_ffn_probe = nullptr, *k_pack = nullptr;
     bool moe_probe = false;  // measurement only: the copy-only twin of moe_ffn runs in its place (outputs are not produced)
     // slot sharding on top of the fused exchange: attention / GDN (their projections included) run only for the rows whose
     // slot this rank owns (slot % ep_size == ep_rank); the out-projection stores its rows into every rank's `ob` and publishes
@@ -196,6 +201,30 @@ bool init_weights(qw_engine *e) {
     return true;
 }
 
+// Re-codes every layer's expert matrices (already in their IQ3_S buffers) into IQ3X for the fused expert-FFN kernel.
+bool pack_experts(qw_engine *e) {
+    const size_t gu_bytes = (size_t)e->I * e->rbD, ex_bytes = (size_t)e->EL * gu_bytes;
+    struct { uint32_t mode, experts, I, D; } a;
+    for (int l = 0; l < e->L; l++) {
+        qw_batch *b = qw_batch_begin(e->g, false);
+        auto enc = [&](uint32_t mode, uint32_t experts, const qw_buf *A, size_t ao, const qw_buf *B, size_t bo, const qw_buf *dst, size_t dofs) {
+            a = {mode, experts, (uint32_t)e->I, (uint32_t)e->D};
+            qw_batch_kernel(b, e->k_pack);
+            qw_batch_buf(b, 0, A, ao);
+            if (B) qw_batch_buf(b, 1, B, bo);
+            qw_batch_buf(b, 2, dst, dofs);
+            qw_batch_bytes(b, 3, &a, sizeof a);
+            qw_batch_dispatch(b, 1, 1, 1, 256, 1, 1);
+        };
+        enc(0, (uint32_t)e->EL, &e->exg, (size_t)l * ex_bytes, &e->exu, (size_t)l * ex_bytes, &e->xq_gu, (size_t)l * e->EL * e->x_gus);
+        enc(1, (uint32_t)e->EL, &e->exd, (size_t)l * ex_bytes, nullptr, 0, &e->xq_d, (size_t)l * e->EL * e->x_dns);
+        enc(0, 1, &e->shg, (size_t)l * gu_bytes, &e->shu, (size_t)l * gu_bytes, &e->xs_gu, (size_t)l * e->x_gus);
+        enc(1, 1, &e->shd, (size_t)l * gu_bytes, nullptr, 0, &e->xs_d, (size_t)l * e->x_dns);
+        if (qw_batch_end(b) < 0) return e->fail("re-coding of the expert weights failed at layer %d", l);
+    }
+    return true;
+}
+
 }  // namespace
 
 extern "C" void qw_model_cfg_default(qw_model_cfg *c) {
@@ -214,7 +243,7 @@ extern "C" void qw_engine_close(qw_engine *e) {
     if (!e) return;
     qw_buf *all[] = {&e->emb, &e->lm_head, &e->dense, &e->small, &e->router, &e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd, &e->kvpool,
                      &e->ptab, &e->sstate, &e->cstate, &e->ctl_h, &e->ctl_d, &e->h, &e->x, &e->proj, &e->cv, &e->la, &e->be, &e->gy, &e->qb,
-                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->cand_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt};
+                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->cand_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt, &e->xq_gu, &e->xq_d, &e->xs_gu, &e->xs_d};
     // mappings of the other ranks' exchange buffers go first (their owners free the memory), then this rank's own
     for (int r = 0; r < 8; r++)
         if (r != e->c.ep_rank && e->ep_peer[r].handle) qw_buf_free(&e->ep_peer[r]);
@@ -304,10 +333,14 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
         // one expert per block is the right grain when a rank has about as many chosen experts as SMs; with the experts spread
         // over several ranks the two-launch family, which cuts every expert into units for all blocks, is faster
         e->ffn_fused = e->D % 2048 == 0 && e->D <= 2048 && e->I == 512 && (c.ep_size == 1 || (fm && !strcmp(fm, "fused"))) && !(fm && !strcmp(fm, "split"));
+        e->ffn_iq3x = e->ffn_fused && !(fm && !strcmp(fm, "fused"));
         if (ok && e->ffn_fused) {
-            auto mp = md;
+            auto mf = md;
+            mf.push_back({"IQ3X", e->ffn_iq3x ? 1 : 0});
+            auto mp = mf;
             mp.push_back({"PROBE", 1});
-            ok = compile(e, "moe_ffn", "moe_ffn", md, &e->k_ffn) && compile(e, "moe_ffn", "moe_ffn_copy_probe", mp, &e->k_ffn_probe);
+            ok = compile(e, "moe_ffn", "moe_ffn", mf, &e->k_ffn) && compile(e, "moe_ffn", "moe_ffn_copy_probe", mp, &e->k_ffn_probe) &&
+                 (!e->ffn_iq3x || compile(e, "iq3x_pack", "iq3x_pack", {}, &e->k_pack));
         }
     }
     ok = ok && compile(e, "k_topk", "k_topk", {}, &e->k_topk);
@@ -344,7 +377,14 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     if (ok) ok = qw_buf_zero(g, &e->msel, 0, e->msel.size) && qw_buf_zero(g, &e->Pg, 0, e->Pg.size) && qw_buf_zero(g, &e->Hhi, 0, e->Hhi.size) &&
                  qw_buf_zero(g, &e->Hlo, 0, e->Hlo.size) && qw_buf_zero(g, &e->ptab, 0, e->ptab.size) &&
                  qw_buf_zero(g, &e->kvpool, 0, e->kvpool.size) && qw_buf_zero(g, &e->rcnt, 0, e->rcnt.size);  // rows past a slot's length are multiplied by probability 0: keep them finite
+    if (ok && e->ffn_iq3x) {
+        e->x_gus = (size_t)(e->I / 64) * (e->D / 512) * 128 * 272;
+        e->x_dns = (size_t)(e->D / 128) * (e->I / 512) * 128 * 272;
+        ok = new_buf(e, &e->xq_gu, (size_t)e->L * e->EL * e->x_gus) && new_buf(e, &e->xq_d, (size_t)e->L * e->EL * e->x_dns) &&
+             new_buf(e, &e->xs_gu, (size_t)e->L * e->x_gus) && new_buf(e, &e->xs_d, (size_t)e->L * e->x_dns);
+    }
     if (ok) ok = init_weights(e);
+    if (ok && e->ffn_iq3x) ok = pack_experts(e);
     if (!ok) {
         g_open_error = e->err.empty() ? "engine open failed" : e->err;
         qw_engine_close(e);
@@ -648,14 +688,21 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
                 enc_fill(e, b, &e->Pg, 0, z);
             }
             qw_batch_kernel(b, e->ep_fused ? e->k_ffn_x : e->moe_probe ? e->k_ffn_probe : e->k_ffn);  // gate/up, SiLU * up and down of every chosen expert in one launch
-            qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
-            qw_batch_buf(b, 1, &e->exu, (size_t)l * ex_bytes);
-            qw_batch_buf(b, 2, &e->shg, (size_t)l * gu_bytes);
-            qw_batch_buf(b, 3, &e->shu, (size_t)l * gu_bytes);
+            if (e->ffn_iq3x) {
+                qw_batch_buf(b, 0, &e->xq_gu, (size_t)l * e->EL * e->x_gus);
+                qw_batch_buf(b, 2, &e->xs_gu, (size_t)l * e->x_gus);
+                qw_batch_buf(b, 6, &e->xq_d, (size_t)l * e->EL * e->x_dns);
+                qw_batch_buf(b, 7, &e->xs_d, (size_t)l * e->x_dns);
+            } else {
+                qw_batch_buf(b, 0, &e->exg, (size_t)l * ex_bytes);
+                qw_batch_buf(b, 1, &e->exu, (size_t)l * ex_bytes);
+                qw_batch_buf(b, 2, &e->shg, (size_t)l * gu_bytes);
+                qw_batch_buf(b, 3, &e->shu, (size_t)l * gu_bytes);
+                qw_batch_buf(b, 6, &e->exd, (size_t)l * ex_bytes);
+                qw_batch_buf(b, 7, &e->shd, (size_t)l * gu_bytes);
+            }
             qw_batch_buf(b, 4, &e->x, 0);
             qw_batch_buf(b, 5, &e->msel, selo);
-            qw_batch_buf(b, 6, &e->exd, (size_t)l * ex_bytes);
-            qw_batch_buf(b, 7, &e->shd, (size_t)l * gu_bytes);
             bind_pg();
             qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
         } else {
@@ -987,7 +1034,9 @@ extern "C" void qw_engine_last_step_bytes(qw_engine *e, qw_step_bytes *o) {
         uint32_t U = 0;
         qw_buf_download(e->g, &e->msel, (size_t)l * e->sel_bytes, &U, 4);
         usum += (int)U;
-        o->moe += ((double)U + (e->c.ep_rank == 0 ? 1 : 0)) * 3 * gu + (double)(e->E + 1) * e->D * 2;  // the shared expert runs on rank 0
+        const double nexp = (double)U + (e->c.ep_rank == 0 ? 1 : 0);  // the shared expert runs on rank 0
+        o->moe += nexp * (e->ffn_iq3x ? (double)(e->x_gus + e->x_dns) : 3 * gu) + (double)(e->E + 1) * e->D * 2;
+        o->moe_iq3s += nexp * 3 * gu + (double)(e->E + 1) * e->D * 2;
         const LayerW &w = e->layers[l];
         o->dense += (double)w.n_in * e->rbD + (double)e->D * (w.attn ? e->rbKA : e->rbKG);
     }
@@ -1078,7 +1127,9 @@ extern "C" int qw_engine_ep_connect(qw_engine *e, const void *handles, int n) {
     }
     std::vector<std::pair<const char *, long>> md = {{"E", e->E}, {"EL", e->EL}, {"D", (long)e->D}, {"I", e->I}, {"TOPK", e->TOPK},
                                                       {"SHARED", e->c.ep_rank == 0 ? 1 : 0}, {"RESID", 0}, {"EPX", n}};
-    if ((e->ffn_fused && !compile(e, "moe_ffn", "moe_ffn_epx", md, &e->k_ffn_x)) || !compile(e, "moe_dn", "moe_dn_epx", md, &e->k_dn_x) ||
+    auto mfx = md;
+    mfx.push_back({"IQ3X", e->ffn_iq3x ? 1 : 0});
+    if ((e->ffn_fused && !compile(e, "moe_ffn", "moe_ffn_epx", mfx, &e->k_ffn_x)) || !compile(e, "moe_dn", "moe_dn_epx", md, &e->k_dn_x) ||
         !compile(e, "add_rmsnorm", "cmb_add_rmsnorm_epx", {{"CMB", 1}, {"TOPK", e->TOPK}, {"EPX", n}}, &e->k_norm_cmb_x))
         return -1;
     if (!qw_buf_zero(e->g, &e->rcnt, 64, 8)) return -1;

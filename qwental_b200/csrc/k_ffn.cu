@@ -18,6 +18,7 @@
 // come from padded shared-memory rows by one 16-byte load per sub-block; lanes whose column is absent load nothing.
 // Every wait is bounded (about two seconds); a warp that gives up records ST_MBAR_TIMEOUT and keeps walking the same
 // control flow without waiting again, so no barrier is ever left short of a participant.
+#include "iq3x.cuh"
 #include "moe_sel.h"
 #include "qmv_core.cuh"
 #include "qw_kern.h"
@@ -33,16 +34,21 @@ namespace {
 
 constexpr int FFN_CW = 16;                       // consumer warps
 constexpr int FFN_THREADS = (FFN_CW + 1) * 32;   // + the producer warp
-constexpr int FFN_STG = 3;
-constexpr int FFN_PF = 2;                        // whole tiles (56 - 112 KB) the L2 prefetch cursor runs ahead of the copies (QW_FFN_PF overrides)
-constexpr int FFN_PITCH = 240;                   // bytes between staged gate/up rows
-constexpr int FFN_SLOT = 128 * FFN_PITCH;        // 30720: also holds a down tile of 128 x 220 bytes
-constexpr int FFN_TAB = 65536;
-constexpr int FFN_OFF_TAB = 128;
-constexpr int FFN_MAXG = 520;                               // groups kept in shared memory: E <= 512 experts (+ end markers)
-constexpr int FFN_OFF_PRE = FFN_OFF_TAB + FFN_TAB;          // uint32 pre[FFN_MAXG], off[FFN_MAXG], ue[FFN_MAXG] of the selection record
-constexpr int FFN_OFF_RED = FFN_OFF_PRE + 3 * FFN_MAXG * 4 + 32;  // [2][8 row groups][32 lanes] float4  (6272 = 49 * 128)
-constexpr int FFN_OFF_XS = FFN_OFF_RED + 2 * 8 * 32 * 16;   // tokens of the pass, then H planes, then the stages
+constexpr int FFN_PF = 0;                        // whole tiles the optional L2 prefetch cursor runs ahead of the copies (QW_FFN_PF; measured: no gain)
+constexpr int FFN_PITCH = 240;                   // IQ3_S: bytes between staged gate/up rows
+constexpr int FFN_MAXG = 520;                    // groups kept in shared memory: E <= 512 experts (+ end markers)
+// Shared-memory plan per weight format.  FMT 0 = the raw IQ3_S blocks (64 KB codebook, three 30 KB stages); FMT 1 = IQ3X
+// (iq3x.cuh: no codebook, four 34 KB stages).
+template <int FMT>
+struct FfnCfg {
+    static constexpr int STG = FMT ? 4 : 3;
+    static constexpr int SLOT = FMT ? IQ3X_STAGE : 128 * FFN_PITCH;   // 30720 also holds an IQ3_S down tile of 128 x 220 bytes
+    static constexpr int TAB = FMT ? 0 : 65536;
+    static constexpr int OFF_TAB = 128;
+    static constexpr int OFF_PRE = OFF_TAB + TAB;                      // uint32 pre[FFN_MAXG], off[FFN_MAXG], ue[FFN_MAXG] of the selection record
+    static constexpr int OFF_RED = OFF_PRE + 3 * FFN_MAXG * 4 + 32;    // [2][8 row groups][32 lanes] float4  (6272 = 49 * 128)
+    static constexpr int OFF_XS = OFF_RED + 2 * 8 * 32 * 16;           // tokens of the pass, then H planes, then the stages
+};
 
 struct FfnP {
     const uint8_t *Wd, *Sd;   // routed down [E][D][rbI], shared expert's down [D][rbI] (nullptr: no shared expert)
@@ -61,6 +67,10 @@ struct FfnP {
 __device__ __forceinline__ void tma_box_2d(uint32_t dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm),
                  "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_s(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {  // 1-D bulk copy to a shared-space address
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
 __device__ __forceinline__ void bar_sync_n(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
@@ -166,16 +176,11 @@ __device__ __forceinline__ float row_sub(uint32_t blk_t, uint32_t blk_s, const R
     return fmaf(h.d2, (float)n, h.d);
 }
 // one sub-block of rows g (at u0) and g + 8 (at u1): PLANES = 1 for fp16 tokens, 2 for H as fp16 high + low
-template <int IB, int PLANES, int VAR>
+template <int IB, int PLANES>
 __device__ __forceinline__ void ffn_sub(uint32_t u0, uint32_t u1, int t, const RowHdr &h0, const RowHdr &h1, uint32_t tabl, const ZeroRegs &zr, uint32_t bh,
                                         uint32_t bl, uint32_t have, uint4 &xv, uint4 &xl, float (&acc)[4]) {
-    if (VAR == 1) {  // every lane loads: a lane whose column is absent reads its own (stale) row -- that column's results are never stored
-        xv = lds_v4(bh + IB * 64);
-        if (PLANES == 2) xl = lds_v4(bl + IB * 64);
-    } else {
-        lds_v4_if<IB * 64>(xv, bh, have);
-        if (PLANES == 2) lds_v4_if<IB * 64>(xl, bl, have);
-    }
+    lds_v4_if<IB * 64>(xv, bh, have);
+    if (PLANES == 2) lds_v4_if<IB * 64>(xl, bl, have);
     uint32_t wa[4], wb[4];
     const float dba = row_sub<IB>(u0 + 2 * t, u0 + t, h0, tabl, wa);
     const float dbb = row_sub<IB>(u1 + 2 * t, u1 + t, h1, tabl, wb);
@@ -193,34 +198,120 @@ __device__ __forceinline__ void ffn_sub(uint32_t u0, uint32_t u1, int t, const R
     acc[2] = fmaf(dbb, p[2], acc[2]);
     acc[3] = fmaf(dbb, p[3], acc[3]);
 }
-template <int PLANES, int VAR>
+template <int PLANES>
 __device__ __forceinline__ void ffn_unit(uint32_t u0, uint32_t u1, int t, uint32_t tabl, const ZeroRegs &zr, uint32_t bh, uint32_t bl, uint32_t have,
                                          float (&acc)[4]) {
     const RowHdr h0 = row_hdr(u0, t), h1 = row_hdr(u1, t);
     uint4 xv = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
-    ffn_sub<0, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<1, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<2, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<3, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<4, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<5, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<6, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
-    ffn_sub<7, PLANES, VAR>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<0, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<1, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<2, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<3, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<4, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<5, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<6, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+    ffn_sub<7, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
+}
+
+// ---- IQ3X units (iq3x.cuh): rec = shared address of the row record, kh = which super-block of the pair
+struct XHdr {
+    float d, d2;
+    uint32_t sclo, schi;
+};
+__device__ __forceinline__ XHdr x_hdr(uint32_t rec, int kh) {
+    XHdr h;
+    h.d = h2f((uint16_t)lds_u16<256>(rec + 2 * kh));
+    h.d2 = h.d + h.d;
+    uint32_t sc;
+    asm volatile("ld.shared.u32 %0, [%1+260];" : "=r"(sc) : "r"(rec + 4 * kh));
+    h.sclo = sc & 0x0f0f0f0fu;
+    h.schi = (sc >> 4) & 0x0f0f0f0fu;
+    return h;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u32_off(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+// Software-pipelined over the sub-blocks: the MMAs of sub-block i are issued, then the loads and the decode of sub-block
+// i + 1, then the scaling of sub-block i -- the MMA results are not waited for.  (The predicated B loads keep zeros in lanes
+// whose column is absent.)
+struct XDec {
+    uint32_t a0[4], a1[4];  // A fragments of the sub-block's two MMAs
+    float dba, dbb;         // scales of rows g and g + 8
+};
+template <int IB, int PLANES>
+__device__ __forceinline__ void x_load(uint32_t c0, uint32_t c1, uint32_t bh, uint32_t bl, uint32_t have, uint32_t (&q)[2], uint4 &xv, uint4 &xl) {
+    lds_v4_if<IB * 64>(xv, bh, have);
+    if (PLANES == 2) lds_v4_if<IB * 64>(xl, bl, have);
+    q[0] = lds_u32_off<IB * 16>(c0);
+    q[1] = lds_u32_off<IB * 16>(c1);
+}
+template <int IB>
+__device__ __forceinline__ void x_decode(const uint32_t (&q)[2], const XHdr &h0, const XHdr &h1, XDec &d) {
+    uint32_t wa[4], wb[4];
+    iq3x_word(q[0], wa);
+    iq3x_word(q[1], wb);
+    d.dba = fmaf(h0.d2, (float)__byte_perm(IB & 1 ? h0.schi : h0.sclo, 0, 0x4440 | (IB >> 1)), h0.d);
+    d.dbb = fmaf(h1.d2, (float)__byte_perm(IB & 1 ? h1.schi : h1.sclo, 0, 0x4440 | (IB >> 1)), h1.d);
+    d.a0[0] = wa[0]; d.a0[1] = wb[0]; d.a0[2] = wa[1]; d.a0[3] = wb[1];
+    d.a1[0] = wa[2]; d.a1[1] = wb[2]; d.a1[2] = wa[3]; d.a1[3] = wb[3];
+}
+template <int PLANES>
+__device__ __forceinline__ void x_mma(const XDec &d, const uint4 &xv, const uint4 &xl, const ZeroRegs &zr, float (&p)[4]) {
+    mma_f16(p, d.a0, xv.x, xv.y, zr.z);
+    mma_f16(p, d.a1, xv.z, xv.w, p);
+    if (PLANES == 2) {
+        mma_f16(p, d.a0, xl.x, xl.y, p);
+        mma_f16(p, d.a1, xl.z, xl.w, p);
+    }
+}
+// rec0 / rec1: row records of MMA rows g and g + 8
+template <int PLANES>
+__device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int t, const ZeroRegs &zr, uint32_t bh, uint32_t bl, uint32_t have, float (&acc)[4]) {
+    const uint32_t c0 = rec0 + kh * 128 + t * 4, c1 = rec1 + kh * 128 + t * 4;
+    uint32_t q[2];
+    uint4 xv = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
+    XDec dec;
+    float p[4], sa, sb;
+    x_load<0, PLANES>(c0, c1, bh, bl, have, q, xv, xl);
+    const XHdr h0 = x_hdr(rec0, kh), h1 = x_hdr(rec1, kh);
+    x_decode<0>(q, h0, h1, dec);
+#define X_STEP(IB)                                               \
+    x_mma<PLANES>(dec, xv, xl, zr, p);                           \
+    x_load<IB + 1, PLANES>(c0, c1, bh, bl, have, q, xv, xl);     \
+    sa = dec.dba; sb = dec.dbb;                                  \
+    x_decode<IB + 1>(q, h0, h1, dec);                            \
+    acc[0] = fmaf(sa, p[0], acc[0]); acc[1] = fmaf(sa, p[1], acc[1]); acc[2] = fmaf(sb, p[2], acc[2]); acc[3] = fmaf(sb, p[3], acc[3]);
+    X_STEP(0)
+    X_STEP(1)
+    X_STEP(2)
+    X_STEP(3)
+    X_STEP(4)
+    X_STEP(5)
+    X_STEP(6)
+#undef X_STEP
+    x_mma<PLANES>(dec, xv, xl, zr, p);
+    acc[0] = fmaf(dec.dba, p[0], acc[0]); acc[1] = fmaf(dec.dba, p[1], acc[1]); acc[2] = fmaf(dec.dbb, p[2], acc[2]); acc[3] = fmaf(dec.dbb, p[3], acc[3]);
 }
 
 // PROBE = true is the copy-only twin used to measure what the staging pipeline alone can deliver: the same items, the same
 // TMA boxes and bulk copies through the same ring, but the consumers only read every staged byte once (16-byte loads) and
 // compute nothing -- the role of the reference's pure-read probes (bench/moe_bw.c:1-3, bench/qmv.c:357-382).
-template <bool PROBE, int VAR>
+// (17 warps put five on one scheduler, whose 16 K registers then allow 96 per thread)
+template <bool PROBE, int FMT>
 __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
                                                            const __grid_constant__ CUtensorMap mSG, const __grid_constant__ CUtensorMap mSU, const FfnP p) {
+    using C = FfnCfg<FMT>;
+    constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
     uint64_t *full = bars, *empty = bars + FFN_STG, *tab_bar = bars + 2 * FFN_STG, *xfull = tab_bar + 1, *xfree = tab_bar + 2;
-    uint32_t *pre = (uint32_t *)(smem + FFN_OFF_PRE);
-    float4 *red = (float4 *)(smem + FFN_OFF_RED);
+    uint32_t *pre = (uint32_t *)(smem + C::OFF_PRE);
+    float4 *red = (float4 *)(smem + C::OFF_RED);
     const uint32_t xpitch = p.D * 2 + 64, hpitch = p.I * 2 + 64;
-    uint8_t *xs = smem + FFN_OFF_XS, *hs = xs + 8 * xpitch, *stage0 = hs + 16 * hpitch;
+    uint8_t *xs = smem + C::OFF_XS, *hs = xs + 8 * xpitch, *stage0 = hs + 16 * hpitch;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const uint32_t KP = p.D / 512, GT = p.I / 64, DT = p.D / 128, KU = p.I / 256;
 
@@ -234,8 +325,10 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
         mbar_init(xfull, 1);
         mbar_init(xfree, FFN_CW);
         mbar_init_fence();
-        mbar_expect_tx(tab_bar, FFN_TAB);
-        bulk_g2s(smem + FFN_OFF_TAB, p.tab->grid_u32x32, FFN_TAB, tab_bar);
+        if (FMT == 0) {
+            mbar_expect_tx(tab_bar, C::TAB);
+            bulk_g2s(smem + C::OFF_TAB, p.tab->grid_u32x32, C::TAB, tab_bar);
+        }
     }
     pdl_wait();  // the selection record, the tokens and Pg belong to earlier kernels
     const moe_sel *ms = p.ms;
@@ -280,9 +373,14 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 c.erow = it.shared ? 0 : (pre[2 * FFN_MAXG + it.u] - p.ebase);
                 c.tg = it.shared ? &mSG : &mG;
                 c.tu = it.shared ? &mSU : &mU;
-                c.wg = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * p.I * p.rbD;
-                c.wu = (it.shared ? p.Su : p.Wu) + (size_t)c.erow * p.I * p.rbD;
-                c.wd = it.shared ? p.Sd : p.Wd + (size_t)c.erow * p.D * p.rbI;
+                if (FMT == 0) {
+                    c.wg = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * p.I * p.rbD;
+                    c.wu = (it.shared ? p.Su : p.Wu) + (size_t)c.erow * p.I * p.rbD;
+                    c.wd = it.shared ? p.Sd : p.Wd + (size_t)c.erow * p.D * p.rbI;
+                } else {  // IQ3X: stage-ordered records, gate and up interleaved in one buffer
+                    c.wg = c.wu = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * GT * KP * IQ3X_STAGE;
+                    c.wd = (it.shared ? p.Sd : p.Wd) + (size_t)c.erow * DT * (p.I / 512) * IQ3X_STAGE;
+                }
                 return c;
             };
             auto l2_prefetch = [](const uint8_t *ptr, uint32_t bytes) {
@@ -293,7 +391,10 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             if (pw < items) pc = src_of(pw);
             auto prefetch_next = [&]() {
                 if (pw >= items) return;
-                if (pu < GT) {
+                if (FMT == 1) {
+                    if (pu < GT) l2_prefetch(pc.wg + (size_t)pu * KP * IQ3X_STAGE, KP * IQ3X_STAGE);
+                    else l2_prefetch(pc.wd + (size_t)(pu - GT) * 2 * IQ3X_STAGE, 2 * IQ3X_STAGE);
+                } else if (pu < GT) {
                     l2_prefetch(pc.wg + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
                     l2_prefetch(pc.wu + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
                 } else {
@@ -323,14 +424,16 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 for (uint32_t gt = 0; gt < GT; gt++) {
                     if (p.pf) prefetch_next();
                     for (uint32_t kp = 0; kp < KP; kp++, j++) {
-                        const uint32_t dst = slot_for(2 * 64 * FFN_PITCH);
+                        const uint32_t dst = slot_for(FMT ? IQ3X_STAGE : 2 * 64 * FFN_PITCH);
+                        if (FMT == 1) {  // one contiguous stage
+                            bulk_s(dst, sc.wg + ((size_t)gt * KP + kp) * IQ3X_STAGE, IQ3X_STAGE, &full[j % FFN_STG]);
+                            continue;
+                        }
                         const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * p.I + gt * 64);
                         if (PROBE && p.probe1d) {  // measurement only: the same bytes per stage as two contiguous runs instead of two boxes
                             const size_t o = ((size_t)gt * KP + kp) * 64 * FFN_PITCH;
-                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                                         "l"(sc.wg + o), "r"(64 * FFN_PITCH), "r"(smem_u32(&full[j % FFN_STG])) : "memory");
-                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + 64 * FFN_PITCH),
-                                         "l"(sc.wu + o), "r"(64 * FFN_PITCH), "r"(smem_u32(&full[j % FFN_STG])) : "memory");
+                            bulk_s(dst, sc.wg + o, 64 * FFN_PITCH, &full[j % FFN_STG]);
+                            bulk_s(dst + 64 * FFN_PITCH, sc.wu + o, 64 * FFN_PITCH, &full[j % FFN_STG]);
                             continue;
                         }
                         tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
@@ -339,19 +442,18 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 }
                 for (uint32_t dt = 0; dt < DT; dt++, j++) {
                     if (p.pf && !(dt & 1)) prefetch_next();
-                    const uint32_t dst = slot_for(128 * p.rbI);
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                                 "l"(sc.wd + (size_t)dt * 128 * p.rbI), "r"(128 * p.rbI), "r"(smem_u32(&full[j % FFN_STG]))
-                                 : "memory");
+                    const uint32_t bytes = FMT ? IQ3X_STAGE : 128 * p.rbI;
+                    const uint32_t dst = slot_for(bytes);
+                    bulk_s(dst, sc.wd + (size_t)dt * bytes, bytes, &full[j % FFN_STG]);
                 }
             }
         }
     } else {
         // ---- consumers
         const int r = warp & 7, kh = warp >> 3;
-        bool ok = mbar_wait(tab_bar, 0);
+        bool ok = FMT == 0 ? mbar_wait(tab_bar, 0) : true;
         if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 8);
-        const uint32_t tabl = smem_u32(smem + FFN_OFF_TAB) + lane * 4;  // this lane's copy of the interleaved codebook
+        const uint32_t tabl = smem_u32(smem + C::OFF_TAB) + lane * 4;  // this lane's copy of the interleaved codebook
         const ZeroRegs zr = zero_regs();
         const uint32_t xb0 = smem_u32(xs) + g * xpitch + t * 16;
         const uint32_t hb0 = smem_u32(hs) + g * hpitch + t * 16;
@@ -411,7 +513,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             if (PROBE) {
                 uint32_t sink = 0;
                 for (uint32_t sidx = 0; sidx < GT * KP + DT; sidx++) {
-                    const uint32_t st = wait_full(), bytes = sidx < GT * KP ? 128 * FFN_PITCH : 128 * p.rbI;
+                    const uint32_t st = wait_full(), bytes = FMT ? IQ3X_STAGE : sidx < GT * KP ? 128 * FFN_PITCH : 128 * p.rbI;
                     for (uint32_t o = (warp * 32 + lane) * 16; o < bytes; o += FFN_CW * 32 * 16) {
                         const uint4 v = lds_v4(st + o);
                         sink ^= v.x ^ v.y ^ v.z ^ v.w;
@@ -428,9 +530,14 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 for (uint32_t kp = 0; kp < KP; kp++) {
                     const uint32_t st = wait_full();
-                    const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
                     const uint32_t bx = xb0 + (2 * kp + kh) * 512;
-                    ffn_unit<1, VAR>(u0, u1, t, tabl, zr, bx, bx, have, acc);
+                    if (FMT == 1) {
+                        const uint32_t rec0 = st + (8 * r + g) * IQ3X_REC;
+                        x_unit<1>(rec0, rec0 + 64 * IQ3X_REC, kh, t, zr, bx, bx, have, acc);
+                    } else {
+                        const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
+                        ffn_unit<1>(u0, u1, t, tabl, zr, bx, bx, have, acc);
+                    }
                     release();
                 }
                 pair_sum(acc);
@@ -459,9 +566,14 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 const uint32_t st = wait_full();
                 for (uint32_t ks = kh; ks < KU; ks += 2) {
-                    const uint32_t u0 = st + (16 * r + 2 * g) * p.rbI + ks * 110, u1 = u0 + p.rbI;
                     const uint32_t bh = hb0 + ks * 512, bl = bh + 8 * hpitch;
-                    ffn_unit<2, VAR>(u0, u1, t, tabl, zr, bh, bl, have, acc);
+                    if (FMT == 1) {  // positions 16 r + g and 16 r + 8 + g hold output rows 16 r + 2 g and 16 r + 2 g + 1
+                        const uint32_t rec0 = st + (16 * r + g) * IQ3X_REC;
+                        x_unit<2>(rec0, rec0 + 8 * IQ3X_REC, kh, t, zr, bh, bl, have, acc);
+                    } else {
+                        const uint32_t u0 = st + (16 * r + 2 * g) * p.rbI + ks * 110, u1 = u0 + p.rbI;
+                        ffn_unit<2>(u0, u1, t, tabl, zr, bh, bl, have, acc);
+                    }
                 }
                 release();
                 pair_sum(acc);
@@ -528,21 +640,26 @@ const CUtensorMap *ffn_tensor_map(const void *base, uint64_t pitch, uint64_t row
 // 4 = x fp16 [nb][D], 5 = moe_sel, 6 = routed down [EL][D][rbI], 7 = shared down, 9 = Pg fp32 [64][TOPK+1][D],
 // 10 = id of the first expert held in the weight buffers (optional, default 0); with EPX = ranks also 11, 12, 16 + r,
 // 24 + r as for moe_dn.  defines: E, D, I, TOPK, EL, SHARED, EPX.  The host's grid and block are ignored.
+// With IQ3X defined 1 the weights are the re-coded form of iq3x.cuh (made by iq3x_pack): 0 = routed gate + up
+// [EL][I/64][D/512] stages, 2 = the shared expert's, 6 = routed down [EL][D/128][I/512] stages, 7 = the shared expert's;
+// binds 1 and 3 are not used.
 static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     FfnP p{};
     const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
+    const bool x4 = L.def("IQ3X", 0) != 0;
     p.D = (uint32_t)L.def("D", 2048);
     p.I = (uint32_t)L.def("I", 512);
     QW_CHECK_ARG(p.D % 2048 == 0 && p.I == 512 && topk < MOE_MAXK && E <= 512);
     p.rbD = p.D / 256 * 110;
     p.rbI = p.I / 256 * 110;
-    const size_t smem = FFN_OFF_XS + (size_t)8 * (p.D * 2 + 64) + (size_t)16 * (p.I * 2 + 64) + (size_t)FFN_STG * FFN_SLOT;
-    QW_CHECK_ARG(smem <= 227 * 1024 && 128 * p.rbI <= FFN_SLOT && (128 * p.rbI) % 16 == 0);
+    const size_t act = (size_t)8 * (p.D * 2 + 64) + (size_t)16 * (p.I * 2 + 64);
+    const size_t smem = x4 ? FfnCfg<1>::OFF_XS + act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT : FfnCfg<0>::OFF_XS + act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
+    QW_CHECK_ARG(smem <= 227 * 1024 && 128 * p.rbI <= FfnCfg<0>::SLOT && (128 * p.rbI) % 16 == 0);
     const bool shared = L.def("SHARED", 1) != 0;
     const uint32_t EL = (uint32_t)L.def("EL", E);
     p.ebase = L.has_bytes(10, 4) ? L.bytes<uint32_t>(10) : 0;
     QW_CHECK_ARG(EL >= 1 && p.ebase + EL <= E);
-    const uint8_t *Wg = L.buf<uint8_t>(0), *Wu = L.buf<uint8_t>(1), *Sg = shared ? L.buf<uint8_t>(2) : nullptr, *Su = shared ? L.buf<uint8_t>(3) : nullptr;
+    const uint8_t *Wg = L.buf<uint8_t>(0), *Wu = x4 ? Wg : L.buf<uint8_t>(1), *Sg = shared ? L.buf<uint8_t>(2) : nullptr, *Su = !shared ? nullptr : x4 ? Sg : L.buf<uint8_t>(3);
     p.Wd = L.buf<uint8_t>(6);
     p.Wg = Wg; p.Wu = Wu; p.Sg = Sg; p.Su = Su;
     p.Sd = shared ? L.buf<uint8_t>(7) : nullptr;
@@ -551,9 +668,15 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     p.Pg = L.buf<float>(9);
     p.tab = (const QwTables *)L.tables;
     p.status = L.status;
-    const size_t wsz = (size_t)EL * p.I * p.rbD, ssz = (size_t)p.I * p.rbD;
-    QW_CHECK_ARG(Wg && Wu && p.Wd && p.x && p.ms && p.Pg && L.avail(0) >= wsz && L.avail(1) >= wsz && L.avail(6) >= wsz && L.avail(5) >= sizeof(moe_sel));
-    QW_CHECK_ARG(!shared || (Sg && Su && p.Sd && L.avail(2) >= ssz && L.avail(3) >= ssz && L.avail(7) >= ssz));
+    QW_CHECK_ARG(Wg && Wu && p.Wd && p.x && p.ms && p.Pg && L.avail(5) >= sizeof(moe_sel));
+    QW_CHECK_ARG(!shared || (Sg && Su && p.Sd));
+    if (x4) {
+        const size_t gus = (size_t)(p.I / 64) * (p.D / 512) * IQ3X_STAGE, dns = (size_t)(p.D / 128) * (p.I / 512) * IQ3X_STAGE;
+        QW_CHECK_ARG(L.avail(0) >= EL * gus && L.avail(6) >= EL * dns && (!shared || (L.avail(2) >= gus && L.avail(7) >= dns)));
+    } else {
+        const size_t wsz = (size_t)EL * p.I * p.rbD, ssz = (size_t)p.I * p.rbD;
+        QW_CHECK_ARG(L.avail(0) >= wsz && L.avail(1) >= wsz && L.avail(6) >= wsz && (!shared || (L.avail(2) >= ssz && L.avail(3) >= ssz && L.avail(7) >= ssz)));
+    }
     QW_CHECK_ARG((((uintptr_t)Wg | (uintptr_t)Wu | (uintptr_t)p.Wd | (uintptr_t)Sg | (uintptr_t)Su | (uintptr_t)p.Sd | (uintptr_t)p.x) & 15) == 0);
     QW_CHECK_ARG(L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4 && L.avail(4) >= (size_t)p.D * 2);
     p.ep = EpPeers{};
@@ -571,9 +694,15 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
             QW_CHECK_ARG(p.PgR[r] && p.ep.flagR[r] && L.avail(24 + r) >= p.ep.nranks * 4 && L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
         }
     }
-    const CUtensorMap *mG = ffn_tensor_map(Wg, p.rbD, (uint64_t)EL * p.I), *mU = ffn_tensor_map(Wu, p.rbD, (uint64_t)EL * p.I);
-    const CUtensorMap *mSG = shared ? ffn_tensor_map(Sg, p.rbD, p.I) : mG, *mSU = shared ? ffn_tensor_map(Su, p.rbD, p.I) : mU;
-    QW_CHECK_ARG(mG && mU && mSG && mSU);
+    static const CUtensorMap no_map{};  // IQ3X stages are contiguous: no tensor maps
+    const CUtensorMap *mG = &no_map, *mU = &no_map, *mSG = &no_map, *mSU = &no_map;
+    if (!x4) {
+        mG = ffn_tensor_map(Wg, p.rbD, (uint64_t)EL * p.I);
+        mU = ffn_tensor_map(Wu, p.rbD, (uint64_t)EL * p.I);
+        mSG = shared ? ffn_tensor_map(Sg, p.rbD, p.I) : mG;
+        mSU = shared ? ffn_tensor_map(Su, p.rbD, p.I) : mU;
+        QW_CHECK_ARG(mG && mU && mSG && mSU);
+    }
     static const int pf_env = getenv("QW_FFN_PF") ? atoi(getenv("QW_FFN_PF")) : FFN_PF;
     p.pf = (uint32_t)(pf_env < 0 ? 0 : pf_env > 64 ? 64 : pf_env);
     p.probe1d = getenv("QW_FFN_PROBE_1D") ? 1 : 0;
@@ -581,8 +710,8 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     p.hint = (uint32_t)(hint_env < 0 ? 0 : hint_env);
     p.dbg = L.def("DBG", 0) ? L.buf<unsigned long long>(13) : nullptr;
     if (L.def("DBG", 0)) QW_CHECK_ARG(p.dbg && L.avail(13) >= 64);
-    static const int var_env = getenv("QW_FFN_VAR") ? atoi(getenv("QW_FFN_VAR")) : 0;
-    auto kern = L.def("PROBE", 0) ? moe_ffn_k<true, 0> : var_env == 1 ? moe_ffn_k<false, 1> : moe_ffn_k<false, 0>;  // PROBE defined 1: the copy-only twin (outputs are not written)
+    const bool probe = L.def("PROBE", 0) != 0;  // PROBE defined 1: the copy-only twin (outputs are not written)
+    auto kern = x4 ? (probe ? moe_ffn_k<true, 1> : moe_ffn_k<false, 1>) : (probe ? moe_ffn_k<true, 0> : moe_ffn_k<false, 0>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     qw_launch(kern, L.sm_count, FFN_THREADS, smem, L.stream, *mG, *mU, *mSG, *mSU, p);

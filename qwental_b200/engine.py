@@ -18,7 +18,7 @@ class ModelCfg(C.Structure):
 
 class StepBytes(C.Structure):
     _fields_ = [(n, C.c_double) for n in ("moe", "dense", "lm_head", "kv", "gdn_state", "other", "total")] + \
-               [("unique_experts_sum", C.c_int), ("ctx_tokens", C.c_longlong)]
+               [("unique_experts_sum", C.c_int), ("ctx_tokens", C.c_longlong), ("moe_iq3s", C.c_double)]
 
 
 def _bind(L):

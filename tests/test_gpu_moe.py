@@ -51,11 +51,12 @@ def run_layer(gpu, layer, x, fused_route=False):
     return ob.download(np.float16, nb * layer.D).reshape(nb, layer.D)
 
 
-@pytest.mark.parametrize("ffn", ["fused", "split"])
+@pytest.mark.parametrize("ffn", ["iq3x", "fused", "split"])
 @pytest.mark.parametrize("E,B", [(64, 16), (64, 1), (64, 64), (512, 16)])
 def test_moe_layer_parity(gpu, E, B, ffn):
-    """ffn = "fused": gate/up + down in one launch with H in shared memory (what the engine runs at these shapes);
-    "split": the two-launch family that serves every other shape."""
+    """ffn = "iq3x": gate/up + down in one launch with H in shared memory, on expert weights re-coded once into the kernel's
+    own layout (what the engine runs at these shapes); "fused": the same kernel on the raw IQ3_S blocks; "split": the
+    two-launch family that serves every other shape."""
     D, I, topk = 2048, 512, 10
     layer, h, _ = make_layer(gpu, E, D, I, topk, seed=10 + E, ffn=ffn)
     x = synth.acts_fp16(np.random.default_rng(B), B, D)
@@ -89,7 +90,7 @@ def test_moe_layer_parity(gpu, E, B, ffn):
             assert set(ids64[t]) == set(ids[t])
 
 
-@pytest.mark.parametrize("ffn", ["fused", "split"])
+@pytest.mark.parametrize("ffn", ["iq3x", "fused", "split"])
 def test_moe_batched_equals_alone(gpu, ffn):
     D, I, topk, E, B = 2048, 512, 10, 64, 24
     layer, h, _ = make_layer(gpu, E, D, I, topk, seed=3, ffn=ffn)
@@ -104,7 +105,7 @@ def test_moe_batched_equals_alone(gpu, ffn):
     assert all(np.array_equal(outs[i].view(np.uint16), out[0].view(np.uint16)) for i in range(20))
 
 
-@pytest.mark.parametrize("ffn", ["fused", "split"])
+@pytest.mark.parametrize("ffn", ["iq3x", "fused", "split"])
 def test_moe_expert_range_partitions_the_work(gpu, ffn):
     """Expert-parallel building block: with experts restricted to [lo, hi) each part writes only its own
     (token, rank) rows; the union over a partition equals the full layer's rows bit for bit."""
@@ -177,3 +178,28 @@ def test_selection_with_equal_logits_takes_lowest_ids(gpu):
         assert np.array_equal(ids[:6, :topk], ref_ids), fused
         assert list(ids[0, :topk]) == list(range(topk))
         assert np.abs(w[:6, :topk] - ref_w).max() < 1e-6
+
+
+def test_iq3x_recoding_is_lossless(gpu):
+    """iq3x_pack followed by the IQ3X decoder gives, bit for bit, what the CPU oracle decodes from the original IQ3_S blocks
+    (the oracle itself is pinned against gguf and the reference's decoder): the re-coding keeps every weight's exact value.
+    Edge blocks included: all-zero and all-one fields, largest scales, every sign pattern."""
+    from qwental_b200.layers import u32
+    rng = np.random.default_rng(77)
+    rows, K = 256, 1024
+    W = synth.iq3s_rows(rng, rows, K, 1.0).copy()
+    blk = W.reshape(rows, K // 256, 110)
+    blk[0, 0, 2:110] = 0          # every index 0, no signs, scale 0
+    blk[1, 0, 2:110] = 255        # every index 511, all signs, scale 15
+    blk[2, 1, 74:106] = 0xAA      # alternating signs
+    blk[3, 2, 66:74] = 0x55       # alternating codebook high bits
+    src = gpu.buf_from(W)
+    dst = gpu.buf((rows // 128) * (K // 512) * 128 * 272)
+    y = gpu.buf(rows * K * 4)
+    bt = gpu.batch()
+    bt.kernel(gpu.compile("iq3x_pack", "iq3x_pack")).buf(0, src).buf(2, dst).bytes(3, u32(1, 1, K, rows)).dispatch((1,), (256,))
+    bt.kernel(gpu.compile("iq3x_dq_test", "iq3x_dq_test")).buf(0, dst).buf(1, y).bytes(2, u32(rows, K)).dispatch((1,), (128,))
+    bt.end()
+    got = y.download(np.float32, rows * K).reshape(rows, K)
+    ref = orc.dq_rows(orc.IQ3_S, W, K)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
