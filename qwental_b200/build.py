@@ -19,8 +19,7 @@ OUT = os.path.join(HERE, "_build")
 LIB = os.path.join(OUT, "libqw_gpu_cuda.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
-         "-ccbin", "/usr/bin/g++", "-I", os.path.join(ROOT, "include"), "--use_fast_math=false"]
-FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]
+         "-ccbin", "/usr/bin/g++", "-I", os.path.join(ROOT, "include")]
 
 
 def _newer(src: str, dst: str, deps) -> bool:

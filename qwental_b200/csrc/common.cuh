@@ -38,6 +38,13 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     return v;
 }
 
+// ---- flags between the blocks of one kernel
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // ---- exchange between the ranks of one machine through peer memory: a producing kernel stores its rows into every rank's
 // buffer and then publishes; the consuming kernel waits until every rank has published the same step.
 struct EpPeers {
@@ -112,30 +119,6 @@ __device__ __forceinline__ void ep_wait(const unsigned *flags, const unsigned *s
         }
     }
     __syncthreads();
-}
-
-// The same with a suspend-time hint: the warp may sleep inside the instruction for up to hint_ns and wakes when the phase
-// completes, so a waiting warp issues few instructions (its polls would otherwise take issue slots from the working warps).
-__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, unsigned parity, unsigned hint_ns) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_hint(uint64_t *bar, unsigned parity, unsigned hint_ns) {
-    for (int i = 0; i < 64; i++)
-        if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
-    const uint64_t t0 = global_ns();
-    for (;;) {
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
-        if (global_ns() - t0 > 2000000000ull) return false;
-    }
 }
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {

@@ -14,6 +14,7 @@
 //     as CUDA graphs.
 #include "../../include/qw_engine.h"
 #include "../../include/qw_gpu_ext.h"
+#include "moe_sel.h"
 
 #include <algorithm>
 #include <cstdarg>
@@ -104,6 +105,7 @@ struct qw_engine {
     // instead of 110 bytes per 256 weights; QW_MOE_FFN=fused keeps the fused kernel on the raw IQ3_S blocks
     bool ffn_iq3x = false;
     qw_buf xq_gu{}, xq_d{}, xs_gu{}, xs_d{};  // routed gate+up / down and the shared expert's, per layer
+    qw_buf ffn_scr{};  // moe_ffn's scratch (moe_sel.h): per-item counters, zero between launches, and H
     size_t x_gus = 0, x_dns = 0;              // IQ3X bytes of one expert's gate+up / down
     qw_kernel *k_ffn = nullptr, *k_ffn_x = nullptr, *k_ffn_probe = nullptr, *k_pack = nullptr;
     bool moe_probe = false;  // measurement only: the copy-only twin of moe_ffn runs in its place (outputs are not produced)
@@ -243,7 +245,7 @@ extern "C" void qw_engine_close(qw_engine *e) {
     if (!e) return;
     qw_buf *all[] = {&e->emb, &e->lm_head, &e->dense, &e->small, &e->router, &e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd, &e->kvpool,
                      &e->ptab, &e->sstate, &e->cstate, &e->ctl_h, &e->ctl_d, &e->h, &e->x, &e->proj, &e->cv, &e->la, &e->be, &e->gy, &e->qb,
-                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->cand_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt, &e->xq_gu, &e->xq_d, &e->xs_gu, &e->xs_d};
+                     &e->part, &e->ya, &e->ob, &e->mo, &e->logits, &e->ids, &e->ids_h, &e->logits_h, &e->cand_h, &e->mlog, &e->msel, &e->Hhi, &e->Hlo, &e->Pg, &e->rcnt, &e->xq_gu, &e->xq_d, &e->xs_gu, &e->xs_d, &e->ffn_scr};
     // mappings of the other ranks' exchange buffers go first (their owners free the memory), then this rank's own
     for (int r = 0; r < 8; r++)
         if (r != e->c.ep_rank && e->ep_peer[r].handle) qw_buf_free(&e->ep_peer[r]);
@@ -377,6 +379,7 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     if (ok) ok = qw_buf_zero(g, &e->msel, 0, e->msel.size) && qw_buf_zero(g, &e->Pg, 0, e->Pg.size) && qw_buf_zero(g, &e->Hhi, 0, e->Hhi.size) &&
                  qw_buf_zero(g, &e->Hlo, 0, e->Hlo.size) && qw_buf_zero(g, &e->ptab, 0, e->ptab.size) &&
                  qw_buf_zero(g, &e->kvpool, 0, e->kvpool.size) && qw_buf_zero(g, &e->rcnt, 0, e->rcnt.size);  // rows past a slot's length are multiplied by probability 0: keep them finite
+    if (ok && e->ffn_fused) ok = new_buf(e, &e->ffn_scr, MOE_FFN_SCRATCH_BYTES(e->I)) && qw_buf_zero(g, &e->ffn_scr, 0, e->ffn_scr.size);
     if (ok && e->ffn_iq3x) {
         e->x_gus = (size_t)(e->I / 64) * (e->D / 512) * 128 * 272;
         e->x_dns = (size_t)(e->D / 128) * (e->I / 512) * 128 * 272;
@@ -703,6 +706,7 @@ void encode_step(qw_engine *e, qw_batch *b, uint32_t nb, uint32_t max_chunks, bo
             }
             qw_batch_buf(b, 4, &e->x, 0);
             qw_batch_buf(b, 5, &e->msel, selo);
+            qw_batch_buf(b, 8, &e->ffn_scr, 0);
             bind_pg();
             qw_batch_dispatch(b, e->I / 16, nb * e->TOPK + 1, 1, 256, 1, 1);
         } else {

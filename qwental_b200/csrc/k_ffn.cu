@@ -1,23 +1,31 @@
-// MoE expert FFN in one launch: gate/up, SiLU * up and the down projection of every (expert, pass of 8 tokens) item,
-// with H = silu(gate x) * (up x) kept in shared memory between the two halves.  Replaces the reference's moe_gu_gg +
-// moe_dn_gg pair (kernels/moe_gg.metal:600-652; host src/engine.c:568-646) for the benchmark shapes (D a multiple of
-// 2048 that fits, I = 512); the two-launch family in k_moe.cu stays for every other shape.
+// MoE expert FFN in one launch: gate/up, SiLU * up and the down projection of every (expert, pass of 8 tokens) item.
+// Replaces the reference's moe_gu_gg + moe_dn_gg pair (kernels/moe_gg.metal:600-652; host src/engine.c:568-646) for the
+// benchmark shapes (D = 2048, I = 512); the two-launch family in k_moe.cu stays for every other shape.
 //
-// Structure.  A work item is one pass (up to 8 token columns) of one distinct expert, or of the shared expert; items are
-// dealt round-robin to persistent blocks (one per SM).  A block is 16 consumer warps + 1 producer warp around a ring of
-// three 30 KB stages:
-//   gate/up   stage = 64 gate rows + 64 up rows of the expert x 512 K values: two 2-D tiled TMA boxes of 64 rows x 240
-//             bytes (two 110-byte super-blocks plus what 16-byte alignment of the box start costs).  Rows land 240 bytes
-//             apart, so the eight rows a warp instruction touches fall into eight different groups of four banks.
-//   down      stage = 128 rows of the down matrix over all of K = 512 (rows are contiguous: one 1-D bulk copy).
-// Consumer warp w = (row group r = w % 8, K half kh = w / 8) owns 16 MMA rows of the stage and one of the stage's two
-// super-blocks; the accumulators live across the stages of a tile, and the two K halves of a row group meet once per
-// tile through shared memory (always low half + high half: the order never depends on the batch).  In the gate/up
-// half MMA row g is gate row 8r + g and row g + 8 is the up row of the same intermediate index, so a lane holds both
-// factors of H and no exchange between row groups exists.  B operands (the tokens, then H as fp16 high + low planes)
-// come from padded shared-memory rows by one 16-byte load per sub-block; lanes whose column is absent load nothing.
-// Every wait is bounded (about two seconds); a warp that gives up records ST_MBAR_TIMEOUT and keeps walking the same
-// control flow without waiting again, so no barrier is ever left short of a participant.
+// Work.  An item is one pass (up to 8 token columns) of one distinct expert, or of the shared expert.  A decode step of 16
+// slots touches about a hundred items -- fewer than there are SMs, and far fewer when the experts are spread over ranks --
+// so an item is cut into pieces: GT gate/up pieces (64 intermediate indices each, all of K = D) and DT down pieces (128
+// output rows each, all of K = I).  Persistent blocks (one per SM) take an even, contiguous share of the gate/up piece
+// list, then an even share of the down piece list.  H = silu(gate x) * (up x) travels from the blocks that ran an item's
+// gate/up pieces to the blocks that run its down pieces through a small global buffer (it stays in L2) and a per-item
+// counter: a block only ever waits for H after it has finished all of its own gate/up pieces, so every wait is on blocks
+// that are running and never wait themselves.  The arithmetic of a piece does not depend on which block runs it.
+//
+// A block is 16 consumer warps + 1 producer warp around a ring of weight stages:
+//   gate/up   stage = 64 gate rows + 64 up rows of the expert x 512 K values.  IQ3_S: two 2-D tiled TMA boxes of 64 rows x
+//             240 bytes (two 110-byte super-blocks plus what 16-byte alignment of the box start costs); rows land 240
+//             bytes apart, so the eight rows a warp instruction touches fall into eight different groups of four banks.
+//             IQ3X: one contiguous 34 KB run.
+//   down      stage = 128 rows of the down matrix over all of K = 512 (contiguous: one 1-D bulk copy).
+// and a ring of activation slots (the tokens of an item's columns for its gate/up pieces, its H planes for the down pieces),
+// filled by the producer with bulk copies.  Consumer warp w = (row group r = w % 8, K half kh = w / 8) owns 16 MMA rows of
+// the stage and one of the stage's two super-blocks; the accumulators live across the stages of a piece, and the two K
+// halves of a row group meet once per piece through shared memory (always low half + high half: the order never depends on
+// the batch).  In a gate/up piece MMA row g is gate row 8r + g and row g + 8 is the up row of the same intermediate
+// index, so a lane holds both factors of H and no exchange between row groups exists.  B operands (the tokens, then H
+// as fp16 high + low planes) come from padded shared-memory rows by one 16-byte load per sub-block; lanes whose column is
+// absent load nothing.  Every wait is bounded (about two seconds); a warp that gives up records ST_MBAR_TIMEOUT and keeps
+// walking the same control flow without waiting again, so no barrier is ever left short of a participant.
 #include "iq3x.cuh"
 #include "moe_sel.h"
 #include "qmv_core.cuh"
@@ -34,32 +42,36 @@ namespace {
 
 constexpr int FFN_CW = 16;                       // consumer warps
 constexpr int FFN_THREADS = (FFN_CW + 1) * 32;   // + the producer warp
-constexpr int FFN_PF = 0;                        // whole tiles the optional L2 prefetch cursor runs ahead of the copies (QW_FFN_PF; measured: no gain)
+constexpr int FFN_MAXITEMS = MOE_FFN_MAXITEMS;   // see moe_sel.h: the scratch buffer
+constexpr int FFN_SYNC_BYTES = MOE_FFN_SYNC_BYTES;
 constexpr int FFN_PITCH = 240;                   // IQ3_S: bytes between staged gate/up rows
+constexpr int FFN_D = 2048, FFN_I = 512;         // the shapes this kernel is built for (the launcher refuses others)
 constexpr int FFN_MAXG = 520;                    // groups kept in shared memory: E <= 512 experts (+ end markers)
-// Shared-memory plan per weight format.  FMT 0 = the raw IQ3_S blocks (64 KB codebook, three 30 KB stages); FMT 1 = IQ3X
-// (iq3x.cuh: no codebook, four 34 KB stages).
+// Shared-memory plan per weight format.  FMT 0 = the raw IQ3_S blocks (64 KB codebook, three 30 KB stages, one activation
+// slot); FMT 1 = IQ3X (iq3x.cuh: no codebook, four 34 KB stages, two activation slots).
 template <int FMT>
 struct FfnCfg {
     static constexpr int STG = FMT ? 4 : 3;
     static constexpr int SLOT = FMT ? IQ3X_STAGE : 128 * FFN_PITCH;   // 30720 also holds an IQ3_S down tile of 128 x 220 bytes
     static constexpr int TAB = FMT ? 0 : 65536;
+    static constexpr int NACT = FMT ? 2 : 1;
     static constexpr int OFF_TAB = 128;
     static constexpr int OFF_PRE = OFF_TAB + TAB;                      // uint32 pre[FFN_MAXG], off[FFN_MAXG], ue[FFN_MAXG] of the selection record
     static constexpr int OFF_RED = OFF_PRE + 3 * FFN_MAXG * 4 + 32;    // [2][8 row groups][32 lanes] float4  (6272 = 49 * 128)
-    static constexpr int OFF_XS = OFF_RED + 2 * 8 * 32 * 16;           // tokens of the pass, then H planes, then the stages
+    static constexpr int OFF_XS = OFF_RED + 2 * 8 * 32 * 16;           // the activation slots, then the stages
 };
 
 struct FfnP {
     const uint8_t *Wd, *Sd;   // routed down [E][D][rbI], shared expert's down [D][rbI] (nullptr: no shared expert)
-    const uint8_t *Wg, *Wu, *Sg, *Su;  // gate / up matrices (the copies go through the tensor maps; these are for the L2 prefetch)
+    const uint8_t *Wg, *Sg;   // IQ3X: routed / shared gate + up stages (IQ3_S copies go through the tensor maps)
     const __half *x;          // tokens fp16 [nb][D]
     float *Pg;                // [nb][topk+1][D]
     const moe_sel *ms;
     const QwTables *tab;
     unsigned *status;
-    uint32_t D, I, rbD, rbI, ebase, pf, probe1d, hint;
-    unsigned long long *dbg;  // optional (define DBG 1, bind 13): cycle counters of the consumer warps, for tuning
+    uint32_t ebase;
+    unsigned *sync;           // [0 .. FFN_MAXITEMS) per-item counters of finished gate/up warps, [FFN_MAXITEMS] finished blocks; all zero between launches
+    __half *H;                // [FFN_MAXITEMS][2][8][I]
     float *PgR[8];            // expert-parallel exchange: Pg of every rank (see moe_dn in k_moe.cu)
     EpPeers ep;
 };
@@ -296,7 +308,7 @@ __device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int
     acc[0] = fmaf(dec.dba, p[0], acc[0]); acc[1] = fmaf(dec.dba, p[1], acc[1]); acc[2] = fmaf(dec.dbb, p[2], acc[2]); acc[3] = fmaf(dec.dbb, p[3], acc[3]);
 }
 
-// PROBE = true is the copy-only twin used to measure what the staging pipeline alone can deliver: the same items, the same
+// PROBE = true is the copy-only twin used to measure what the staging pipeline alone can deliver: the same pieces, the same
 // TMA boxes and bulk copies through the same ring, but the consumers only read every staged byte once (16-byte loads) and
 // compute nothing -- the role of the reference's pure-read probes (bench/moe_bw.c:1-3, bench/qmv.c:357-382).
 // (17 warps put five on one scheduler, whose 16 K registers then allow 96 per thread)
@@ -304,16 +316,18 @@ template <bool PROBE, int FMT>
 __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
                                                            const __grid_constant__ CUtensorMap mSG, const __grid_constant__ CUtensorMap mSU, const FfnP p) {
     using C = FfnCfg<FMT>;
-    constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT;
+    constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT, NACT = C::NACT;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
-    uint64_t *full = bars, *empty = bars + FFN_STG, *tab_bar = bars + 2 * FFN_STG, *xfull = tab_bar + 1, *xfree = tab_bar + 2;
+    uint64_t *full = bars, *empty = bars + FFN_STG, *tab_bar = bars + 2 * FFN_STG, *actfull = tab_bar + 1, *actfree = actfull + 2;
     uint32_t *pre = (uint32_t *)(smem + C::OFF_PRE);
     float4 *red = (float4 *)(smem + C::OFF_RED);
-    const uint32_t xpitch = p.D * 2 + 64, hpitch = p.I * 2 + 64;
-    uint8_t *xs = smem + C::OFF_XS, *hs = xs + 8 * xpitch, *stage0 = hs + 16 * hpitch;
+    constexpr uint32_t D = FFN_D, I = FFN_I, rbI = I / 256 * 110;
+    constexpr uint32_t xpitch = D * 2 + 64, hpitch = I * 2 + 64, act_slot = 8 * xpitch;  // a slot holds 8 token rows or 16 H rows
+    static_assert(act_slot >= 16 * hpitch, "activation slot");
+    uint8_t *act0 = smem + C::OFF_XS, *stage0 = act0 + NACT * act_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t KP = p.D / 512, GT = p.I / 64, DT = p.D / 128, KU = p.I / 256;
+    constexpr uint32_t KP = D / 512, GT = I / 64, DT = D / 128, KU = I / 256;
 
     pdl_launch();
     if (tid == 0) {
@@ -322,8 +336,10 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             mbar_init(&empty[s], FFN_CW);
         }
         mbar_init(tab_bar, 1);
-        mbar_init(xfull, 1);
-        mbar_init(xfree, FFN_CW);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&actfull[s], 1);
+            mbar_init(&actfree[s], FFN_CW);
+        }
         mbar_init_fence();
         if (FMT == 0) {
             mbar_expect_tx(tab_bar, C::TAB);
@@ -339,14 +355,22 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
     }
     const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
     __syncthreads();
-    const uint32_t items = pre[U] + (p.Sd ? (nb + 7) / 8 : 0);
+    uint32_t items = pre[U] + (p.Sd ? (nb + 7) / 8 : 0);
+    if (items > FFN_MAXITEMS) {  // cannot happen with E <= 512 and 64 tokens; never index past the flags
+        if (tid == 0) set_status(p.status, ST_BAD_ARG | 5);
+        items = 0;
+    }
     const uint32_t slot0 = smem_u32(stage0);
+    // this block's pieces: gate/up tiles [a_lo, a_hi) of the items x GT list, then down tiles [b_lo, b_hi) of the items x DT list
+    const uint32_t G = gridDim.x, bx_ = blockIdx.x;
+    const uint32_t a_lo = (uint32_t)((uint64_t)bx_ * items * GT / G), a_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * GT / G);
+    const uint32_t b_lo = (uint32_t)((uint64_t)bx_ * items * DT / G), b_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * DT / G);
 
     if (warp == FFN_CW) {
-        // ---- producer: one lane walks the block's items and keeps the ring full
+        // ---- producer: one lane walks the block's pieces and keeps the ring full
         if (lane == 0) {
             bool ok = true;
-            uint32_t j = 0, n = 0;
+            uint32_t j = 0, k = 0;
             auto slot_for = [&](uint32_t bytes) {  // waits until stage j % STG is free, arms its barrier; returns its address
                 const uint32_t s = j % FFN_STG;
                 if (j >= FFN_STG && ok && !mbar_wait(&empty[s], (j / FFN_STG - 1) & 1)) {
@@ -357,95 +381,90 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 mbar_expect_tx(&full[s], bytes);
                 return slot0 + s * FFN_SLOT;
             };
-            // The gate/up stages read 240 bytes of every 880-byte row at a time: left to the copies alone, DRAM would see small
-            // scattered pieces.  A second cursor therefore runs ahead of the copies and asks for whole tiles -- 64 contiguous
-            // rows of gate and of up (56 KB each), pairs of down tiles (56 KB) -- to be brought into L2 (prefetches hold no shared
-            // memory), so DRAM streams contiguous ranges and the strided boxes are served from L2.
-            const uint32_t PU = GT + DT / 2;  // prefetch units per item
+            auto act_for = [&](uint32_t bytes) {  // the same for the activation slots (tokens of an item, or its H)
+                const uint32_t s = k % NACT, n = k / NACT;
+                if (n >= 1 && ok && !mbar_wait(&actfree[s], (n - 1) & 1)) {
+                    ok = false;
+                    set_status(p.status, ST_MBAR_TIMEOUT | 7);
+                }
+                fence_proxy_async();
+                mbar_expect_tx(&actfull[s], bytes);
+                return act0 + s * act_slot;
+            };
             struct Src {
                 const CUtensorMap *tg, *tu;
                 const uint8_t *wg, *wu, *wd;
                 uint32_t erow;
             };
-            auto src_of = [&](uint32_t w) {
-                const FfnItem it = ffn_item(pre, U, nb, w);
+            auto src_of = [&](const FfnItem &it) {
                 Src c;
                 c.erow = it.shared ? 0 : (pre[2 * FFN_MAXG + it.u] - p.ebase);
                 c.tg = it.shared ? &mSG : &mG;
                 c.tu = it.shared ? &mSU : &mU;
                 if (FMT == 0) {
-                    c.wg = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * p.I * p.rbD;
-                    c.wu = (it.shared ? p.Su : p.Wu) + (size_t)c.erow * p.I * p.rbD;
-                    c.wd = it.shared ? p.Sd : p.Wd + (size_t)c.erow * p.D * p.rbI;
+                    c.wg = c.wu = nullptr;  // the copies go through the tensor maps
+                    c.wd = it.shared ? p.Sd : p.Wd + (size_t)c.erow * D * rbI;
                 } else {  // IQ3X: stage-ordered records, gate and up interleaved in one buffer
                     c.wg = c.wu = (it.shared ? p.Sg : p.Wg) + (size_t)c.erow * GT * KP * IQ3X_STAGE;
-                    c.wd = (it.shared ? p.Sd : p.Wd) + (size_t)c.erow * DT * (p.I / 512) * IQ3X_STAGE;
+                    c.wd = (it.shared ? p.Sd : p.Wd) + (size_t)c.erow * DT * (I / 512) * IQ3X_STAGE;
                 }
                 return c;
             };
-            auto l2_prefetch = [](const uint8_t *ptr, uint32_t bytes) {
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(bytes) : "memory");
-            };
-            uint32_t pw = blockIdx.x, pu = 0;
-            Src pc{};
-            if (pw < items) pc = src_of(pw);
-            auto prefetch_next = [&]() {
-                if (pw >= items) return;
-                if (FMT == 1) {
-                    if (pu < GT) l2_prefetch(pc.wg + (size_t)pu * KP * IQ3X_STAGE, KP * IQ3X_STAGE);
-                    else l2_prefetch(pc.wd + (size_t)(pu - GT) * 2 * IQ3X_STAGE, 2 * IQ3X_STAGE);
-                } else if (pu < GT) {
-                    l2_prefetch(pc.wg + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
-                    l2_prefetch(pc.wu + (size_t)pu * 64 * p.rbD, 64 * p.rbD);
-                } else {
-                    l2_prefetch(pc.wd + (size_t)(pu - GT) * 256 * p.rbI, 256 * p.rbI);
-                }
-                if (++pu == PU) {
-                    pu = 0;
-                    pw += gridDim.x;
-                    if (pw < items) pc = src_of(pw);
-                }
-            };
-            for (uint32_t i = 0; i < p.pf; i++) prefetch_next();
-            for (uint32_t w = blockIdx.x; w < items; w += gridDim.x, n++) {
-                const FfnItem it = ffn_item(pre, U, nb, w);
-                if (n > 0 && ok && !mbar_wait(xfree, (n - 1) & 1)) {  // every consumer warp is done with the previous item's tokens
-                    ok = false;
-                    set_status(p.status, ST_MBAR_TIMEOUT | 7);
-                }
-                fence_proxy_async();
-                mbar_expect_tx(xfull, it.ncols * p.D * 2);
-                for (uint32_t c = 0; c < it.ncols; c++) {
-                    uint32_t tok, rank;
-                    ffn_entry(ms, it, topk, c, tok, rank);
-                    bulk_g2s(xs + c * xpitch, p.x + (size_t)tok * p.D, p.D * 2, xfull);
-                }
-                const Src sc = src_of(w);
-                for (uint32_t gt = 0; gt < GT; gt++) {
-                    if (p.pf) prefetch_next();
-                    for (uint32_t kp = 0; kp < KP; kp++, j++) {
-                        const uint32_t dst = slot_for(FMT ? IQ3X_STAGE : 2 * 64 * FFN_PITCH);
-                        if (FMT == 1) {  // one contiguous stage
-                            bulk_s(dst, sc.wg + ((size_t)gt * KP + kp) * IQ3X_STAGE, IQ3X_STAGE, &full[j % FFN_STG]);
-                            continue;
-                        }
-                        const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * p.I + gt * 64);
-                        if (PROBE && p.probe1d) {  // measurement only: the same bytes per stage as two contiguous runs instead of two boxes
-                            const size_t o = ((size_t)gt * KP + kp) * 64 * FFN_PITCH;
-                            bulk_s(dst, sc.wg + o, 64 * FFN_PITCH, &full[j % FFN_STG]);
-                            bulk_s(dst + 64 * FFN_PITCH, sc.wu + o, 64 * FFN_PITCH, &full[j % FFN_STG]);
-                            continue;
-                        }
-                        tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
-                        tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
+            Src sc{};
+            uint32_t cur = 0xffffffffu;
+            for (uint32_t a = a_lo; a < a_hi; a++) {
+                const uint32_t w = a / GT, gt = a - w * GT;
+                if (w != cur) {  // the tokens of the item's columns
+                    cur = w;
+                    const FfnItem it = ffn_item(pre, U, nb, w);
+                    uint8_t *dst = act_for(it.ncols * D * 2);
+                    for (uint32_t c = 0; c < it.ncols; c++) {
+                        uint32_t tok, rank;
+                        ffn_entry(ms, it, topk, c, tok, rank);
+                        bulk_g2s(dst + c * xpitch, p.x + (size_t)tok * D, D * 2, &actfull[k % NACT]);
                     }
+                    k++;
+                    sc = src_of(it);
                 }
-                for (uint32_t dt = 0; dt < DT; dt++, j++) {
-                    if (p.pf && !(dt & 1)) prefetch_next();
-                    const uint32_t bytes = FMT ? IQ3X_STAGE : 128 * p.rbI;
-                    const uint32_t dst = slot_for(bytes);
-                    bulk_s(dst, sc.wd + (size_t)dt * bytes, bytes, &full[j % FFN_STG]);
+                for (uint32_t kp = 0; kp < KP; kp++, j++) {
+                    const uint32_t dst = slot_for(FMT ? IQ3X_STAGE : 2 * 64 * FFN_PITCH);
+                    if (FMT == 1) {  // one contiguous stage
+                        bulk_s(dst, sc.wg + ((size_t)gt * KP + kp) * IQ3X_STAGE, IQ3X_STAGE, &full[j % FFN_STG]);
+                        continue;
+                    }
+                    const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * I + gt * 64);
+                    tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
+                    tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
                 }
+            }
+            cur = 0xffffffffu;
+            for (uint32_t bi = b_lo; bi < b_hi; bi++, j++) {
+                const uint32_t w = bi / DT, dt = bi - w * DT;
+                if (w != cur) {  // H of the item: written by the blocks that ran its gate/up pieces, complete when all GT x 8 warps have counted in
+                    cur = w;
+                    const FfnItem it = ffn_item(pre, U, nb, w);
+                    if (!PROBE && ok && ld_acquire_gpu(p.sync + w) < GT * 8) {
+                        const uint64_t t0 = global_ns();
+                        while (ld_acquire_gpu(p.sync + w) < GT * 8)
+                            if (global_ns() - t0 > 2000000000ull) {
+                                ok = false;
+                                set_status(p.status, ST_MBAR_TIMEOUT | 11);
+                                break;
+                            }
+                    }
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // the H rows were written by ordinary stores; the copy engine reads them
+                    uint8_t *dst = act_for(2 * it.ncols * I * 2);
+                    const __half *Hw = p.H + (size_t)w * 16 * I;
+                    for (uint32_t c = 0; c < it.ncols; c++) {
+                        bulk_g2s(dst + c * hpitch, Hw + (size_t)c * I, I * 2, &actfull[k % NACT]);
+                        bulk_g2s(dst + (8 + c) * hpitch, Hw + (size_t)(8 + c) * I, I * 2, &actfull[k % NACT]);
+                    }
+                    k++;
+                    sc = src_of(it);
+                }
+                const uint32_t bytes = FMT ? IQ3X_STAGE : 128 * rbI;
+                const uint32_t dst = slot_for(bytes);
+                bulk_s(dst, sc.wd + (size_t)dt * bytes, bytes, &full[j % FFN_STG]);
             }
         }
     } else {
@@ -455,18 +474,12 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
         if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 8);
         const uint32_t tabl = smem_u32(smem + C::OFF_TAB) + lane * 4;  // this lane's copy of the interleaved codebook
         const ZeroRegs zr = zero_regs();
-        const uint32_t xb0 = smem_u32(xs) + g * xpitch + t * 16;
-        const uint32_t hb0 = smem_u32(hs) + g * hpitch + t * 16;
-        uint32_t j = 0, n = 0, rc = 0;
-        long long c_wait = 0, c_bar = 0, c_x = 0;
-        const long long c_begin = clock64();
+        uint32_t j = 0, k = 0, rc = 0;
         auto wait_full = [&]() {
-            const long long c0 = p.dbg ? clock64() : 0;
-            if (ok && !(p.hint ? mbar_wait_hint(&full[j % FFN_STG], (j / FFN_STG) & 1, p.hint) : mbar_wait(&full[j % FFN_STG], (j / FFN_STG) & 1))) {
+            if (ok && !mbar_wait(&full[j % FFN_STG], (j / FFN_STG) & 1)) {
                 ok = false;
                 if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 9);
             }
-            if (p.dbg) c_wait += clock64() - c0;
             return slot0 + (j % FFN_STG) * FFN_SLOT;
         };
         auto release = [&]() {
@@ -474,14 +487,32 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             if (lane == 0) mbar_arrive(&empty[j % FFN_STG]);
             j++;
         };
+        // activation slot of the next item: waits for its copy, returns its shared address
+        auto act_wait = [&]() {
+            const uint32_t s = k % NACT;
+            if (ok && !mbar_wait(&actfull[s], (k / NACT) & 1)) {
+                ok = false;
+                if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 10);
+            }
+            return smem_u32(act0) + s * act_slot;
+        };
+        auto act_release = [&]() {  // this warp is done with the current item's slot
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&actfree[k % NACT]);
+            k++;
+        };
+        auto probe_read = [&](uint32_t st, uint32_t bytes, uint32_t &sink) {
+            for (uint32_t o = (warp * 32 + lane) * 16; o < bytes; o += FFN_CW * 32 * 16) {
+                const uint4 v = lds_v4(st + o);
+                sink ^= v.x ^ v.y ^ v.z ^ v.w;
+            }
+        };
         // the two K halves of a row group: the high half hands its partial sums over, the low half adds them to its own
         auto pair_sum = [&](float (&acc)[4]) {
             float4 *rd = red + ((rc & 1) * 8 + r) * 32 + lane;
             rc++;
             if (kh) *rd = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            const long long c0 = p.dbg ? clock64() : 0;
             bar_sync_n(1 + r, 64);
-            if (p.dbg) c_bar += clock64() - c0;
             if (!kh) {
                 const float4 v = *rd;
                 acc[0] += v.x;
@@ -490,114 +521,124 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 acc[3] += v.w;
             }
         };
-        for (uint32_t w = blockIdx.x; w < items; w += gridDim.x, n++) {
-            const FfnItem it = ffn_item(pre, U, nb, w);
-            if (n > 0) bar_sync_n(9, FFN_CW * 32);  // nobody still reads the previous item's H rows
-            const uint32_t have = (uint32_t)g < it.ncols ? 1u : 0u;
-            uint32_t oo[2] = {0xffffffffu, 0xffffffffu};  // element offsets of the output rows of columns 2t and 2t + 1
-#pragma unroll
-            for (int c = 0; c < 2; c++)
-                if ((uint32_t)(2 * t + c) < it.ncols) {
-                    uint32_t tok, rank;
-                    ffn_entry(ms, it, topk, 2 * t + c, tok, rank);
-                    oo[c] = (tok * (topk + 1) + rank) * p.D;
-                }
-            {
-                const long long c0 = p.dbg ? clock64() : 0;
-                if (ok && !mbar_wait(xfull, n & 1)) {
-                    ok = false;
-                    if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 10);
-                }
-                if (p.dbg) c_x += clock64() - c0;
+        uint32_t sink = 0;
+        // ---- gate/up pieces: tiles of 64 intermediate indices
+        uint32_t cur = 0xffffffffu, have = 0, ncols = 0, xb0 = 0;
+        for (uint32_t a = a_lo; a < a_hi; a++) {
+            const uint32_t w = a / GT, gt = a - w * GT;
+            if (w != cur) {
+                if (cur != 0xffffffffu) act_release();
+                cur = w;
+                ncols = ffn_item(pre, U, nb, w).ncols;
+                have = (uint32_t)g < ncols ? 1u : 0u;
+                xb0 = act_wait() + g * xpitch + t * 16;
             }
-            if (PROBE) {
-                uint32_t sink = 0;
-                for (uint32_t sidx = 0; sidx < GT * KP + DT; sidx++) {
-                    const uint32_t st = wait_full(), bytes = FMT ? IQ3X_STAGE : sidx < GT * KP ? 128 * FFN_PITCH : 128 * p.rbI;
-                    for (uint32_t o = (warp * 32 + lane) * 16; o < bytes; o += FFN_CW * 32 * 16) {
-                        const uint4 v = lds_v4(st + o);
-                        sink ^= v.x ^ v.y ^ v.z ^ v.w;
-                    }
-                    release();
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(xfree);
-                if (sink == 0x9e3779b9u && oo[0] != 0xffffffffu) p.Pg[oo[0]] = 0.f;  // keeps the loads observable; practically never taken
-                continue;
-            }
-            // ---- gate/up: tiles of 64 intermediate indices
-            for (uint32_t gt = 0; gt < GT; gt++) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                for (uint32_t kp = 0; kp < KP; kp++) {
-                    const uint32_t st = wait_full();
-                    const uint32_t bx = xb0 + (2 * kp + kh) * 512;
-                    if (FMT == 1) {
-                        const uint32_t rec0 = st + (8 * r + g) * IQ3X_REC;
-                        x_unit<1>(rec0, rec0 + 64 * IQ3X_REC, kh, t, zr, bx, bx, have, acc);
-                    } else {
-                        const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
-                        ffn_unit<1>(u0, u1, t, tabl, zr, bx, bx, have, acc);
-                    }
-                    release();
-                }
-                pair_sum(acc);
-                if (!kh) {
-                    // acc[0], acc[1] = gate of index 64 gt + 8 r + g for columns 2t, 2t + 1; acc[2], acc[3] = up.  H travels to the
-                    // down half as an fp16 high part plus an fp16 remainder (22 mantissa bits where the remainder is normal)
-                    const uint32_t idx = gt * 64 + 8 * r + g;
-#pragma unroll
-                    for (int c = 0; c < 2; c++) {
-                        const float gs = acc[c], us = acc[2 + c];
-                        float h = gs / (1.0f + expf(-gs)) * us;
-                        h = fminf(fmaxf(h, -65504.0f), 65504.0f);
-                        const __half hi = __float2half_rn(h);
-                        const __half lo = __float2half_rn(h - __half2float(hi));
-                        uint8_t *hr = hs + (size_t)(2 * t + c) * hpitch + idx * 2;
-                        *(__half *)hr = hi;
-                        *(__half *)(hr + 8 * hpitch) = lo;
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(xfree);
-            bar_sync_n(9, FFN_CW * 32);  // H of the item is complete
-            // ---- down: tiles of 128 output rows; MMA row g is tile row 16 r + 2 g, row g + 8 the next one
-            for (uint32_t dt = 0; dt < DT; dt++) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (uint32_t kp = 0; kp < KP; kp++) {
                 const uint32_t st = wait_full();
-                for (uint32_t ks = kh; ks < KU; ks += 2) {
-                    const uint32_t bh = hb0 + ks * 512, bl = bh + 8 * hpitch;
-                    if (FMT == 1) {  // positions 16 r + g and 16 r + 8 + g hold output rows 16 r + 2 g and 16 r + 2 g + 1
-                        const uint32_t rec0 = st + (16 * r + g) * IQ3X_REC;
-                        x_unit<2>(rec0, rec0 + 8 * IQ3X_REC, kh, t, zr, bh, bl, have, acc);
-                    } else {
-                        const uint32_t u0 = st + (16 * r + 2 * g) * p.rbI + ks * 110, u1 = u0 + p.rbI;
-                        ffn_unit<2>(u0, u1, t, tabl, zr, bh, bl, have, acc);
-                    }
+                const uint32_t bx = xb0 + (2 * kp + kh) * 512;
+                if (PROBE) probe_read(st, FMT ? IQ3X_STAGE : 128 * FFN_PITCH, sink);
+                else if (FMT == 1) {
+                    const uint32_t rec0 = st + (8 * r + g) * IQ3X_REC;
+                    x_unit<1>(rec0, rec0 + 64 * IQ3X_REC, kh, t, zr, bx, bx, have, acc);
+                } else {
+                    const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
+                    ffn_unit<1>(u0, u1, t, tabl, zr, bx, bx, have, acc);
                 }
                 release();
-                pair_sum(acc);
-                if (!kh) {
-                    // acc[0], acc[2] = rows 2g, 2g + 1 of column 2t; acc[1], acc[3] = the same rows of column 2t + 1
-                    const uint32_t row = dt * 128 + 16 * r + 2 * g;
-                    if (p.ep.nranks > 1) {
-                        for (uint32_t q = 0; q < p.ep.nranks; q++) {
-                            if (oo[0] != 0xffffffffu) *(float2 *)(p.PgR[q] + oo[0] + row) = make_float2(acc[0], acc[2]);
-                            if (oo[1] != 0xffffffffu) *(float2 *)(p.PgR[q] + oo[1] + row) = make_float2(acc[1], acc[3]);
-                        }
-                    } else {
-                        if (oo[0] != 0xffffffffu) *(float2 *)(p.Pg + oo[0] + row) = make_float2(acc[0], acc[2]);
-                        if (oo[1] != 0xffffffffu) *(float2 *)(p.Pg + oo[1] + row) = make_float2(acc[1], acc[3]);
+            }
+            if (PROBE) continue;
+            pair_sum(acc);
+            if (!kh) {
+                // acc[0], acc[1] = gate of index 64 gt + 8 r + g for columns 2t, 2t + 1; acc[2], acc[3] = up.  H travels to the
+                // down pieces (run by whichever blocks hold them) through global memory as an fp16 high part plus an fp16
+                // remainder (22 mantissa bits where the remainder is normal): [item][plane][column][I]
+                const uint32_t idx = gt * 64 + 8 * r + g;
+                __half *Hw = p.H + (size_t)w * 16 * I + idx;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    const float gs = acc[c], us = acc[2 + c];
+                    float h = gs / (1.0f + expf(-gs)) * us;
+                    h = fminf(fmaxf(h, -65504.0f), 65504.0f);
+                    const __half hi = __float2half_rn(h);
+                    const __half lo = __float2half_rn(h - __half2float(hi));
+                    if ((uint32_t)(2 * t + c) < ncols) {
+                        Hw[(size_t)(2 * t + c) * I] = hi;
+                        Hw[(size_t)(8 + 2 * t + c) * I] = lo;
                     }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    __threadfence();  // the warp's H values (cumulative over the warp barrier) before the count
+                    atomicAdd(p.sync + w, 1u);
                 }
             }
         }
-        if (p.dbg && lane == 0 && n > 0) {
-            atomicAdd(p.dbg + 0, (unsigned long long)(clock64() - c_begin));
-            atomicAdd(p.dbg + 1, (unsigned long long)c_wait);
-            atomicAdd(p.dbg + 2, (unsigned long long)c_bar);
-            atomicAdd(p.dbg + 3, (unsigned long long)c_x);
-            atomicAdd(p.dbg + 4, 1ull);
+        if (cur != 0xffffffffu) act_release();
+        // ---- down pieces: tiles of 128 output rows; MMA row g is tile row 16 r + 2 g, row g + 8 the next one
+        cur = 0xffffffffu;
+        uint32_t hb0 = 0, oo[2] = {0xffffffffu, 0xffffffffu};  // element offsets of the output rows of columns 2t and 2t + 1
+        for (uint32_t bi = b_lo; bi < b_hi; bi++) {
+            const uint32_t w = bi / DT, dt = bi - w * DT;
+            if (w != cur) {
+                if (cur != 0xffffffffu) act_release();
+                cur = w;
+                const FfnItem it = ffn_item(pre, U, nb, w);
+                have = (uint32_t)g < it.ncols ? 1u : 0u;
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    oo[c] = 0xffffffffu;
+                    if ((uint32_t)(2 * t + c) < it.ncols) {
+                        uint32_t tok, rank;
+                        ffn_entry(ms, it, topk, 2 * t + c, tok, rank);
+                        oo[c] = (tok * (topk + 1) + rank) * D;
+                    }
+                }
+                hb0 = act_wait() + g * hpitch + t * 16;
+            }
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t st = wait_full();
+            if (PROBE) {
+                probe_read(st, FMT ? IQ3X_STAGE : 128 * rbI, sink);
+                release();
+                continue;
+            }
+            for (uint32_t ks = kh; ks < KU; ks += 2) {
+                const uint32_t bh = hb0 + ks * 512, bl = bh + 8 * hpitch;
+                if (FMT == 1) {  // positions 16 r + g and 16 r + 8 + g hold output rows 16 r + 2 g and 16 r + 2 g + 1
+                    const uint32_t rec0 = st + (16 * r + g) * IQ3X_REC;
+                    x_unit<2>(rec0, rec0 + 8 * IQ3X_REC, kh, t, zr, bh, bl, have, acc);
+                } else {
+                    const uint32_t u0 = st + (16 * r + 2 * g) * rbI + ks * 110, u1 = u0 + rbI;
+                    ffn_unit<2>(u0, u1, t, tabl, zr, bh, bl, have, acc);
+                }
+            }
+            release();
+            pair_sum(acc);
+            if (!kh) {
+                // acc[0], acc[2] = rows 2g, 2g + 1 of column 2t; acc[1], acc[3] = the same rows of column 2t + 1
+                const uint32_t row = dt * 128 + 16 * r + 2 * g;
+                if (p.ep.nranks > 1) {
+                    for (uint32_t q = 0; q < p.ep.nranks; q++) {
+                        if (oo[0] != 0xffffffffu) *(float2 *)(p.PgR[q] + oo[0] + row) = make_float2(acc[0], acc[2]);
+                        if (oo[1] != 0xffffffffu) *(float2 *)(p.PgR[q] + oo[1] + row) = make_float2(acc[1], acc[3]);
+                    }
+                } else {
+                    if (oo[0] != 0xffffffffu) *(float2 *)(p.Pg + oo[0] + row) = make_float2(acc[0], acc[2]);
+                    if (oo[1] != 0xffffffffu) *(float2 *)(p.Pg + oo[1] + row) = make_float2(acc[1], acc[3]);
+                }
+            }
+        }
+        if (cur != 0xffffffffu) act_release();
+        if (PROBE && sink == 0x9e3779b9u) p.Pg[0] = 0.f;  // keeps the loads observable; practically never taken
+    }
+    // the last block to finish clears the items' counters for the next launch (every block has read what it needed by then)
+    __syncthreads();
+    if (tid == 0 && !PROBE) {
+        __threadfence();
+        if (atomicAdd(p.sync + FFN_MAXITEMS, 1u) == gridDim.x - 1) {
+            for (uint32_t i = 0; i < items; i++) p.sync[i] = 0;
+            p.sync[FFN_MAXITEMS] = 0;
         }
     }
     if (p.ep.nranks > 1) ep_publish(p.ep);
@@ -637,7 +678,8 @@ const CUtensorMap *ffn_tensor_map(const void *base, uint64_t pitch, uint64_t row
 }  // namespace
 
 // binds: 0 = routed gate, 1 = routed up [EL][I][rbD], 2 = shared gate, 3 = shared up (used unless SHARED is defined 0),
-// 4 = x fp16 [nb][D], 5 = moe_sel, 6 = routed down [EL][D][rbI], 7 = shared down, 9 = Pg fp32 [64][TOPK+1][D],
+// 4 = x fp16 [nb][D], 5 = moe_sel, 6 = routed down [EL][D][rbI], 7 = shared down, 8 = scratch (MOE_FFN_SCRATCH_BYTES(I) of
+// moe_sel.h, zeroed once by the owner, private to one stream), 9 = Pg fp32 [64][TOPK+1][D],
 // 10 = id of the first expert held in the weight buffers (optional, default 0); with EPX = ranks also 11, 12, 16 + r,
 // 24 + r as for moe_dn.  defines: E, D, I, TOPK, EL, SHARED, EPX.  The host's grid and block are ignored.
 // With IQ3X defined 1 the weights are the re-coded form of iq3x.cuh (made by iq3x_pack): 0 = routed gate + up
@@ -647,21 +689,24 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     FfnP p{};
     const uint32_t E = (uint32_t)L.def("E", 512), topk = (uint32_t)L.def("TOPK", 10);
     const bool x4 = L.def("IQ3X", 0) != 0;
-    p.D = (uint32_t)L.def("D", 2048);
-    p.I = (uint32_t)L.def("I", 512);
-    QW_CHECK_ARG(p.D % 2048 == 0 && p.I == 512 && topk < MOE_MAXK && E <= 512);
-    p.rbD = p.D / 256 * 110;
-    p.rbI = p.I / 256 * 110;
-    const size_t act = (size_t)8 * (p.D * 2 + 64) + (size_t)16 * (p.I * 2 + 64);
-    const size_t smem = x4 ? FfnCfg<1>::OFF_XS + act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT : FfnCfg<0>::OFF_XS + act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
-    QW_CHECK_ARG(smem <= 227 * 1024 && 128 * p.rbI <= FfnCfg<0>::SLOT && (128 * p.rbI) % 16 == 0);
+    const uint32_t D = (uint32_t)L.def("D", 2048), I = (uint32_t)L.def("I", 512);
+    QW_CHECK_ARG(D == FFN_D && I == FFN_I && topk < MOE_MAXK && E <= 512);
+    const uint32_t rbD = D / 256 * 110, rbI = I / 256 * 110;
+    const size_t act = (size_t)8 * (D * 2 + 64);  // an activation slot: 8 token rows, or 16 H rows
+    const size_t smem = x4 ? FfnCfg<1>::OFF_XS + FfnCfg<1>::NACT * act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT
+                           : FfnCfg<0>::OFF_XS + FfnCfg<0>::NACT * act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
+    QW_CHECK_ARG(smem <= 227 * 1024 && 128 * rbI <= FfnCfg<0>::SLOT && (128 * rbI) % 16 == 0);
     const bool shared = L.def("SHARED", 1) != 0;
     const uint32_t EL = (uint32_t)L.def("EL", E);
     p.ebase = L.has_bytes(10, 4) ? L.bytes<uint32_t>(10) : 0;
     QW_CHECK_ARG(EL >= 1 && p.ebase + EL <= E);
     const uint8_t *Wg = L.buf<uint8_t>(0), *Wu = x4 ? Wg : L.buf<uint8_t>(1), *Sg = shared ? L.buf<uint8_t>(2) : nullptr, *Su = !shared ? nullptr : x4 ? Sg : L.buf<uint8_t>(3);
     p.Wd = L.buf<uint8_t>(6);
-    p.Wg = Wg; p.Wu = Wu; p.Sg = Sg; p.Su = Su;
+    p.Wg = Wg;
+    p.Sg = Sg;
+    p.sync = L.buf<unsigned>(8);
+    QW_CHECK_ARG(p.sync && ((uintptr_t)p.sync & 15) == 0 && L.avail(8) >= MOE_FFN_SCRATCH_BYTES(I));
+    p.H = (__half *)((uint8_t *)p.sync + FFN_SYNC_BYTES);
     p.Sd = shared ? L.buf<uint8_t>(7) : nullptr;
     p.x = L.buf<__half>(4);
     p.ms = L.buf<moe_sel>(5);
@@ -671,14 +716,14 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     QW_CHECK_ARG(Wg && Wu && p.Wd && p.x && p.ms && p.Pg && L.avail(5) >= sizeof(moe_sel));
     QW_CHECK_ARG(!shared || (Sg && Su && p.Sd));
     if (x4) {
-        const size_t gus = (size_t)(p.I / 64) * (p.D / 512) * IQ3X_STAGE, dns = (size_t)(p.D / 128) * (p.I / 512) * IQ3X_STAGE;
+        const size_t gus = (size_t)(I / 64) * (D / 512) * IQ3X_STAGE, dns = (size_t)(D / 128) * (I / 512) * IQ3X_STAGE;
         QW_CHECK_ARG(L.avail(0) >= EL * gus && L.avail(6) >= EL * dns && (!shared || (L.avail(2) >= gus && L.avail(7) >= dns)));
     } else {
-        const size_t wsz = (size_t)EL * p.I * p.rbD, ssz = (size_t)p.I * p.rbD;
+        const size_t wsz = (size_t)EL * I * rbD, ssz = (size_t)I * rbD;
         QW_CHECK_ARG(L.avail(0) >= wsz && L.avail(1) >= wsz && L.avail(6) >= wsz && (!shared || (L.avail(2) >= ssz && L.avail(3) >= ssz && L.avail(7) >= ssz)));
     }
     QW_CHECK_ARG((((uintptr_t)Wg | (uintptr_t)Wu | (uintptr_t)p.Wd | (uintptr_t)Sg | (uintptr_t)Su | (uintptr_t)p.Sd | (uintptr_t)p.x) & 15) == 0);
-    QW_CHECK_ARG(L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4 && L.avail(4) >= (size_t)p.D * 2);
+    QW_CHECK_ARG(L.avail(9) >= (size_t)MOE_MAXB * (topk + 1) * D * 4 && L.avail(4) >= (size_t)D * 2);
     p.ep = EpPeers{};
     p.ep.nranks = 1;
     if (L.def("EPX", 0) > 1) {
@@ -691,25 +736,18 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
         for (uint32_t r = 0; r < p.ep.nranks; r++) {
             p.PgR[r] = L.buf<float>(16 + r);
             p.ep.flagR[r] = L.buf<unsigned>(24 + r);
-            QW_CHECK_ARG(p.PgR[r] && p.ep.flagR[r] && L.avail(24 + r) >= p.ep.nranks * 4 && L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * p.D * 4);
+            QW_CHECK_ARG(p.PgR[r] && p.ep.flagR[r] && L.avail(24 + r) >= p.ep.nranks * 4 && L.avail(16 + r) >= (size_t)MOE_MAXB * (topk + 1) * D * 4);
         }
     }
     static const CUtensorMap no_map{};  // IQ3X stages are contiguous: no tensor maps
     const CUtensorMap *mG = &no_map, *mU = &no_map, *mSG = &no_map, *mSU = &no_map;
     if (!x4) {
-        mG = ffn_tensor_map(Wg, p.rbD, (uint64_t)EL * p.I);
-        mU = ffn_tensor_map(Wu, p.rbD, (uint64_t)EL * p.I);
-        mSG = shared ? ffn_tensor_map(Sg, p.rbD, p.I) : mG;
-        mSU = shared ? ffn_tensor_map(Su, p.rbD, p.I) : mU;
+        mG = ffn_tensor_map(Wg, rbD, (uint64_t)EL * I);
+        mU = ffn_tensor_map(Wu, rbD, (uint64_t)EL * I);
+        mSG = shared ? ffn_tensor_map(Sg, rbD, I) : mG;
+        mSU = shared ? ffn_tensor_map(Su, rbD, I) : mU;
         QW_CHECK_ARG(mG && mU && mSG && mSU);
     }
-    static const int pf_env = getenv("QW_FFN_PF") ? atoi(getenv("QW_FFN_PF")) : FFN_PF;
-    p.pf = (uint32_t)(pf_env < 0 ? 0 : pf_env > 64 ? 64 : pf_env);
-    p.probe1d = getenv("QW_FFN_PROBE_1D") ? 1 : 0;
-    static const int hint_env = getenv("QW_FFN_HINT") ? atoi(getenv("QW_FFN_HINT")) : 0;
-    p.hint = (uint32_t)(hint_env < 0 ? 0 : hint_env);
-    p.dbg = L.def("DBG", 0) ? L.buf<unsigned long long>(13) : nullptr;
-    if (L.def("DBG", 0)) QW_CHECK_ARG(p.dbg && L.avail(13) >= 64);
     const bool probe = L.def("PROBE", 0) != 0;  // PROBE defined 1: the copy-only twin (outputs are not written)
     auto kern = x4 ? (probe ? moe_ffn_k<true, 1> : moe_ffn_k<false, 1>) : (probe ? moe_ffn_k<true, 0> : moe_ffn_k<false, 0>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

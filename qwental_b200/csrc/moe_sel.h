@@ -19,3 +19,11 @@ struct moe_sel {
     uint32_t pre[MOE_MAXE + 2];               // passes of 8 entries in the groups before u (pre[U] = all routed passes)
 };
 
+
+// Scratch buffer of the fused expert-FFN kernel (k_ffn.cu): the items' counters and the finished-block counter in the first
+// MOE_FFN_SYNC_BYTES (all zero between launches: the owner zeroes the buffer once), then H [item][2 planes][8 columns][I] fp16.
+// An item is one pass of up to 8 tokens of one chosen expert or of the shared expert: at most 512 experts + the extra passes
+// of 64 tokens x 10 choices + the shared expert's 8.
+#define MOE_FFN_MAXITEMS 640
+#define MOE_FFN_SYNC_BYTES 4096
+#define MOE_FFN_SCRATCH_BYTES(I) ((size_t)MOE_FFN_SYNC_BYTES + (size_t)MOE_FFN_MAXITEMS * 16 * (I) * 2)

@@ -66,7 +66,7 @@ class MoeLayer:
         # "iq3x" = the fused kernel on expert weights re-coded once by iq3x_pack (lossless; 136 instead of 110 bytes per 256 weights)
         assert ffn in ("auto", "fused", "split", "iq3x")
         self.iq3x = ffn == "iq3x"
-        self.fused_ffn = ffn in ("fused", "iq3x") or (ffn == "auto" and D % 2048 == 0 and I == 512)
+        self.fused_ffn = ffn in ("fused", "iq3x") or (ffn == "auto" and D == 2048 and I == 512)
         self.Wr, self.Wsg, self.Wg, self.Wu, self.Wd, self.Sg, self.Su, self.Sd = Wr, Wsg, Wg, Wu, Wd, Sg, Su, Sd
         self.e_lo, self.e_hi = e_lo, E if e_hi is None else e_hi
         tag = "_e%d_d%d_i%d_k%d" % (E, D, I, topk)
@@ -89,6 +89,8 @@ class MoeLayer:
         self.Hhi = gpu.buf(MOE_MAXB * (topk + 1) * I * 2).zero()
         self.Hlo = gpu.buf(MOE_MAXB * (topk + 1) * I * 2).zero()
         self.Pg = gpu.buf(MOE_MAXB * (topk + 1) * D * 4).zero()
+        # moe_ffn's scratch (csrc/moe_sel.h): 4 KB of counters that are zero between launches, then H of up to 640 items
+        self.ffn_scr = gpu.buf(4096 + 640 * 16 * I * 2).zero() if self.fused_ffn else None
 
     def encode(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None = None, fused_route: bool = False):
         E, D, I = self.E, self.D, self.I
@@ -107,12 +109,12 @@ class MoeLayer:
             b.kernel(self.k_ffn).buf(0, self.Xgu)
             if self.Sg is not None:
                 b.buf(2, self.XSgu).buf(7, self.XSd)
-            b.buf(4, x).buf(5, self.sel).buf(6, self.Xd).buf(9, self.Pg).dispatch((I // 16, nb * self.topk + 1), (256,))
+            b.buf(4, x).buf(5, self.sel).buf(6, self.Xd).buf(8, self.ffn_scr).buf(9, self.Pg).dispatch((I // 16, nb * self.topk + 1), (256,))
         elif self.fused_ffn:
             b.kernel(self.k_ffn).buf(0, self.Wg).buf(1, self.Wu)
             if self.Sg is not None:
                 b.buf(2, self.Sg).buf(3, self.Su).buf(7, self.Sd)
-            b.buf(4, x).buf(5, self.sel).buf(6, self.Wd).buf(9, self.Pg).dispatch((I // 16, nb * self.topk + 1), (256,))
+            b.buf(4, x).buf(5, self.sel).buf(6, self.Wd).buf(8, self.ffn_scr).buf(9, self.Pg).dispatch((I // 16, nb * self.topk + 1), (256,))
         else:
             b.kernel(self.k_gu).buf(0, self.Wg).buf(1, self.Wu)
             if self.Sg is not None:
