@@ -332,9 +332,9 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          compile(e, "add_rmsnorm", "cmb_add_rmsnorm", {{"CMB", 1}, {"TOPK", e->TOPK}}, &e->k_norm_cmb);
     {
         const char *fm = getenv("QW_MOE_FFN");
-        // one expert per block is the right grain when a rank has about as many chosen experts as SMs; with the experts spread
-        // over several ranks the two-launch family, which cuts every expert into units for all blocks, is faster
-        e->ffn_fused = e->D % 2048 == 0 && e->D <= 2048 && e->I == 512 && (c.ep_size == 1 || (fm && !strcmp(fm, "fused"))) && !(fm && !strcmp(fm, "split"));
+        // moe_ffn spreads the pieces of the chosen experts over all blocks, so it is the default at every rank count;
+        // QW_MOE_FFN=split keeps the two-launch family, QW_MOE_FFN=fused runs moe_ffn on the raw IQ3_S blocks
+        e->ffn_fused = e->D == 2048 && e->I == 512 && !(fm && !strcmp(fm, "split"));
         e->ffn_iq3x = e->ffn_fused && !(fm && !strcmp(fm, "fused"));
         if (ok && e->ffn_fused) {
             auto mf = md;

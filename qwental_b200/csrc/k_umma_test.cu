@@ -1,0 +1,71 @@
+// Self-test of the tcgen05 helpers (umma.cuh): D[128][16] = A[128][K] * B[16][K]^T, fp16 operands laid out by the threads in
+// the un-swizzled K-major form, fp32 accumulator in tensor memory, read back and written out.  Used by the parity tests to
+// pin the descriptor conventions the expert-FFN kernel relies on.
+#include "qw_kern.h"
+#include "umma.cuh"
+
+using namespace qw;
+
+struct umma_test_args {
+    uint32_t K;      // multiple of 16, <= 128
+    uint32_t order;  // 0: core matrices stored [row group][K group] (K stride 128 bytes), 1: [K group][row group]
+};
+
+__global__ void __launch_bounds__(128) umma_test_k(const __half *A, const __half *B, float *out, umma_test_args a, unsigned *status) {
+    __shared__ __align__(128) uint8_t sa[128 * 128 * 2];
+    __shared__ __align__(128) uint8_t sb[16 * 128 * 2];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t slot;
+    pdl_sync();
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t KG = a.K / 8;
+    // strides of the core matrices (bytes)
+    const uint32_t a_k = a.order ? 16 * 128 : 128, a_mn = a.order ? 128 : KG * 128;
+    const uint32_t b_k = a.order ? 2 * 128 : 128, b_mn = a.order ? 128 : KG * 128;
+    if (warp == 0) tmem_alloc(&slot, 32);
+    if (tid == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    for (uint32_t c = tid; c < 128 * KG; c += 128) {  // 16-byte chunk (row, K group)
+        const uint32_t row = c / KG, j = c % KG;
+        *(uint4 *)(sa + (row >> 3) * a_mn + j * a_k + (row & 7) * 16) = *(const uint4 *)(A + (size_t)row * a.K + j * 8);
+    }
+    for (uint32_t c = tid; c < 16 * KG; c += 128) {
+        const uint32_t row = c / KG, j = c % KG;
+        *(uint4 *)(sb + (row >> 3) * b_mn + j * b_k + (row & 7) * 16) = *(const uint4 *)(B + (size_t)row * a.K + j * 8);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the generic stores above are read by the tensor core's proxy
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = slot;
+    if (tid == 0) {
+        const uint32_t idesc = umma_idesc_f16(128, 16);
+        for (uint32_t k = 0; k < a.K / 16; k++)
+            umma_f16(tmem, umma_desc(smem_u32(sa) + 2 * k * a_k, a_k, a_mn), umma_desc(smem_u32(sb) + 2 * k * b_k, b_k, b_mn), idesc, k > 0);
+        umma_commit(&bar);
+    }
+    const bool ok = mbar_wait(&bar, 0);
+    tc_fence_after_sync();
+    if (ok) {
+        uint32_t v[16];
+        tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16), v);
+        tmem_ld_wait();
+        for (int c = 0; c < 16; c++) out[(size_t)tid * 16 + c] = __uint_as_float(v[c]);
+    } else if (tid == 0) set_status(status, ST_MBAR_TIMEOUT | 12);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 32);
+}
+
+// binds: 0 = A fp16 [128][K], 1 = B fp16 [16][K], 2 = out fp32 [128][16], 3 = umma_test_args
+static cudaError_t launch_umma_test(const QwLaunch &L) {
+    const umma_test_args a = L.bytes<umma_test_args>(3);
+    QW_CHECK_ARG(L.has_bytes(3, 8) && a.K >= 16 && a.K <= 128 && a.K % 16 == 0 && a.order <= 1);
+    QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(1) && L.buf<void>(2) && L.avail(0) >= 128 * a.K * 2 && L.avail(1) >= 16 * a.K * 2 && L.avail(2) >= 128 * 16 * 4);
+    QW_CHECK_ARG((((uintptr_t)L.buf<void>(0) | (uintptr_t)L.buf<void>(1)) & 15) == 0);
+    qw_launch(umma_test_k, 1, 128, 0, L.stream, L.buf<__half>(0), L.buf<__half>(1), L.buf<float>(2), a, L.status);
+    return cudaGetLastError();
+}
+QW_FAMILY(umma_test, launch_umma_test, 128)
