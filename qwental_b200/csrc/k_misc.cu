@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "moe_sel.h"
 #include "qw_kern.h"
+#include <cooperative_groups.h>
 
 using namespace qw;
 
@@ -103,6 +104,52 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
     }
     for (uint32_t d = tid + 4 * nth; d < D; d += nth) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
 }
+// The MoE-combine form for D = 2048 (the step's hot case: it sits between the expert FFN and the next projection, and
+// nothing else can run beside it).  A token is served by a cluster of 8 blocks of 256 threads, one column per thread: the
+// twelve loads of a column are independent, the blocks are small enough to be resident next to the FFN's blocks while they
+// wait for it, and the sum of squares of the row meets through the cluster's shared memory (the eight partial sums are
+// added in block order by every block, so the result does not depend on timing).  grid (8 nb) x 256, cluster 8.
+__global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_k(float *h, const float *w, __half *x, const moe_sel *ms, const float *Pg,
+                                                                                    uint32_t topk, const unsigned *flags, const unsigned *seq,
+                                                                                    uint32_t nranks, unsigned *status) {
+    constexpr uint32_t D = 2048;
+    namespace cg = cooperative_groups;
+    __shared__ float tmp[8];
+    __shared__ float part;
+    cg::cluster_group cl = cg::this_cluster();
+    const uint32_t t = blockIdx.x >> 3, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, d = (blockIdx.x & 7) * 256 + tid;
+    pdl_launch();
+    const float wd = w[d];  // the norm weights are static
+    pdl_wait();
+    if (nranks > 1) ep_wait(flags, seq, nranks, status);
+    float wk[MOE_MAXK], pv[MOE_MAXK];
+#pragma unroll
+    for (uint32_t s = 0; s < MOE_MAXK; s++) wk[s] = s <= topk ? ms->w[t][s] : 0.f;
+#pragma unroll
+    for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? Pg[((size_t)t * (topk + 1) + s) * D + d] : 0.f;
+    float v = h[(size_t)t * D + d];
+    float o = 0.f;
+#pragma unroll
+    for (uint32_t s = 0; s < MOE_MAXK; s++)
+        if (s <= topk) o = fmaf(wk[s], pv[s], o);  // rank order, as moe_cmb
+    v += __half2float(__float2half_rn(o));
+    h[(size_t)t * D + d] = v;
+    const float ss = warp_sum(v * v);
+    if (lane == 0) tmp[warp] = ss;
+    __syncthreads();
+    if (tid == 0) {
+        float b = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) b += tmp[i];
+        part = b;
+    }
+    cl.sync();
+    float tot = 0.f;
+#pragma unroll
+    for (unsigned r = 0; r < 8; r++) tot += *cl.map_shared_rank(&part, r);
+    x[(size_t)t * D + d] = __float2half_rn(v * rsqrtf(tot / D + 1e-6f) * wd);
+    cl.sync();  // nobody leaves while its partial sum may still be read
+}
 static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
     struct { uint32_t nb, D; } a = L.bytes<decltype(a)>(4);
     QW_CHECK_ARG(L.buf<void>(0) && L.buf<void>(2) && L.buf<void>(3) && L.has_bytes(4, 8) && a.nb >= 1 && a.nb <= 64);
@@ -114,6 +161,11 @@ static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
         // (one sequence number per rank), 8 = this rank's sequence counter
         const uint32_t nranks = (uint32_t)L.def("EPX", 1);
         if (nranks > 1) QW_CHECK_ARG(nranks <= 8 && L.buf<void>(7) && L.avail(7) >= nranks * 4 && L.buf<void>(8) && L.avail(8) >= 4);
+        if (a.D == 2048) {
+            qw_launch(cmb_rmsnorm_cl_k, a.nb * 8, 256, 0, L.stream, L.buf<float>(0), L.buf<float>(2), L.buf<__half>(3), L.buf<moe_sel>(5), L.buf<float>(6), topk,
+                      nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
+            return cudaGetLastError();
+        }
         qw_launch(add_rmsnorm_k<2>, a.nb, 1024, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, L.buf<moe_sel>(5), L.buf<float>(6), topk,
                   nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
     } else if (L.def("ADD", 0)) {
