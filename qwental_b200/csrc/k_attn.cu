@@ -201,14 +201,17 @@ QW_FAMILY(qsa_attn_simt, launch_qsa_attn, 256)
 // ------------------------------------------------------------------------------------------------ attention core, tensor cores
 // Same contract and partial format as qsa_attn_simt above, computed with warp MMAs on K / V tiles staged by 2-D
 // tiled TMA copies (cp.async.bulk.tensor, 128-byte swizzle) -- this is the family the engine uses ("qsa_attn").
-// Block = 4 warps = the four 64-token quarters of one 256-token page for one kv head; a warp walks its quarter in
-// steps of 16 tokens with its own two mbarriers (K buffer, V buffer), so no block-wide synchronisation happens
-// until the final merge of the four quarters.
+// Persistent warps: the (page chunk, kv head, slot) tasks of the launch are numbered slot-major and warp number w of the
+// grid takes tasks w, w + W, w + 2W, ...  A warp owns a task completely: it walks the page's up to 256 tokens in steps
+// of 16 with its own K and V tile and two mbarriers, keeps the online-softmax state of the 8 query heads in registers and
+// writes the partial straight from them -- no block-wide synchronisation after the start, and the tiles of a warp's next
+// task are requested while the current one finishes, so a warp always has a copy in flight.
 //   scores   S^T[16 tokens][8 heads] = K[16][256] . Q^T            16 MMAs m16n8k16, A = K rows via ldmatrix
 //   softmax  online, per head, over the token rows (lanes that share t = lane % 4 hold the same two heads)
 //   output   O^T[256 dims][8 heads] += V^T[256][16 tokens] . P^T   16 MMAs, A = V via ldmatrix.trans,
 //            B = the probabilities moved from accumulator layout to operand layout with four shuffles
-// The 8 query heads of the kv head fill the MMA's N dimension exactly: nothing is padded.
+// The 8 query heads of the kv head fill the MMA's N dimension exactly: nothing is padded.  What a task computes depends
+// only on its slot's own length, never on which warp runs it or on the other slots of the batch.
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)),
                  "l"(tm), "r"(x), "r"(y), "r"(smem_u32(bar))
@@ -222,30 +225,73 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
 }
 
 constexpr int AT_WARP_BYTES = 16384;  // per warp: K tile 8 KB + V tile 8 KB (4 swizzled boxes of 16 rows x 128 B each)
+constexpr int AT_TAB_BYTES = 1024;    // per block: first task of every slot [65], tokens [64], slot id [64]
+constexpr int AT_SMEM = 4 * AT_WARP_BYTES + 64 + AT_TAB_BYTES + 1024;
+constexpr int AT_BLOCKS_PER_SM = 3;   // what the shared memory and the registers of the kernel allow
 
 __global__ void __launch_bounds__(128) qsa_attn_mma_k(const __grid_constant__ CUtensorMap tm, const __half *q, const int32_t *pt, const int32_t *posv,
                                                       const int32_t *sids, float *part, qsa_args a, uint32_t QH, uint32_t KVH, unsigned *status) {
     constexpr uint32_t HD = 256;
     extern __shared__ uint8_t smem_raw[];
-    pdl_sync();
-    const uint32_t ch = blockIdx.x, kvh = blockIdx.y, ts = blockIdx.z;
-    const uint32_t ntok = (uint32_t)posv[ts] + 1;
-    if (ch * QSA_PAGE >= ntok) return;
-    const uint32_t n = min((uint32_t)QSA_PAGE, ntok - ch * QSA_PAGE);
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     uint8_t *smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);  // swizzled boxes need 1024-byte alignment
     uint8_t *Kb = smem + warp * AT_WARP_BYTES, *Vb = Kb + 8192;
     uint64_t *bars = (uint64_t *)(smem + 4 * AT_WARP_BYTES) + warp * 2;
-    const uint32_t tok0 = warp * 64;
-    const uint32_t wn = n > tok0 ? min(64u, n - tok0) : 0, steps = (wn + 15) / 16;
+    uint32_t *first = (uint32_t *)(smem + 4 * AT_WARP_BYTES + 64), *ntokv = first + 65, *sidv = ntokv + 64;
     if (lane == 0) {
         mbar_init(&bars[0], 1);
         mbar_init(&bars[1], 1);
         mbar_init_fence();
     }
-    __syncwarp();
-    const uint32_t page = (uint32_t)pt[(size_t)sids[ts] * a.max_pages + ch];
-    const int rowK = (int)(((page * a.nlayers + a.layer) * 2) * KVH * QSA_PAGE + kvh * QSA_PAGE + tok0), rowV = rowK + (int)(KVH * QSA_PAGE);
+    pdl_sync();
+    // pages of every slot and their running sum: slot s owns page numbers first[s] .. first[s + 1] - 1 of the launch
+    if (warp == 0) {
+        uint32_t c[2], nt[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t sl = lane + 32 * h;
+            nt[h] = sl < a.nb ? (uint32_t)posv[sl] + 1 : 0;
+            c[h] = min((nt[h] + QSA_PAGE - 1) / QSA_PAGE, a.max_chunks);
+            ntokv[sl] = nt[h];
+            sidv[sl] = sl < a.nb ? (uint32_t)sids[sl] : 0;
+        }
+        uint32_t s0 = c[0], s1 = c[1];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t u0 = __shfl_up_sync(0xffffffffu, s0, o), u1 = __shfl_up_sync(0xffffffffu, s1, o);
+            if (lane >= (uint32_t)o) {
+                s0 += u0;
+                s1 += u1;
+            }
+        }
+        const uint32_t tot0 = __shfl_sync(0xffffffffu, s0, 31);
+        first[lane] = s0 - c[0];
+        first[32 + lane] = tot0 + s1 - c[1];
+        if (lane == 31) first[64] = tot0 + s1;
+    }
+    __syncthreads();
+    const uint32_t tasks = first[64] * KVH, W = gridDim.x * 4;
+    struct Task {
+        uint32_t ts, kvh, ch, n;
+        int rowK;
+    };
+    auto task_of = [&](uint32_t i) {  // i < tasks
+        Task k;
+        const uint32_t pi = i / KVH;
+        k.kvh = i - pi * KVH;
+        uint32_t lo = 0, hi = a.nb;  // largest slot with first[slot] <= pi (every slot of the step has at least one page)
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (first[mid] <= pi) lo = mid;
+            else hi = mid;
+        }
+        k.ts = lo;
+        k.ch = pi - first[lo];
+        k.n = min((uint32_t)QSA_PAGE, ntokv[lo] - k.ch * QSA_PAGE);
+        const uint32_t page = (uint32_t)pt[(size_t)sidv[lo] * a.max_pages + k.ch];
+        k.rowK = (int)(((page * a.nlayers + a.layer) * 2) * KVH * QSA_PAGE + k.kvh * QSA_PAGE);
+        return k;
+    };
     auto load = [&](uint8_t *dst, uint64_t *bar, int row) {
         if (lane == 0) {
             fence_proxy_async();  // the warp's reads of this buffer (ordered by __syncwarp) before the async-proxy writes
@@ -254,137 +300,127 @@ __global__ void __launch_bounds__(128) qsa_attn_mma_k(const __grid_constant__ CU
             for (int db = 0; db < 4; db++) tma_load_2d(dst + db * 2048, &tm, db * 64, row, bar);
         }
     };
-    if (steps) {
-        load(Kb, &bars[0], rowK);
-        load(Vb, &bars[1], rowV);
-    }
-    // Q as B fragments (k = dim, n = head g), pre-scaled by HD^-1/2 = 1/16 (exact in fp16)
-    uint32_t qf[16][2];
-    {
-        const __half *qp = q + ((size_t)ts * QH + kvh * 8 + g) * HD + 2 * t;
-        const __half2 sc = __floats2half2_rn(0.0625f, 0.0625f);
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            const __half2 v0 = __hmul2(*(const __half2 *)(qp + 16 * ks), sc), v1 = __hmul2(*(const __half2 *)(qp + 16 * ks + 8), sc);
-            qf[ks][0] = *(const uint32_t *)&v0;
-            qf[ks][1] = *(const uint32_t *)&v1;
-        }
-    }
-    float o[16][4];
-#pragma unroll
-    for (int dt = 0; dt < 16; dt++) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     // ldmatrix lane roles: matrix mi = lane / 8, row r8 = lane % 8 (the swizzle key of that row)
     const uint32_t mi = lane >> 3, r8 = lane & 7;
     const uint32_t kbase = smem_u32(Kb) + ((mi & 1) * 8 + r8) * 128, vbase = smem_u32(Vb) + ((mi >> 1) * 8 + r8) * 128;
+    const int vrows = (int)(KVH * QSA_PAGE);  // rows from a page's K tile to its V tile
+    uint32_t kph = 0, vph = 0;  // copies waited for so far on the K / V barrier (their parity selects the phase)
     bool ok = true;
-    for (uint32_t step = 0; step < steps; step++) {
-        if (!mbar_wait(&bars[0], step & 1)) { ok = false; break; }
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ks = 0; ks < 16; ks++) {
-            uint32_t af[4];
-            ldsm_x4(af, kbase + (ks >> 2) * 2048 + ((((ks & 3) * 2 + (mi >> 1)) ^ r8) << 4));
-            mma_f16(s, af, qf[ks][0], qf[ks][1], s);
-        }
-        __syncwarp();
-        if (step + 1 < steps) load(Kb, &bars[0], rowK + (int)(step + 1) * 16);
-        const uint32_t ta = step * 16 + g;
-        if (ta >= wn) s[0] = s[1] = -INFINITY;
-        if (ta + 8 >= wn) s[2] = s[3] = -INFINITY;
-        float x0 = fmaxf(s[0], s[2]), x1 = fmaxf(s[1], s[3]);
-#pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
-            x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
-        }
-        const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
-        const float a0 = expf(m0 - n0), a1 = expf(m1 - n1);
-        const float p0 = expf(s[0] - n0), p1 = expf(s[1] - n1), p2 = expf(s[2] - n0), p3 = expf(s[3] - n1);
-        l0 = l0 * a0 + (p0 + p2);
-        l1 = l1 * a1 + (p1 + p3);
-        m0 = n0;
-        m1 = n1;
-#pragma unroll
-        for (int dt = 0; dt < 16; dt++) {
-            o[dt][0] *= a0;
-            o[dt][1] *= a1;
-            o[dt][2] *= a0;
-            o[dt][3] *= a1;
-        }
-        // probabilities: accumulator layout (token g / g+8, heads 2t, 2t+1) -> B operand layout (tokens 2t, 2t+1 / +8,
-        // head g).  Each probability travels as an fp16 high part plus an fp16 remainder (two MMAs per dim tile), so the
-        // weighted sum keeps ~22 bits of p instead of 11.
-        const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-        const __half2 r01 = __floats2half2_rn(p0 - f01.x, p1 - f01.y), r23 = __floats2half2_rn(p2 - f23.x, p3 - f23.y);
-        const int srcA = (2 * t) * 4 + (g >> 1), srcB = srcA + 4;
-        const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
-        auto to_b = [&](const __half2 &h) {
-            const uint32_t u = *(const uint32_t *)&h;
-            return __byte_perm(__shfl_sync(0xffffffffu, u, srcA), __shfl_sync(0xffffffffu, u, srcB), sel);
-        };
-        const uint32_t b0 = to_b(h01), b1 = to_b(h23), c0 = to_b(r01), c1 = to_b(r23);
-        if (!mbar_wait(&bars[1], step & 1)) { ok = false; break; }
-#pragma unroll
-        for (int dt = 0; dt < 16; dt++) {
-            uint32_t af[4];
-            ldsm_x4_t(af, vbase + (dt >> 2) * 2048 + ((((dt & 3) * 2 + (mi & 1)) ^ r8) << 4));
-            mma_f16(o[dt], af, b0, b1, o[dt]);
-            mma_f16(o[dt], af, c0, c1, o[dt]);
-        }
-        __syncwarp();
-        if (step + 1 < steps) load(Vb, &bars[1], rowV + (int)(step + 1) * 16);
+    uint32_t i = blockIdx.x * 4 + warp;
+    Task cur{};
+    if (i < tasks) {
+        cur = task_of(i);
+        load(Kb, &bars[0], cur.rowK);
+        load(Vb, &bars[1], cur.rowK + vrows);
     }
-    if (!ok && lane == 0) set_status(status, ST_MBAR_TIMEOUT | 4);
-    // this quarter's totals, then the merge of the four quarters in quarter order
+    while (i < tasks && ok) {
+        const uint32_t steps = (cur.n + 15) / 16;
+        const bool more = i + W < tasks;
+        Task nxt{};
+        if (more) nxt = task_of(i + W);  // looked up now: its first tiles are requested as soon as this task's last ones are consumed
+        // Q as B fragments (k = dim, n = head g), pre-scaled by HD^-1/2 = 1/16 (exact in fp16)
+        uint32_t qf[16][2];
+        {
+            const __half *qp = q + ((size_t)cur.ts * QH + cur.kvh * 8 + g) * HD + 2 * t;
+            const __half2 sc = __floats2half2_rn(0.0625f, 0.0625f);
 #pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
-    }
-    float *osm = (float *)(smem + warp * AT_WARP_BYTES);  // [8 heads][256 dims], then m[8], l[8]; the warp's own, fully consumed tiles
-    __syncwarp();
-#pragma unroll
-    for (int dt = 0; dt < 16; dt++) {
-        osm[(2 * t) * HD + 16 * dt + g] = o[dt][0];
-        osm[(2 * t + 1) * HD + 16 * dt + g] = o[dt][1];
-        osm[(2 * t) * HD + 16 * dt + g + 8] = o[dt][2];
-        osm[(2 * t + 1) * HD + 16 * dt + g + 8] = o[dt][3];
-    }
-    if (g == 0) {
-        osm[8 * HD + 2 * t] = m0;
-        osm[8 * HD + 2 * t + 1] = m1;
-        osm[8 * HD + 8 + 2 * t] = l0;
-        osm[8 * HD + 8 + 2 * t + 1] = l1;
-    }
-    __syncthreads();
-    for (uint32_t e = threadIdx.x; e < 8 * HD; e += 128) {
-        const uint32_t h = e >> 8, d = e & 255;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-            const float *ow = (const float *)(smem + w * AT_WARP_BYTES);
-            if (ow[8 * HD + 8 + h] > 0.f) M = fmaxf(M, ow[8 * HD + h]);
-        }
-        float L = 0.f, acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-            const float *ow = (const float *)(smem + w * AT_WARP_BYTES);
-            const float lw = ow[8 * HD + 8 + h];
-            if (lw > 0.f) {
-                const float wt = expf(ow[8 * HD + h] - M);
-                L = fmaf(lw, wt, L);
-                acc = fmaf(ow[h * HD + d], wt, acc);
+            for (int ks = 0; ks < 16; ks++) {
+                const __half2 v0 = __hmul2(*(const __half2 *)(qp + 16 * ks), sc), v1 = __hmul2(*(const __half2 *)(qp + 16 * ks + 8), sc);
+                qf[ks][0] = *(const uint32_t *)&v0;
+                qf[ks][1] = *(const uint32_t *)&v1;
             }
         }
-        float *po = part + (((size_t)ts * a.max_chunks + ch) * QH + kvh * 8 + h) * (HD + 2);
-        po[d] = acc;
-        if (d == 0) {
-            po[HD] = M;
-            po[HD + 1] = L;
+        float o[16][4];
+#pragma unroll
+        for (int dt = 0; dt < 16; dt++) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        for (uint32_t step = 0; step < steps; step++) {
+            if (!mbar_wait(&bars[0], kph & 1)) { ok = false; break; }
+            kph++;
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                uint32_t af[4];
+                ldsm_x4(af, kbase + (ks >> 2) * 2048 + ((((ks & 3) * 2 + (mi >> 1)) ^ r8) << 4));
+                mma_f16(s, af, qf[ks][0], qf[ks][1], s);
+            }
+            __syncwarp();
+            if (step + 1 < steps) load(Kb, &bars[0], cur.rowK + (int)(step + 1) * 16);
+            else if (more) load(Kb, &bars[0], nxt.rowK);
+            const uint32_t ta = step * 16 + g;
+            if (ta >= cur.n) s[0] = s[1] = -INFINITY;
+            if (ta + 8 >= cur.n) s[2] = s[3] = -INFINITY;
+            float x0 = fmaxf(s[0], s[2]), x1 = fmaxf(s[1], s[3]);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {
+                x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, off));
+                x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, off));
+            }
+            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+            const float a0 = expf(m0 - n0), a1 = expf(m1 - n1);
+            const float p0 = expf(s[0] - n0), p1 = expf(s[1] - n1), p2 = expf(s[2] - n0), p3 = expf(s[3] - n1);
+            l0 = l0 * a0 + (p0 + p2);
+            l1 = l1 * a1 + (p1 + p3);
+            m0 = n0;
+            m1 = n1;
+#pragma unroll
+            for (int dt = 0; dt < 16; dt++) {
+                o[dt][0] *= a0;
+                o[dt][1] *= a1;
+                o[dt][2] *= a0;
+                o[dt][3] *= a1;
+            }
+            // probabilities: accumulator layout (token g / g+8, heads 2t, 2t+1) -> B operand layout (tokens 2t, 2t+1 / +8,
+            // head g).  Each probability travels as an fp16 high part plus an fp16 remainder (two MMAs per dim tile), so the
+            // weighted sum keeps ~22 bits of p instead of 11.
+            const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 r01 = __floats2half2_rn(p0 - f01.x, p1 - f01.y), r23 = __floats2half2_rn(p2 - f23.x, p3 - f23.y);
+            const int srcA = (2 * t) * 4 + (g >> 1), srcB = srcA + 4;
+            const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+            auto to_b = [&](const __half2 &h) {
+                const uint32_t u = *(const uint32_t *)&h;
+                return __byte_perm(__shfl_sync(0xffffffffu, u, srcA), __shfl_sync(0xffffffffu, u, srcB), sel);
+            };
+            const uint32_t b0 = to_b(h01), b1 = to_b(h23), c0 = to_b(r01), c1 = to_b(r23);
+            if (!mbar_wait(&bars[1], vph & 1)) { ok = false; break; }
+            vph++;
+#pragma unroll
+            for (int dt = 0; dt < 16; dt++) {
+                uint32_t af[4];
+                ldsm_x4_t(af, vbase + (dt >> 2) * 2048 + ((((dt & 3) * 2 + (mi & 1)) ^ r8) << 4));
+                mma_f16(o[dt], af, b0, b1, o[dt]);
+                mma_f16(o[dt], af, c0, c1, o[dt]);
+            }
+            __syncwarp();
+            if (step + 1 < steps) load(Vb, &bars[1], cur.rowK + vrows + (int)(step + 1) * 16);
+            else if (more) load(Vb, &bars[1], nxt.rowK + vrows);
         }
+        if (!ok) break;
+        // the page's totals (the lanes that share t hold the same two heads), then the partial straight from the registers
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+        }
+        float *po0 = part + (((size_t)cur.ts * a.max_chunks + cur.ch) * QH + cur.kvh * 8 + 2 * t) * (HD + 2), *po1 = po0 + (HD + 2);
+#pragma unroll
+        for (int dt = 0; dt < 16; dt++) {
+            po0[16 * dt + g] = o[dt][0];
+            po1[16 * dt + g] = o[dt][1];
+            po0[16 * dt + g + 8] = o[dt][2];
+            po1[16 * dt + g + 8] = o[dt][3];
+        }
+        if (g == 0) {
+            po0[HD] = m0;
+            po0[HD + 1] = l0;
+            po1[HD] = m1;
+            po1[HD + 1] = l1;
+        }
+        cur = nxt;
+        i += W;
     }
+    if (!ok && lane == 0) set_status(status, ST_MBAR_TIMEOUT | 4);
 }
 
 // cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the library has no link
@@ -430,10 +466,12 @@ static cudaError_t launch_qsa_attn_mma(const QwLaunch &L) {
     QW_CHECK_ARG(((uintptr_t)L.buf<void>(1) & 15) == 0 && L.avail(1) >= 512 && L.avail(1) / 512 < 0x7fffffffull);
     const CUtensorMap *tm = attn_tensor_map(L.buf<void>(1), L.avail(1) / 512 * 512);
     QW_CHECK_ARG(tm != nullptr);
-    const size_t smem = 4 * AT_WARP_BYTES + 64 + 1024;
+    const size_t smem = AT_SMEM;
     cudaError_t e = cudaFuncSetAttribute(qsa_attn_mma_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    qw_launch(qsa_attn_mma_k, dim3(a.max_chunks, KVH, a.nb), 128, smem, L.stream, *tm, L.buf<__half>(0), L.buf<int32_t>(2), L.buf<int32_t>(3),
+    // persistent: as many blocks as fit on the device at once, or fewer when the step cannot have that many tasks
+    const uint32_t most = (a.nb * a.max_chunks * KVH + 3) / 4, cap = (uint32_t)L.sm_count * AT_BLOCKS_PER_SM;
+    qw_launch(qsa_attn_mma_k, most < cap ? most : cap, 128, smem, L.stream, *tm, L.buf<__half>(0), L.buf<int32_t>(2), L.buf<int32_t>(3),
                                                                           L.buf<int32_t>(4), L.buf<float>(5), a, QH, KVH, L.status);
     return cudaGetLastError();
 }
@@ -562,11 +600,14 @@ extern "C" int qw_attn_decode_static(const void *q, const void *kv_pool, size_t 
     CUtensorMap tm;  // encoded on the stack: no allocation
     if (!attn_encode_map(&tm, kv_pool, kv_pool_bytes / 512 * 512)) return fail(-3, "tensor map encoding failed");
     qsa_args a = {nb, layer, nlayers, qkv_stride, max_pages, max_chunks, 0, 0};
-    const size_t smem = 4 * AT_WARP_BYTES + 64 + 1024;
+    const size_t smem = AT_SMEM;
     cudaError_t e = cudaFuncSetAttribute(qsa_attn_mma_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(-3, cudaGetErrorString(e));
     cudaStream_t st = (cudaStream_t)stream;
-    qsa_attn_mma_k<<<dim3(max_chunks, KVH, nb), 128, smem, st>>>(tm, (const __half *)q, page_table, pos, slot_ids, part, a, QH, KVH, nullptr);
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return fail(-3, "cannot read the SM count");
+    const uint32_t most = (nb * max_chunks * KVH + 3) / 4, cap = (uint32_t)sms * AT_BLOCKS_PER_SM;
+    qsa_attn_mma_k<<<most < cap ? most : cap, 128, smem, st>>>(tm, (const __half *)q, page_table, pos, slot_ids, part, a, QH, KVH, nullptr);
     qsa_merge_k<<<dim3(QH, nb), 1024, 0, st>>>(part, (const __half *)qkv, (__half *)y, pos, a, QH);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(-3, cudaGetErrorString(e));
