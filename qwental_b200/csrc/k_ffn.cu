@@ -5,8 +5,8 @@
 // Work.  An item is one pass (up to 8 token columns) of one distinct expert, or of the shared expert.  A decode step of 16
 // slots touches about a hundred items -- fewer than there are SMs, and far fewer when the experts are spread over ranks --
 // so an item is cut into pieces: GT gate/up pieces (64 intermediate indices each, all of K = D) and DT down pieces (128
-// output rows each, all of K = I).  Persistent blocks (one per SM) take an even, contiguous share of the gate/up piece
-// list, then an even share of the down piece list.  H = silu(gate x) * (up x) travels from the blocks that ran an item's
+// output rows each, all of K = I).  Persistent blocks (one per SM for IQ3_S, two for IQ3X) take an even, contiguous share of
+// the gate/up piece list, then an even share of the down piece list.  H = silu(gate x) * (up x) travels from the blocks that ran an item's
 // gate/up pieces to the blocks that run its down pieces through a small global buffer (it stays in L2) and a per-item
 // counter: a block only ever waits for H after it has finished all of its own gate/up pieces, so every wait is on blocks
 // that are running and never wait themselves.  The arithmetic of a piece does not depend on which block runs it.
@@ -31,7 +31,6 @@
 #include "qmv_core.cuh"
 #include "qw_kern.h"
 #include <cuda.h>
-#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -47,18 +46,22 @@ constexpr int FFN_SYNC_BYTES = MOE_FFN_SYNC_BYTES;
 constexpr int FFN_PITCH = 240;                   // IQ3_S: bytes between staged gate/up rows
 constexpr int FFN_D = 2048, FFN_I = 512;         // the shapes this kernel is built for (the launcher refuses others)
 constexpr int FFN_MAXG = 520;                    // groups kept in shared memory: E <= 512 experts (+ end markers)
-// Shared-memory plan per weight format.  FMT 0 = the raw IQ3_S blocks (64 KB codebook, three 30 KB stages, one activation
-// slot); FMT 1 = IQ3X (iq3x.cuh: no codebook, four 34 KB stages, two activation slots).
+constexpr int FFN_RECS = 8;                      // items a block's gate/up share (and its down share) can touch
+// Shared-memory plan per weight format.  FMT 0 = the raw IQ3_S blocks: 64 KB codebook, three 30 KB stages, one block per SM.
+// FMT 1 = IQ3X (iq3x.cuh): no codebook and 56 registers per thread, so two blocks share an SM (two 34 KB stages each):
+// while the warps of one wait -- for a stage, for their partner's partial sums, for a fixed-latency result -- the other's issue.
 template <int FMT>
 struct FfnCfg {
-    static constexpr int STG = FMT ? 4 : 3;
+    static constexpr int PER_SM = FMT ? 2 : 1;
+    static constexpr int STG = FMT ? 2 : 3;
     static constexpr int SLOT = FMT ? IQ3X_STAGE : 128 * FFN_PITCH;   // 30720 also holds an IQ3_S down tile of 128 x 220 bytes
-    static constexpr int TAB = FMT ? 0 : 65536;
-    static constexpr int NACT = FMT ? 2 : 1;
+    static constexpr int TAB = FMT ? 256 : 65536;                      // IQ3_S: the codebook; IQ3X: the multiply-add constants of the 16 scale values
+    static constexpr int NACT = 1;
     static constexpr int OFF_TAB = 128;
-    static constexpr int OFF_PRE = OFF_TAB + TAB;                      // uint32 pre[FFN_MAXG], off[FFN_MAXG], ue[FFN_MAXG] of the selection record
-    static constexpr int OFF_RED = OFF_PRE + 3 * FFN_MAXG * 4 + 32;    // [2][8 row groups][32 lanes] float4  (6272 = 49 * 128)
-    static constexpr int OFF_XS = OFF_RED + 2 * 8 * 32 * 16;           // the activation slots, then the stages
+    static constexpr int OFF_PRE = OFF_TAB + TAB;                      // uint32 pre[FFN_MAXG] of the selection record, then 2 x FFN_RECS item records of 32 bytes
+    static constexpr int OFF_REC = OFF_PRE + FFN_MAXG * 4;
+    static constexpr int OFF_RED = OFF_REC + 2 * FFN_RECS * 32 + 32;   // [2][8 row groups][32 lanes] float4
+    static constexpr int OFF_XS = (OFF_RED + 2 * 8 * 32 * 16 + 127) / 128 * 128;  // the activation slots, then the stages
 };
 
 struct FfnP {
@@ -87,21 +90,22 @@ __device__ __forceinline__ void bulk_s(uint32_t dst, const void *src, uint32_t b
 }
 __device__ __forceinline__ void bar_sync_n(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 
-struct FfnItem {
-    uint32_t u, e0, cnt, c0, ncols;
-    bool shared;
+struct __align__(16) FfnItem {
+    uint32_t e0, c0, ncols, erow;  // first entry of the group, first column of the pass, columns, expert's row in the weight buffers
+    uint32_t shared, pad[3];
 };
-// item number w -> (group, pass): routed groups first (pre[] = passes before each group), then the shared expert's passes
-__device__ __forceinline__ FfnItem ffn_item(const uint32_t *pre, uint32_t U, uint32_t nb, uint32_t w) {
-    const uint32_t *off = pre + FFN_MAXG;
-    FfnItem it;
+// item number w -> (group, pass): routed groups first (pre[] = passes before each group, in shared memory), then the shared
+// expert's passes.  The group's entries and expert come from the selection record in global memory.
+__device__ __forceinline__ FfnItem ffn_item(const uint32_t *pre, const moe_sel *ms, uint32_t U, uint32_t nb, uint32_t ebase, uint32_t w) {
+    FfnItem it{};
     const uint32_t routed = pre[U];
+    uint32_t cnt;
     if (w >= routed) {
-        it.shared = true;
-        it.u = U;
+        it.shared = 1;
         it.e0 = 0;
-        it.cnt = nb;
+        cnt = nb;
         it.c0 = (w - routed) * 8;
+        it.erow = 0;
     } else {
         uint32_t lo = 0, hi = U;  // largest u with pre[u] <= w
         while (hi - lo > 1) {
@@ -109,13 +113,13 @@ __device__ __forceinline__ FfnItem ffn_item(const uint32_t *pre, uint32_t U, uin
             if (pre[mid] <= w) lo = mid;
             else hi = mid;
         }
-        it.shared = false;
-        it.u = lo;
-        it.e0 = off[lo];
-        it.cnt = off[lo + 1] - it.e0;
+        it.shared = 0;
+        it.e0 = ms->off[lo];
+        cnt = ms->off[lo + 1] - it.e0;
         it.c0 = (w - pre[lo]) * 8;
+        it.erow = ms->ue[lo] - ebase;
     }
-    it.ncols = it.cnt - it.c0 < 8 ? it.cnt - it.c0 : 8;
+    it.ncols = cnt - it.c0 < 8 ? cnt - it.c0 : 8;
     return it;
 }
 // column col of the item -> (token, rank)
@@ -225,19 +229,19 @@ __device__ __forceinline__ void ffn_unit(uint32_t u0, uint32_t u1, int t, uint32
     ffn_sub<7, PLANES>(u0, u1, t, h0, h1, tabl, zr, bh, bl, have, xv, xl, acc);
 }
 
-// ---- IQ3X units (iq3x.cuh): rec = shared address of the row record, kh = which super-block of the pair
+// ---- IQ3X units (iq3x.cuh): rec = shared address of the row record, kh = which super-block of the pair.
+// The sub-block's integer scale S = 1 + 2 s is folded into the weights: w * S is an integer below 2048, exact in fp16, and
+// comes out of the same multiply-add that removes the exponent bias -- its two constants (S, -1040 S) and (S / 16, -80 S)
+// are looked up per (row, sub-block) in a 16-entry table -- so the MMAs accumulate over the whole super-block and the block
+// scale d is applied once per 256 weights.
 struct XHdr {
-    float d, d2;
-    uint32_t sclo, schi;
+    float d;
+    uint32_t sc;  // the eight 4-bit scales, sub-block ib in bits 4 ib .. 4 ib + 3
 };
 __device__ __forceinline__ XHdr x_hdr(uint32_t rec, int kh) {
     XHdr h;
     h.d = h2f((uint16_t)lds_u16<256>(rec + 2 * kh));
-    h.d2 = h.d + h.d;
-    uint32_t sc;
-    asm volatile("ld.shared.u32 %0, [%1+260];" : "=r"(sc) : "r"(rec + 4 * kh));
-    h.sclo = sc & 0x0f0f0f0fu;
-    h.schi = (sc >> 4) & 0x0f0f0f0fu;
+    asm volatile("ld.shared.u32 %0, [%1+260];" : "=r"(h.sc) : "r"(rec + 4 * kh));
     return h;
 }
 template <int OFF>
@@ -246,12 +250,23 @@ __device__ __forceinline__ uint32_t lds_u32_off(uint32_t a) {
     asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
     return v;
 }
+// the lane word's eight codes times S as four packed fp16 pairs; c = the table entry of the sub-block's scale
+__device__ __forceinline__ void iq3x_word_s(uint32_t q, const uint4 &c, uint32_t (&w)[4]) {
+    const uint32_t r = __funnelshift_r(q, q, 8);
+    const uint32_t h0 = lop3_and_or(q, 0x001E001Eu, 0x64016401u), h1 = lop3_and_or(q, 0x01E001E0u, 0x64106410u);
+    const uint32_t h2 = lop3_and_or(r, 0x001E001Eu, 0x64016401u), h3 = lop3_and_or(r, 0x01E001E0u, 0x64106410u);
+    const __half2 m0 = *(const __half2 *)&c.x, a0 = *(const __half2 *)&c.y, m1 = *(const __half2 *)&c.z, a1 = *(const __half2 *)&c.w;
+    const __half2 v0 = __hfma2(*(const __half2 *)&h0, m0, a0), v1 = __hfma2(*(const __half2 *)&h1, m1, a1);
+    const __half2 v2 = __hfma2(*(const __half2 *)&h2, m0, a0), v3 = __hfma2(*(const __half2 *)&h3, m1, a1);
+    w[0] = *(const uint32_t *)&v0;
+    w[1] = *(const uint32_t *)&v1;
+    w[2] = *(const uint32_t *)&v2;
+    w[3] = *(const uint32_t *)&v3;
+}
 // Software-pipelined over the sub-blocks: the MMAs of sub-block i are issued, then the loads and the decode of sub-block
-// i + 1, then the scaling of sub-block i -- the MMA results are not waited for.  (The predicated B loads keep zeros in lanes
-// whose column is absent.)
+// i + 1 -- the MMA results are not waited for.  (The predicated B loads keep zeros in lanes whose column is absent.)
 struct XDec {
     uint32_t a0[4], a1[4];  // A fragments of the sub-block's two MMAs
-    float dba, dbb;         // scales of rows g and g + 8
 };
 template <int IB, int PLANES>
 __device__ __forceinline__ void x_load(uint32_t c0, uint32_t c1, uint32_t bh, uint32_t bl, uint32_t have, uint32_t (&q)[2], uint4 &xv, uint4 &xl) {
@@ -261,18 +276,18 @@ __device__ __forceinline__ void x_load(uint32_t c0, uint32_t c1, uint32_t bh, ui
     q[1] = lds_u32_off<IB * 16>(c1);
 }
 template <int IB>
-__device__ __forceinline__ void x_decode(const uint32_t (&q)[2], const XHdr &h0, const XHdr &h1, XDec &d) {
+__device__ __forceinline__ void x_decode(const uint32_t (&q)[2], const XHdr &h0, const XHdr &h1, uint32_t stab, XDec &d) {
     uint32_t wa[4], wb[4];
-    iq3x_word(q[0], wa);
-    iq3x_word(q[1], wb);
-    d.dba = fmaf(h0.d2, (float)__byte_perm(IB & 1 ? h0.schi : h0.sclo, 0, 0x4440 | (IB >> 1)), h0.d);
-    d.dbb = fmaf(h1.d2, (float)__byte_perm(IB & 1 ? h1.schi : h1.sclo, 0, 0x4440 | (IB >> 1)), h1.d);
+    const uint32_t s0 = IB == 0 ? (h0.sc << 4) & 0xF0u : (h0.sc >> (4 * IB - 4)) & 0xF0u, s1 = IB == 0 ? (h1.sc << 4) & 0xF0u : (h1.sc >> (4 * IB - 4)) & 0xF0u;
+    iq3x_word_s(q[0], lds_v4(stab + s0), wa);
+    iq3x_word_s(q[1], lds_v4(stab + s1), wb);
     d.a0[0] = wa[0]; d.a0[1] = wb[0]; d.a0[2] = wa[1]; d.a0[3] = wb[1];
     d.a1[0] = wa[2]; d.a1[1] = wb[2]; d.a1[2] = wa[3]; d.a1[3] = wb[3];
 }
-template <int PLANES>
+template <int PLANES, bool FIRST>
 __device__ __forceinline__ void x_mma(const XDec &d, const uint4 &xv, const uint4 &xl, const ZeroRegs &zr, float (&p)[4]) {
-    mma_f16(p, d.a0, xv.x, xv.y, zr.z);
+    if (FIRST) mma_f16(p, d.a0, xv.x, xv.y, zr.z);
+    else mma_f16(p, d.a0, xv.x, xv.y, p);
     mma_f16(p, d.a1, xv.z, xv.w, p);
     if (PLANES == 2) {
         mma_f16(p, d.a0, xl.x, xl.y, p);
@@ -281,21 +296,20 @@ __device__ __forceinline__ void x_mma(const XDec &d, const uint4 &xv, const uint
 }
 // rec0 / rec1: row records of MMA rows g and g + 8
 template <int PLANES>
-__device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int t, const ZeroRegs &zr, uint32_t bh, uint32_t bl, uint32_t have, float (&acc)[4]) {
+__device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int t, uint32_t stab, const ZeroRegs &zr, uint32_t bh, uint32_t bl, uint32_t have,
+                                       float (&acc)[4]) {
     const uint32_t c0 = rec0 + kh * 128 + t * 4, c1 = rec1 + kh * 128 + t * 4;
     uint32_t q[2];
     uint4 xv = make_uint4(0, 0, 0, 0), xl = make_uint4(0, 0, 0, 0);
     XDec dec;
-    float p[4], sa, sb;
+    float p[4];
     x_load<0, PLANES>(c0, c1, bh, bl, have, q, xv, xl);
     const XHdr h0 = x_hdr(rec0, kh), h1 = x_hdr(rec1, kh);
-    x_decode<0>(q, h0, h1, dec);
-#define X_STEP(IB)                                               \
-    x_mma<PLANES>(dec, xv, xl, zr, p);                           \
-    x_load<IB + 1, PLANES>(c0, c1, bh, bl, have, q, xv, xl);     \
-    sa = dec.dba; sb = dec.dbb;                                  \
-    x_decode<IB + 1>(q, h0, h1, dec);                            \
-    acc[0] = fmaf(sa, p[0], acc[0]); acc[1] = fmaf(sa, p[1], acc[1]); acc[2] = fmaf(sb, p[2], acc[2]); acc[3] = fmaf(sb, p[3], acc[3]);
+    x_decode<0>(q, h0, h1, stab, dec);
+#define X_STEP(IB)                                           \
+    x_mma<PLANES, IB == 0>(dec, xv, xl, zr, p);              \
+    x_load<IB + 1, PLANES>(c0, c1, bh, bl, have, q, xv, xl); \
+    x_decode<IB + 1>(q, h0, h1, stab, dec);
     X_STEP(0)
     X_STEP(1)
     X_STEP(2)
@@ -304,8 +318,8 @@ __device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int
     X_STEP(5)
     X_STEP(6)
 #undef X_STEP
-    x_mma<PLANES>(dec, xv, xl, zr, p);
-    acc[0] = fmaf(dec.dba, p[0], acc[0]); acc[1] = fmaf(dec.dba, p[1], acc[1]); acc[2] = fmaf(dec.dbb, p[2], acc[2]); acc[3] = fmaf(dec.dbb, p[3], acc[3]);
+    x_mma<PLANES, false>(dec, xv, xl, zr, p);
+    acc[0] = fmaf(h0.d, p[0], acc[0]); acc[1] = fmaf(h0.d, p[1], acc[1]); acc[2] = fmaf(h1.d, p[2], acc[2]); acc[3] = fmaf(h1.d, p[3], acc[3]);
 }
 
 // PROBE = true is the copy-only twin used to measure what the staging pipeline alone can deliver: the same pieces, the same
@@ -313,7 +327,7 @@ __device__ __forceinline__ void x_unit(uint32_t rec0, uint32_t rec1, int kh, int
 // compute nothing -- the role of the reference's pure-read probes (bench/moe_bw.c:1-3, bench/qmv.c:357-382).
 // (17 warps put five on one scheduler, whose 16 K registers then allow 96 per thread)
 template <bool PROBE, int FMT>
-__global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
+__global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
                                                            const __grid_constant__ CUtensorMap mSG, const __grid_constant__ CUtensorMap mSU, const FfnP p) {
     using C = FfnCfg<FMT>;
     constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT, NACT = C::NACT;
@@ -321,6 +335,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
     uint64_t *bars = (uint64_t *)smem;
     uint64_t *full = bars, *empty = bars + FFN_STG, *tab_bar = bars + 2 * FFN_STG, *actfull = tab_bar + 1, *actfree = actfull + 2;
     uint32_t *pre = (uint32_t *)(smem + C::OFF_PRE);
+    FfnItem *recs = (FfnItem *)(smem + C::OFF_REC);
     float4 *red = (float4 *)(smem + C::OFF_RED);
     constexpr uint32_t D = FFN_D, I = FFN_I, rbI = I / 256 * 110;
     constexpr uint32_t xpitch = D * 2 + 64, hpitch = I * 2 + 64, act_slot = 8 * xpitch;  // a slot holds 8 token rows or 16 H rows
@@ -346,13 +361,15 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             bulk_g2s(smem + C::OFF_TAB, p.tab->grid_u32x32, C::TAB, tab_bar);
         }
     }
+    if (FMT == 1 && tid < 16) {  // constants of the decode multiply-adds for scale field s = tid: (S, -1040 S, S / 16, -80 S) as fp16 pairs, S = 1 + 2 s
+        const float S = (float)(1 + 2 * tid);
+        const __half2 m0 = __float2half2_rn(S), a0 = __float2half2_rn(-1040.0f * S), m1 = __float2half2_rn(S * 0.0625f), a1 = __float2half2_rn(-80.0f * S);
+        *(uint4 *)(smem + C::OFF_TAB + 16 * tid) = make_uint4(*(const uint32_t *)&m0, *(const uint32_t *)&a0, *(const uint32_t *)&m1, *(const uint32_t *)&a1);
+    }
     pdl_wait();  // the selection record, the tokens and Pg belong to earlier kernels
     const moe_sel *ms = p.ms;
-    // groups, their first entries, passes and experts: independent loads, so the whole record is in shared memory after one latency
-    for (uint32_t i = tid; i < 3 * FFN_MAXG; i += FFN_THREADS) {
-        const uint32_t a = i / FFN_MAXG, e = i - a * FFN_MAXG;
-        pre[i] = a == 0 ? ms->pre[e] : a == 1 ? ms->off[e] : ms->ue[e];
-    }
+    // passes before every group: independent loads, so the table is in shared memory after one latency
+    for (uint32_t i = tid; i < FFN_MAXG; i += FFN_THREADS) pre[i] = ms->pre[i];
     const uint32_t U = ms->U, nb = ms->nb, topk = ms->topk;
     __syncthreads();
     uint32_t items = pre[U] + (p.Sd ? (nb + 7) / 8 : 0);
@@ -363,8 +380,22 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
     const uint32_t slot0 = smem_u32(stage0);
     // this block's pieces: gate/up tiles [a_lo, a_hi) of the items x GT list, then down tiles [b_lo, b_hi) of the items x DT list
     const uint32_t G = gridDim.x, bx_ = blockIdx.x;
-    const uint32_t a_lo = (uint32_t)((uint64_t)bx_ * items * GT / G), a_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * GT / G);
-    const uint32_t b_lo = (uint32_t)((uint64_t)bx_ * items * DT / G), b_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * DT / G);
+    uint32_t a_lo = (uint32_t)((uint64_t)bx_ * items * GT / G), a_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * GT / G);
+    uint32_t b_lo = (uint32_t)((uint64_t)bx_ * items * DT / G), b_hi = (uint32_t)((uint64_t)(bx_ + 1) * items * DT / G);
+    // the few items those shares touch, looked up once (thread k: item k of the gate/up share, thread FFN_RECS + k: of the down share)
+    const uint32_t wa0 = a_lo / GT, wb0 = b_lo / DT;
+    if ((a_hi > a_lo && (a_hi - 1) / GT - wa0 >= FFN_RECS) || (b_hi > b_lo && (b_hi - 1) / DT - wb0 >= FFN_RECS)) {  // a grid far smaller than the device's
+        if (tid == 0) set_status(p.status, ST_BAD_ARG | 6);
+        a_hi = a_lo;
+        b_hi = b_lo;
+    }
+    if (tid < 2 * FFN_RECS) {
+        const uint32_t k = tid % FFN_RECS, w = (tid < FFN_RECS ? wa0 : wb0) + k;
+        const bool need = tid < FFN_RECS ? (a_hi > a_lo && w <= (a_hi - 1) / GT) : (b_hi > b_lo && w <= (b_hi - 1) / DT);
+        if (need) recs[tid] = ffn_item(pre, ms, U, nb, p.ebase, w);
+    }
+    __syncthreads();
+    const FfnItem *rec_a = recs - wa0, *rec_b = recs + FFN_RECS - wb0;  // rec_a[w], rec_b[w]
 
     if (warp == FFN_CW) {
         // ---- producer: one lane walks the block's pieces and keeps the ring full
@@ -398,7 +429,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             };
             auto src_of = [&](const FfnItem &it) {
                 Src c;
-                c.erow = it.shared ? 0 : (pre[2 * FFN_MAXG + it.u] - p.ebase);
+                c.erow = it.erow;
                 c.tg = it.shared ? &mSG : &mG;
                 c.tu = it.shared ? &mSU : &mU;
                 if (FMT == 0) {
@@ -416,7 +447,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 const uint32_t w = a / GT, gt = a - w * GT;
                 if (w != cur) {  // the tokens of the item's columns
                     cur = w;
-                    const FfnItem it = ffn_item(pre, U, nb, w);
+                    const FfnItem it = rec_a[w];
                     uint8_t *dst = act_for(it.ncols * D * 2);
                     for (uint32_t c = 0; c < it.ncols; c++) {
                         uint32_t tok, rank;
@@ -442,7 +473,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 const uint32_t w = bi / DT, dt = bi - w * DT;
                 if (w != cur) {  // H of the item: written by the blocks that ran its gate/up pieces, complete when all GT x 8 warps have counted in
                     cur = w;
-                    const FfnItem it = ffn_item(pre, U, nb, w);
+                    const FfnItem it = rec_b[w];
                     if (!PROBE && ok && ld_acquire_gpu(p.sync + w) < GT * 8) {
                         const uint64_t t0 = global_ns();
                         while (ld_acquire_gpu(p.sync + w) < GT * 8)
@@ -473,6 +504,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
         bool ok = FMT == 0 ? mbar_wait(tab_bar, 0) : true;
         if (!ok && lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 8);
         const uint32_t tabl = smem_u32(smem + C::OFF_TAB) + lane * 4;  // this lane's copy of the interleaved codebook
+        const uint32_t stab = smem_u32(smem + C::OFF_TAB);             // IQ3X: the scale constants
         const ZeroRegs zr = zero_regs();
         uint32_t j = 0, k = 0, rc = 0;
         auto wait_full = [&]() {
@@ -529,7 +561,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             if (w != cur) {
                 if (cur != 0xffffffffu) act_release();
                 cur = w;
-                ncols = ffn_item(pre, U, nb, w).ncols;
+                ncols = rec_a[w].ncols;
                 have = (uint32_t)g < ncols ? 1u : 0u;
                 xb0 = act_wait() + g * xpitch + t * 16;
             }
@@ -540,7 +572,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 if (PROBE) probe_read(st, FMT ? IQ3X_STAGE : 128 * FFN_PITCH, sink);
                 else if (FMT == 1) {
                     const uint32_t rec0 = st + (8 * r + g) * IQ3X_REC;
-                    x_unit<1>(rec0, rec0 + 64 * IQ3X_REC, kh, t, zr, bx, bx, have, acc);
+                    x_unit<1>(rec0, rec0 + 64 * IQ3X_REC, kh, t, stab, zr, bx, bx, have, acc);
                 } else {
                     const uint32_t u0 = st + (8 * r + g) * FFN_PITCH + ((220 * kp) & 15) + kh * 110, u1 = u0 + 64 * FFN_PITCH;
                     ffn_unit<1>(u0, u1, t, tabl, zr, bx, bx, have, acc);
@@ -583,7 +615,7 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
             if (w != cur) {
                 if (cur != 0xffffffffu) act_release();
                 cur = w;
-                const FfnItem it = ffn_item(pre, U, nb, w);
+                const FfnItem it = rec_b[w];
                 have = (uint32_t)g < it.ncols ? 1u : 0u;
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
@@ -603,11 +635,13 @@ __global__ void __launch_bounds__(FFN_THREADS, 1) moe_ffn_k(const __grid_constan
                 release();
                 continue;
             }
-            for (uint32_t ks = kh; ks < KU; ks += 2) {
+            static_assert(KU == 2, "one super-block of K per K half");
+            {
+                const uint32_t ks = kh;
                 const uint32_t bh = hb0 + ks * 512, bl = bh + 8 * hpitch;
                 if (FMT == 1) {  // positions 16 r + g and 16 r + 8 + g hold output rows 16 r + 2 g and 16 r + 2 g + 1
                     const uint32_t rec0 = st + (16 * r + g) * IQ3X_REC;
-                    x_unit<2>(rec0, rec0 + 8 * IQ3X_REC, kh, t, zr, bh, bl, have, acc);
+                    x_unit<2>(rec0, rec0 + 8 * IQ3X_REC, kh, t, stab, zr, bh, bl, have, acc);
                 } else {
                     const uint32_t u0 = st + (16 * r + 2 * g) * rbI + ks * 110, u1 = u0 + rbI;
                     ffn_unit<2>(u0, u1, t, tabl, zr, bh, bl, have, acc);
@@ -695,7 +729,8 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     const size_t act = (size_t)8 * (D * 2 + 64);  // an activation slot: 8 token rows, or 16 H rows
     const size_t smem = x4 ? FfnCfg<1>::OFF_XS + FfnCfg<1>::NACT * act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT
                            : FfnCfg<0>::OFF_XS + FfnCfg<0>::NACT * act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
-    QW_CHECK_ARG(smem <= 227 * 1024 && 128 * rbI <= FfnCfg<0>::SLOT && (128 * rbI) % 16 == 0);
+    const int per_sm = x4 ? FfnCfg<1>::PER_SM : FfnCfg<0>::PER_SM;
+    QW_CHECK_ARG((smem + 1024) * per_sm <= 227 * 1024 + 1024 && 128 * rbI <= FfnCfg<0>::SLOT && (128 * rbI) % 16 == 0);
     const bool shared = L.def("SHARED", 1) != 0;
     const uint32_t EL = (uint32_t)L.def("EL", E);
     p.ebase = L.has_bytes(10, 4) ? L.bytes<uint32_t>(10) : 0;
@@ -752,7 +787,11 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     auto kern = x4 ? (probe ? moe_ffn_k<true, 1> : moe_ffn_k<false, 1>) : (probe ? moe_ffn_k<true, 0> : moe_ffn_k<false, 0>);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    qw_launch(kern, L.sm_count, FFN_THREADS, smem, L.stream, *mG, *mU, *mSG, *mSU, p);
+    int occ = 0;  // the blocks wait for one another's H: all of them must be resident together
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, FFN_THREADS, smem);
+    if (e != cudaSuccess) return e;
+    QW_CHECK_ARG(occ >= per_sm);
+    qw_launch(kern, L.sm_count * per_sm, FFN_THREADS, smem, L.stream, *mG, *mU, *mSG, *mSU, p);
     return cudaGetLastError();
 }
 QW_FAMILY(moe_ffn, launch_moe_ffn, 512)
