@@ -388,6 +388,15 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     }
     if (ok) ok = init_weights(e);
     if (ok && e->ffn_iq3x) ok = pack_experts(e);
+    // The step reads only the re-coded experts from here on.  A model of real size gives the raw IQ3_S blocks back (33 GB at
+    // the benchmark shape: room for KV pages); small models keep them, so that tests can read the tensors they were built from.
+    if (ok && e->ffn_iq3x && (size_t)e->L * e->EL * 3 * gu_bytes > ((size_t)4 << 30)) {
+        qw_buf *raw[] = {&e->exg, &e->exu, &e->exd, &e->shg, &e->shu, &e->shd};
+        for (qw_buf *b : raw) {
+            qw_buf_free(b);
+            *b = qw_buf{};
+        }
+    }
     if (!ok) {
         g_open_error = e->err.empty() ? "engine open failed" : e->err;
         qw_engine_close(e);
