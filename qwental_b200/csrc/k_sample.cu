@@ -18,7 +18,7 @@ namespace {
 constexpr int TOPK_MAX = 256;
 
 __device__ __forceinline__ uint32_t key_of(float v) {
-    const uint32_t u = __float_as_uint(v);
+    const uint32_t u = __float_as_uint(v + 0.0f);  // -0.0 becomes +0.0: the two compare equal in the reference's sort (ties -> lower id)
     return u ^ ((u >> 31) ? 0xffffffffu : 0x80000000u);
 }
 __device__ __forceinline__ float val_of(uint32_t k) { return __uint_as_float(k ^ ((k >> 31) ? 0x80000000u : 0xffffffffu)); }

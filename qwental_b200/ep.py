@@ -16,15 +16,6 @@ def expert_range(E: int, rank: int, size: int) -> tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
-def owner_of(E: int, size: int, expert_ids: np.ndarray) -> np.ndarray:
-    return np.asarray(expert_ids) // (E // size)
-
-
-def scaling_bound(step_bytes_total: float, moe_bytes: float, n: int) -> float:
-    """Upper bound on the speed-up from sharding only the expert weights over n GPUs (HBM bytes per GPU)."""
-    return step_bytes_total / (step_bytes_total - moe_bytes + moe_bytes / n)
-
-
 def row_order(sids, nranks: int, rank: int):
     """Device row order under slot sharding (slot s belongs to rank s mod nranks), through the C ABI (host logic, no device):
     returns (perm, lo, hi) -- perm[j] = caller's index of device row j, [lo, hi) = this rank's rows."""
