@@ -445,35 +445,48 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
             uint32_t cur = 0xffffffffu;
             for (uint32_t a = a_lo; a < a_hi; a++) {
                 const uint32_t w = a / GT, gt = a - w * GT;
-                if (w != cur) {  // the tokens of the item's columns
+                const bool sw = w != cur;
+                FfnItem it{};
+                if (sw) {
                     cur = w;
-                    const FfnItem it = rec_a[w];
-                    uint8_t *dst = act_for(it.ncols * D * 2);
-                    for (uint32_t c = 0; c < it.ncols; c++) {
-                        uint32_t tok, rank;
-                        ffn_entry(ms, it, topk, c, tok, rank);
-                        bulk_g2s(dst + c * xpitch, p.x + (size_t)tok * D, D * 2, &actfull[k % NACT]);
-                    }
-                    k++;
+                    it = rec_a[w];
                     sc = src_of(it);
                 }
                 for (uint32_t kp = 0; kp < KP; kp++, j++) {
                     const uint32_t dst = slot_for(FMT ? IQ3X_STAGE : 2 * 64 * FFN_PITCH);
                     if (FMT == 1) {  // one contiguous stage
                         bulk_s(dst, sc.wg + ((size_t)gt * KP + kp) * IQ3X_STAGE, IQ3X_STAGE, &full[j % FFN_STG]);
-                        continue;
+                    } else {
+                        const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * I + gt * 64);
+                        tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
+                        tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
                     }
-                    const int xc = (int)((220 * kp) & ~15u), yr = (int)(sc.erow * I + gt * 64);
-                    tma_box_2d(dst, sc.tg, xc, yr, &full[j % FFN_STG]);
-                    tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
+                    if (sw && kp == 0) {  // the tokens of a new item's columns, requested after its first weights (the longer wait)
+                        uint8_t *xd = act_for(it.ncols * D * 2);
+                        for (uint32_t c = 0; c < it.ncols; c++) {
+                            uint32_t tok, rank;
+                            ffn_entry(ms, it, topk, c, tok, rank);
+                            bulk_g2s(xd + c * xpitch, p.x + (size_t)tok * D, D * 2, &actfull[k % NACT]);
+                        }
+                        k++;
+                    }
                 }
             }
             cur = 0xffffffffu;
             for (uint32_t bi = b_lo; bi < b_hi; bi++, j++) {
                 const uint32_t w = bi / DT, dt = bi - w * DT;
-                if (w != cur) {  // H of the item: written by the blocks that ran its gate/up pieces, complete when all GT x 8 warps have counted in
+                const bool sw = w != cur;
+                FfnItem it{};
+                if (sw) {
                     cur = w;
-                    const FfnItem it = rec_b[w];
+                    it = rec_b[w];
+                    sc = src_of(it);
+                }
+                const uint32_t bytes = FMT ? IQ3X_STAGE : 128 * rbI;
+                const uint32_t dst = slot_for(bytes);
+                bulk_s(dst, sc.wd + (size_t)dt * bytes, bytes, &full[j % FFN_STG]);
+                if (sw) {  // H of a new item, after its first weights are on their way: written by the blocks that ran its gate/up
+                           // pieces, complete when all GT x 8 warps have counted in
                     if (!PROBE && ok && ld_acquire_gpu(p.sync + w) < GT * 8) {
                         const uint64_t t0 = global_ns();
                         while (ld_acquire_gpu(p.sync + w) < GT * 8)
@@ -484,18 +497,14 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                             }
                     }
                     asm volatile("fence.proxy.async.global;" ::: "memory");  // the H rows were written by ordinary stores; the copy engine reads them
-                    uint8_t *dst = act_for(2 * it.ncols * I * 2);
+                    uint8_t *hd = act_for(2 * it.ncols * I * 2);
                     const __half *Hw = p.H + (size_t)w * 16 * I;
                     for (uint32_t c = 0; c < it.ncols; c++) {
-                        bulk_g2s(dst + c * hpitch, Hw + (size_t)c * I, I * 2, &actfull[k % NACT]);
-                        bulk_g2s(dst + (8 + c) * hpitch, Hw + (size_t)(8 + c) * I, I * 2, &actfull[k % NACT]);
+                        bulk_g2s(hd + c * hpitch, Hw + (size_t)c * I, I * 2, &actfull[k % NACT]);
+                        bulk_g2s(hd + (8 + c) * hpitch, Hw + (size_t)(8 + c) * I, I * 2, &actfull[k % NACT]);
                     }
                     k++;
-                    sc = src_of(it);
                 }
-                const uint32_t bytes = FMT ? IQ3X_STAGE : 128 * rbI;
-                const uint32_t dst = slot_for(bytes);
-                bulk_s(dst, sc.wd + (size_t)dt * bytes, bytes, &full[j % FFN_STG]);
             }
         }
     } else {

@@ -35,7 +35,8 @@ def test_reference_device_api_is_complete():
 def test_kernel_families_registered():
     L = lib.load()
     fams = {L.qw_gpu_family_name(i).decode() for i in range(L.qw_gpu_family_count())}
-    assert {"dq_test", "qmv_gg", "qmv_mma"} <= fams
+    assert {"dq_test", "qmv_gg", "qmv_mma", "moe_route", "moe_gu", "moe_dn", "moe_ffn", "iq3x_pack", "iq3x_dq_test", "add_rmsnorm", "qsa_prep",
+            "qsa_attn", "qsa_merge", "dn_epi", "gdn_fstep", "k_topk", "stream_probe", "umma_test", "umma_bench"} <= fams
 
 
 def test_open_fails_without_device_and_nothing_falls_back():
