@@ -479,23 +479,23 @@ QW_FAMILY(qsa_attn, launch_qsa_attn_mma, 128)
 
 // ------------------------------------------------------------------------------------------------ merge + output gate
 // binds: 0 = part, 1 = qkv fp16 (gate = qkv[t][qh*2*HD + HD + d]), 2 = y fp16 [nb][QH*HD], 3 = pos, 4 = qsa_args.
-// grid (QH, nb) x 1024.  The chunk weights exp(m_c - M) are computed once per chunk (thread c); then 8 groups of 128
-// threads (two dims per thread, 8-byte loads: a partial's 258 floats keep rows 8-byte aligned, not 16) each sum their chunks
-// in chunk order and the 8 partial sums are added in group order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.
+// grid (QH, nb) x 512.  The chunk weights exp(m_c - M) are computed once per chunk (thread c); then the 16 warps take the
+// chunks c = warp, warp + 16, ... (each in increasing order; a lane owns eight dims: four 8-byte loads per chunk -- a partial's 258
+// floats keep rows 8-byte aligned, not 16 -- four chunks in flight per warp) and the 16 partial sums are added in warp order: o = sum_c w_c acc_c[d] / sum_c w_c l_c.  The order depends only on the slot's own chunk count.
 #define QSA_MAXCH 1024
-__global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
+__global__ void __launch_bounds__(512) qsa_merge_k(const float *part, const __half *qkv, __half *y, const int32_t *posv, qsa_args a, uint32_t QH) {
     constexpr uint32_t HD = 256;
-    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[32], ls[8];
-    __shared__ float2 accs[8][HD / 2];
+    __shared__ float wc[QSA_MAXCH], lc[QSA_MAXCH], tmp[16], ls[16];
+    __shared__ float accs[16][HD];
     pdl_sync();
-    const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, d = tid & 255, d2 = tid & 127, grp = tid >> 7, lane = tid & 31, warp = tid >> 5;
+    const uint32_t qh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // the core wrote max_chunks partials per slot at most: a position beyond that (only a caller that passes its own device
     // positions can produce one) must not make the merge read another slot's partials or run off the buffer
     const uint32_t ntok = (uint32_t)posv[t] + 1, nch = min((ntok + QSA_PAGE - 1) / QSA_PAGE, min(a.max_chunks, (uint32_t)QSA_MAXCH));
     const float *base = part + ((size_t)t * a.max_chunks * QH + qh) * (HD + 2);
     const size_t cstride = (size_t)QH * (HD + 2);
     float mx = -INFINITY;
-    for (uint32_t c = tid; c < nch; c += 1024) {
+    for (uint32_t c = tid; c < nch; c += 512) {
         const float pm = base[c * cstride + HD], pl = base[c * cstride + HD + 1];
         wc[c] = pm;
         lc[c] = pl;
@@ -506,30 +506,32 @@ __global__ void __launch_bounds__(1024) qsa_merge_k(const float *part, const __h
     __syncthreads();
     float M = tmp[0];
 #pragma unroll
-    for (int i = 1; i < 32; i++) M = fmaxf(M, tmp[i]);
-    for (uint32_t c = tid; c < nch; c += 1024) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
+    for (int i = 1; i < 16; i++) M = fmaxf(M, tmp[i]);
+    for (uint32_t c = tid; c < nch; c += 512) wc[c] = lc[c] > 0.f ? expf(wc[c] - M) : 0.f;
     __syncthreads();
-    // eight thread groups take the chunks c = grp, grp + 8, ... (each in increasing order); the partial sums are then added
-    // in group order, so the result depends only on the slot's own chunk count
     float l = 0.f;
-    float2 acc = make_float2(0.f, 0.f);
+    float2 acc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll 4
-    for (uint32_t c = grp; c < nch; c += 8) {
+    for (uint32_t c = warp; c < nch; c += 16) {
         const float w = wc[c];
-        const float2 v = *(const float2 *)(base + c * cstride + 2 * d2);
+        const float2 *pv = (const float2 *)(base + c * cstride) + 4 * lane;
+        const float2 v0 = pv[0], v1 = pv[1], v2 = pv[2], v3 = pv[3];
         l = fmaf(lc[c], w, l);
-        acc.x = fmaf(v.x, w, acc.x);
-        acc.y = fmaf(v.y, w, acc.y);
+        acc[0].x = fmaf(v0.x, w, acc[0].x); acc[0].y = fmaf(v0.y, w, acc[0].y);
+        acc[1].x = fmaf(v1.x, w, acc[1].x); acc[1].y = fmaf(v1.y, w, acc[1].y);
+        acc[2].x = fmaf(v2.x, w, acc[2].x); acc[2].y = fmaf(v2.y, w, acc[2].y);
+        acc[3].x = fmaf(v3.x, w, acc[3].x); acc[3].y = fmaf(v3.y, w, acc[3].y);
     }
-    accs[grp][d2] = acc;
-    if (d2 == 0) ls[grp] = l;
+#pragma unroll
+    for (int i = 0; i < 4; i++) *(float2 *)&accs[warp][8 * lane + 2 * i] = acc[i];
+    if (lane == 0) ls[warp] = l;
     __syncthreads();
     if (tid < HD) {
-        const float *col = (const float *)&accs[0][0] + d;
-        float at = col[0], lt = ls[0];
+        const uint32_t d = tid;
+        float at = accs[0][d], lt = ls[0];
 #pragma unroll
-        for (int g2 = 1; g2 < 8; g2++) {
-            at += col[g2 * HD];
+        for (int g2 = 1; g2 < 16; g2++) {
+            at += accs[g2][d];
             lt += ls[g2];
         }
         const float g = __half2float(qkv[(size_t)t * a.qkv_stride + qh * 2 * HD + HD + d]);
@@ -546,7 +548,7 @@ static cudaError_t launch_qsa_merge(const QwLaunch &L) {
     for (int i = 0; i <= 3; i++) QW_CHECK_ARG(L.buf<void>(i) != nullptr);
     QW_CHECK_ARG(L.avail(0) >= (size_t)a.nb * a.max_chunks * QH * (HD + 2) * 4 && L.avail(2) >= (size_t)a.nb * QH * HD * 2 &&
                  L.avail(1) >= ((size_t)(a.nb - 1) * a.qkv_stride + QH * 2 * HD) * 2);
-    qw_launch(qsa_merge_k, dim3(QH, a.nb), 1024, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<int32_t>(3), a, QH);
+    qw_launch(qsa_merge_k, dim3(QH, a.nb), 512, 0, L.stream, L.buf<float>(0), L.buf<__half>(1), L.buf<__half>(2), L.buf<int32_t>(3), a, QH);
     return cudaGetLastError();
 }
 QW_FAMILY(qsa_merge, launch_qsa_merge, 256)
@@ -608,7 +610,7 @@ extern "C" int qw_attn_decode_static(const void *q, const void *kv_pool, size_t 
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) return fail(-3, "cannot read the SM count");
     const uint32_t most = (nb * max_chunks * KVH + 3) / 4, cap = (uint32_t)sms * AT_BLOCKS_PER_SM;
     qsa_attn_mma_k<<<most < cap ? most : cap, 128, smem, st>>>(tm, (const __half *)q, page_table, pos, slot_ids, part, a, QH, KVH, nullptr);
-    qsa_merge_k<<<dim3(QH, nb), 1024, 0, st>>>(part, (const __half *)qkv, (__half *)y, pos, a, QH);
+    qsa_merge_k<<<dim3(QH, nb), 512, 0, st>>>(part, (const __half *)qkv, (__half *)y, pos, a, QH);
     e = cudaGetLastError();
     if (e != cudaSuccess) return fail(-3, cudaGetErrorString(e));
     if (err && errlen) err[0] = 0;
