@@ -837,6 +837,12 @@ void end_step(qw_engine *e, const int *sids, int B, int nsteps, double wall_ms) 
     e->cost[B] = e->cost[B] == 0 ? per : 0.8 * e->cost[B] + 0.2 * per;
 }
 
+// A step whose batch failed (a wait that ran out, a launch error) may have left the expert-FFN kernel's per-item counters
+// non-zero; the next step must not find them: they would let down pieces start before their H is complete.
+void after_failed_step(qw_engine *e) {
+    if (e->ffn_scr.size) qw_buf_zero(e->g, &e->ffn_scr, 0, MOE_FFN_SYNC_BYTES);
+}
+
 }  // namespace
 
 extern "C" const float *qw_engine_par_step(qw_engine *e, const int *sids, const int32_t *toks, int B, double *gpu_ms) {
@@ -846,7 +852,7 @@ extern "C" const float *qw_engine_par_step(qw_engine *e, const int *sids, const 
     qw_batch *b = qw_batch_begin(e->g, false);
     encode_step(e, b, (uint32_t)B, mc, true, 0);
     const double secs = qw_batch_end(b);
-    if (secs < 0) return e->fail("par_step: device batch failed"), nullptr;
+    if (secs < 0) return after_failed_step(e), e->fail("par_step: device batch failed"), nullptr;
     for (int j = 0; j < B; j++)  // device row j is the caller's row perm[j]
         if (!qw_buf_download(e->g, &e->logits, (size_t)j * e->V * 4, (float *)e->logits_h.ptr + (size_t)e->perm[j] * e->V, (size_t)e->V * 4))
             return e->fail("par_step: logits copy failed"), nullptr;
@@ -862,7 +868,7 @@ extern "C" const int32_t *qw_engine_par_step_greedy(qw_engine *e, const int *sid
     qw_batch *b = qw_batch_begin(e->g, false);
     encode_step(e, b, (uint32_t)B, mc, true, 1);
     const double secs = qw_batch_end(b);
-    if (secs < 0) return e->fail("par_step_greedy: device batch failed"), nullptr;
+    if (secs < 0) return after_failed_step(e), e->fail("par_step_greedy: device batch failed"), nullptr;
     if (gpu_ms) *gpu_ms = secs * 1e3;
     end_step(e, sids, B, 1, (qw_now() - t0) * 1e3);
     e->ids_out.resize(QW_PAR_MAX);
@@ -882,7 +888,7 @@ extern "C" int qw_engine_par_decode_greedy(qw_engine *e, const int *sids, const 
         qw_batch *b = qw_batch_begin(e->g, false);
         encode_step(e, b, (uint32_t)B, mc, s == 0, 2);
         const double secs = qw_batch_end(b);
-        if (secs < 0) return e->fail("par_decode_greedy: device batch failed at step %d", s), -1;
+        if (secs < 0) return after_failed_step(e), e->fail("par_decode_greedy: device batch failed at step %d", s), -1;
         total += secs;
         for (int j = 0; j < B; j++) out_ids[(size_t)s * B + e->perm[j]] = ((const int32_t *)e->ids_h.ptr)[j];
     }
@@ -979,7 +985,7 @@ extern "C" int qw_engine_par_step_sample(qw_engine *e, const int *sids, const in
     qw_batch *b = qw_batch_begin(e->g, false);
     encode_step(e, b, (uint32_t)B, mc, true, 3);
     const double secs = qw_batch_end(b);
-    if (secs < 0) return e->fail("par_step_sample: device batch failed"), -1;
+    if (secs < 0) return after_failed_step(e), e->fail("par_step_sample: device batch failed"), -1;
     if (gpu_ms) *gpu_ms = secs * 1e3;
     const int32_t *cid = (const int32_t *)e->cand_h.ptr;
     const float *cval = (const float *)((const char *)e->cand_h.ptr + (size_t)QW_PAR_MAX * 256 * 4);
@@ -1022,7 +1028,7 @@ extern "C" const float *qw_engine_par_prefill(qw_engine *e, int sid, const int32
             if (!mc) return nullptr;
             qw_batch *b = qw_batch_begin(e->g, false);
             encode_step(e, b, 1, mc, true, 0);
-            if (qw_batch_end(b) < 0) return e->fail("par_prefill: device batch failed at position %d", i), nullptr;
+            if (qw_batch_end(b) < 0) return after_failed_step(e), e->fail("par_prefill: device batch failed at position %d", i), nullptr;
             end_step(e, &sid, 1, 1, (qw_now() - t0) * 1e3);
         } else lg = qw_engine_par_step(e, &sid, &prompt[i], 1, nullptr);
     }
