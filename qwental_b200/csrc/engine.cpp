@@ -99,6 +99,7 @@ struct qw_engine {
     qw_buf epx{};            // [2][Pg] (double-buffered by layer parity) + flag array, exported to the other ranks
     qw_buf ep_peer[8]{};     // the other ranks' epx (ep_peer[own rank] aliases epx)
     qw_kernel *k_dn_x = nullptr, *k_norm_cmb_x = nullptr, *k_topk = nullptr;
+    qw_kernel *k_norm_cmb_rc = nullptr;  // combine + norm that waits on moe_ffn's per-row counters instead of on its whole launch (one GPU)
     // gate/up + down of the expert FFN in one launch (moe_ffn), where the shapes allow it; QW_MOE_FFN=split keeps the two launches
     bool ffn_fused = false;
     // ... on expert weights re-coded once into the kernel's own stage order and bit layout (IQ3X, csrc/iq3x.cuh): lossless, 136
@@ -343,6 +344,9 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
             mp.push_back({"PROBE", 1});
             ok = compile(e, "moe_ffn", "moe_ffn", mf, &e->k_ffn) && compile(e, "moe_ffn", "moe_ffn_copy_probe", mp, &e->k_ffn_probe) &&
                  (!e->ffn_iq3x || compile(e, "iq3x_pack", "iq3x_pack", {}, &e->k_pack));
+            const char *cw = getenv("QW_CMB_WAIT");  // QW_CMB_WAIT=launch: the combine + norm waits for the FFN's whole launch, as with any other kernel
+            if (ok && c.ep_size == 1 && e->D == 2048 && !(cw && !strcmp(cw, "launch")))
+                ok = compile(e, "add_rmsnorm", "cmb_add_rmsnorm_rows", {{"CMB", 1}, {"TOPK", e->TOPK}, {"ROWCNT", 1}}, &e->k_norm_cmb_rc);
         }
     }
     ok = ok && compile(e, "k_topk", "k_topk", {}, &e->k_topk);
@@ -531,7 +535,8 @@ void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_float
     const uint32_t a[2] = {nb, (uint32_t)e->D};
     const bool cmb = delta == &e->Pg;
     const bool gathered = delta == &e->epx;  // slot sharding: the rows were stored by the ranks that own the slots
-    qw_batch_kernel(b, cmb ? (e->ep_fused ? e->k_norm_cmb_x : e->k_norm_cmb) : gathered ? e->k_norm_x : delta ? e->k_norm : e->k_norm0);
+    const bool rows = cmb && e->k_norm_cmb_rc && e->ffn_fused && !e->ep_fused && !e->moe_probe;  // the FFN counts its output rows in
+    qw_batch_kernel(b, cmb ? (e->ep_fused ? e->k_norm_cmb_x : rows ? e->k_norm_cmb_rc : e->k_norm_cmb) : gathered ? e->k_norm_x : delta ? e->k_norm : e->k_norm0);
     qw_batch_buf(b, 0, &e->h, 0);
     if (cmb) {
         qw_batch_buf(b, 5, &e->msel, (size_t)cmb_layer * e->sel_bytes);
@@ -540,6 +545,7 @@ void enc_norm(qw_engine *e, qw_batch *b, const qw_buf *delta, size_t w_off_float
             qw_batch_buf(b, 7, &e->epx, 2 * e->pg_bytes);
             qw_batch_buf(b, 8, &e->rcnt, 64);
         } else qw_batch_buf(b, 6, &e->Pg, 0);
+        if (rows) qw_batch_buf(b, 9, &e->ffn_scr, 0);
     } else if (delta) {
         qw_batch_buf(b, 1, delta, delta_off);
         if (gathered) {

@@ -669,6 +669,14 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                 } else {
                     if (oo[0] != 0xffffffffu) *(float2 *)(p.Pg + oo[0] + row) = make_float2(acc[0], acc[2]);
                     if (oo[1] != 0xffffffffu) *(float2 *)(p.Pg + oo[1] + row) = make_float2(acc[1], acc[3]);
+                    // this warp's 16 rows of the tile are stored for every column: count it in on the columns' output rows (lanes
+                    // t = 0 .. 3 of row g = 0 know two columns each), so that the combine + norm of a token can start when its rows are complete
+                    __syncwarp();
+                    if (g == 0) {
+                        __threadfence();  // the warp's stores (cumulative over the warp barrier) before the counts
+                        if (oo[0] != 0xffffffffu) atomicAdd(p.sync + MOE_FFN_ROWCNT + oo[0] / D, 1u);
+                        if (oo[1] != 0xffffffffu) atomicAdd(p.sync + MOE_FFN_ROWCNT + oo[1] / D, 1u);
+                    }
                 }
             }
         }

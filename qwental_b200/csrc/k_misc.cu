@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
 // added in block order by every block, so the result does not depend on timing).  grid (8 nb) x 256, cluster 8.
 __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_k(float *h, const float *w, __half *x, const moe_sel *ms, const float *Pg,
                                                                                     uint32_t topk, const unsigned *flags, const unsigned *seq,
-                                                                                    uint32_t nranks, unsigned *status) {
+                                                                                    uint32_t nranks, unsigned *rowcnt, unsigned *status) {
     constexpr uint32_t D = 2048;
     namespace cg = cooperative_groups;
     __shared__ float tmp[8];
@@ -120,13 +120,31 @@ __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_
     const uint32_t t = blockIdx.x >> 3, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, d = (blockIdx.x & 7) * 256 + tid;
     pdl_launch();
     const float wd = w[d];  // the norm weights are static
-    pdl_wait();
+    if (rowcnt) {
+        // One GPU, the one-launch expert FFN before us: do not wait for its whole launch, only for this token's topk + 1 output rows
+        // (each counted in by the warps that stored it; see moe_sel.h).  Everything read below was complete before the FFN stored
+        // those rows, and the FFN no longer reads this token's x once they are.  Bounded like every wait of this library.
+        if (tid <= topk) {
+            const unsigned *c = rowcnt + t * (topk + 1) + tid;
+            const uint64_t t0 = global_ns();
+            while (ld_acquire_gpu(c) < MOE_FFN_ROW_DONE(D)) {
+                __nanosleep(100);
+                if (global_ns() - t0 > 2000000000ull) {
+                    set_status(status, ST_PEER_TIMEOUT | 32);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    } else {
+        pdl_wait();
+    }
     if (nranks > 1) ep_wait(flags, seq, nranks, status);
     float wk[MOE_MAXK], pv[MOE_MAXK];
 #pragma unroll
     for (uint32_t s = 0; s < MOE_MAXK; s++) wk[s] = s <= topk ? ms->w[t][s] : 0.f;
 #pragma unroll
-    for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? Pg[((size_t)t * (topk + 1) + s) * D + d] : 0.f;
+    for (uint32_t s = 0; s < MOE_MAXK; s++) pv[s] = s <= topk ? __ldcg(Pg + ((size_t)t * (topk + 1) + s) * D + d) : 0.f;
     float v = h[(size_t)t * D + d];
     float o = 0.f;
 #pragma unroll
@@ -149,6 +167,10 @@ __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_
     for (unsigned r = 0; r < 8; r++) tot += *cl.map_shared_rank(&part, r);
     x[(size_t)t * D + d] = __float2half_rn(v * rsqrtf(tot / D + 1e-6f) * wd);
     cl.sync();  // nobody leaves while its partial sum may still be read
+    if (rowcnt) {
+        pdl_wait();  // this kernel's completion must imply the FFN's: later kernels rely on the chain of completed predecessors
+        if ((blockIdx.x & 7) == 0 && tid <= topk) rowcnt[t * (topk + 1) + tid] = 0;  // cleared for the next layer's launch
+    }
 }
 static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
     struct { uint32_t nb, D; } a = L.bytes<decltype(a)>(4);
@@ -162,8 +184,14 @@ static cudaError_t launch_add_rmsnorm(const QwLaunch &L) {
         const uint32_t nranks = (uint32_t)L.def("EPX", 1);
         if (nranks > 1) QW_CHECK_ARG(nranks <= 8 && L.buf<void>(7) && L.avail(7) >= nranks * 4 && L.buf<void>(8) && L.avail(8) >= 4);
         if (a.D == 2048) {
+            // ROWCNT defined 1 (one GPU, after moe_ffn): 9 = the FFN's scratch buffer, whose per-row counters replace the wait for the launch
+            unsigned *rowcnt = nullptr;
+            if (L.def("ROWCNT", 0)) {
+                QW_CHECK_ARG(nranks == 1 && L.buf<unsigned>(9) && L.avail(9) >= MOE_FFN_SYNC_BYTES && (a.nb * (topk + 1)) <= MOE_MAXB * MOE_MAXK);
+                rowcnt = L.buf<unsigned>(9) + MOE_FFN_ROWCNT;
+            }
             qw_launch(cmb_rmsnorm_cl_k, a.nb * 8, 256, 0, L.stream, L.buf<float>(0), L.buf<float>(2), L.buf<__half>(3), L.buf<moe_sel>(5), L.buf<float>(6), topk,
-                      nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, (unsigned *)L.status);
+                      nranks > 1 ? L.buf<unsigned>(7) : nullptr, nranks > 1 ? L.buf<unsigned>(8) : nullptr, nranks, rowcnt, (unsigned *)L.status);
             return cudaGetLastError();
         }
         qw_launch(add_rmsnorm_k<2>, a.nb, 1024, 0, L.stream, L.buf<float>(0), nullptr, L.buf<float>(2), L.buf<__half>(3), a.D, L.buf<moe_sel>(5), L.buf<float>(6), topk,

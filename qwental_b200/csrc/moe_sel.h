@@ -25,5 +25,10 @@ struct moe_sel {
 // An item is one pass of up to 8 tokens of one chosen expert or of the shared expert: at most 512 experts + the extra passes
 // of 64 tokens x 10 choices + the shared expert's 8.
 #define MOE_FFN_MAXITEMS 640
-#define MOE_FFN_SYNC_BYTES 4096
+#define MOE_FFN_SYNC_BYTES 8192
+// word MOE_FFN_ROWCNT + tok * (topk + 1) + rank of the same area counts the reader warps that have stored their part of output row
+// (tok, rank) of Pg: 8 per tile of 128 output rows, MOE_FFN_ROW_DONE(D) when the row is complete.  The combine + norm kernel that
+// follows waits on the rows of its token instead of on the whole launch, and clears them (one GPU only).
+#define MOE_FFN_ROWCNT 1024
+#define MOE_FFN_ROW_DONE(D) ((D) / 128 * 8)
 #define MOE_FFN_SCRATCH_BYTES(I) ((size_t)MOE_FFN_SYNC_BYTES + (size_t)MOE_FFN_MAXITEMS * 16 * (I) * 2)

@@ -89,8 +89,8 @@ class MoeLayer:
         self.Hhi = gpu.buf(MOE_MAXB * (topk + 1) * I * 2).zero()
         self.Hlo = gpu.buf(MOE_MAXB * (topk + 1) * I * 2).zero()
         self.Pg = gpu.buf(MOE_MAXB * (topk + 1) * D * 4).zero()
-        # moe_ffn's scratch (csrc/moe_sel.h): 4 KB of counters that are zero between launches, then H of up to 640 items
-        self.ffn_scr = gpu.buf(4096 + 640 * 16 * I * 2).zero() if self.fused_ffn else None
+        # moe_ffn's scratch (csrc/moe_sel.h): 8 KB of counters, then H of up to 640 items
+        self.ffn_scr = gpu.buf(8192 + 640 * 16 * I * 2).zero() if self.fused_ffn else None
 
     def encode(self, b: Batch, x: Buf, out: Buf, nb: int, resid: Buf | None = None, fused_route: bool = False):
         E, D, I = self.E, self.D, self.I
