@@ -290,12 +290,13 @@ static cudaError_t qmv_mma_nt(const QmvMmaP &p, int sm, cudaStream_t st) {
 // ---- Variant used for the dense projections: a team of WARPS warps per 16-row tile, one warp per 256-K unit (8 warps
 // at K = 2048, 16 at K = 4096); TEAMS teams share one block (and, for IQ3_S, one conflict-free 16-copy codebook of 64 KB
 // that arrives by a bulk copy while the activations are loaded).  The activations' B fragments of up to 16 tokens stay
-// in registers for the whole kernel; more than 16 tokens run as passes of 16 over the staged tile.
+// in registers for the whole kernel.  More than 16 tokens run as passes of 16 over the staged tile: the MP form decodes half
+// a unit into A fragments once and runs all passes over them, fetching the B fragments per pass.
 template <int N>
 __device__ __forceinline__ void team_bar(int id) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(N) : "memory");
 }
-template <int GF, int WARPS, int TEAMS, bool F32OUT>
+template <int GF, int WARPS, int TEAMS, bool F32OUT, bool MP>
 __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 : 1) qmv_mma2_k(const QmvMmaP p) {
     constexpr int NT = 2, TS = 128, STG = GF == 8 ? 2 : QMV_STAGES, UB = GF == 21 ? 110 : 272, TABB = GF == 21 ? 65536 : 0;
     constexpr int TT = WARPS * 32;  // threads of a team
@@ -344,7 +345,7 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
         }
     };
     pdl_wait();  // weight tiles and the codebook are static; the activations (and the output buffer) are not
-    load_x(0);
+    if (!MP) load_x(0);
     bool ok = GF == 21 ? mbar_wait(&bars[TEAMS * STG], 0) : true;
     const uint32_t passes = (p.nb + 15) / 16;
     uint32_t rb_i = 0;  // alternating reduce buffer
@@ -358,6 +359,68 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
             break;
         }
         const uint32_t rows = smem_u32(stage0) + s * stage_stride + g * p.rs + warp * UB;
+        if constexpr (MP) {
+            // more than 16 tokens: decode half a unit once, run every pass of 16 tokens over it (bit-identical to the loop below)
+            float accp[4][NT][4];
+#pragma unroll
+            for (int ps = 0; ps < 4; ps++)
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) accp[ps][nt][0] = accp[ps][nt][1] = accp[ps][nt][2] = accp[ps][nt][3] = 0.f;
+            auto run_half = [&](const UnitHalf &A, int hf) {
+#pragma unroll
+                for (int ps = 0; ps < 4; ps++) {
+                    if ((uint32_t)ps >= passes) break;  // warp-uniform
+                    const uint32_t ca = ps * 16 + g, cb = ca + 8;
+                    const uint4 *xa = (const uint4 *)(p.x + (size_t)ca * p.xstride) + warp * 32 + t + 16 * hf;
+                    const uint4 *xb = (const uint4 *)(p.x + (size_t)cb * p.xstride) + warp * 32 + t + 16 * hf;
+                    uint4 va[4], vb[4];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        va[i] = ca < p.nb ? __ldcg(xa + 4 * i) : zero;
+                        vb[i] = cb < p.nb ? __ldcg(xb + 4 * i) : zero;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) half_mma(A, i, zr, va[i], vb[i], (uint32_t)ps * 16 + 8 < p.nb, accp[ps]);
+                }
+            };
+            if constexpr (GF == 21) {
+                const Iq3sHdr h0 = iq3s_hdr(rows, t), h1 = iq3s_hdr(rows + 8 * p.rs, t);
+                UnitHalf A;
+                iq3s_decode_half<0, TS>(rows, rows + 8 * p.rs, t, h0, h1, tabc, A);
+                run_half(A, 0);
+                iq3s_decode_half<1, TS>(rows, rows + 8 * p.rs, t, h0, h1, tabc, A);
+                run_half(A, 1);
+            } else {
+                UnitHalf A;
+                q8_decode_half<0>(rows, rows + 8 * p.rs, t, A);
+                run_half(A, 0);
+                q8_decode_half<1>(rows, rows + 8 * p.rs, t, A);
+                run_half(A, 1);
+            }
+#pragma unroll
+            for (int ps = 0; ps < 4; ps++) {
+                if ((uint32_t)ps >= passes) break;
+                float4 *rd = red + rb_i * WARPS * NT * 32;
+                rb_i ^= 1;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) rd[(warp * NT + nt) * 32 + lane] = make_float4(accp[ps][nt][0], accp[ps][nt][1], accp[ps][nt][2], accp[ps][nt][3]);
+                team_bar<TT>(team + 1);
+                for (int e = tt; e < NT * 32 * 4; e += TT) {
+                    const int jj = e & 3, ln = (e >> 2) & 31, nt = e >> 7;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int k2 = 0; k2 < WARPS; k2++) sum += ((const float *)&rd[(k2 * NT + nt) * 32 + ln])[jj];
+                    const uint32_t row = item * 16 + (ln >> 2) + 8 * (jj >> 1), col = ps * 16 + nt * 8 + 2 * (ln & 3) + (jj & 1);
+                    if (col < p.nb && row < p.N) {
+                        if (F32OUT) ((float *)p.y)[(size_t)col * p.ystride + row] = sum;
+                        else if (p.ep.nranks > 1) {
+                            const __half hv = __float2half_rn(sum);
+                            for (uint32_t r = 0; r < p.ep.nranks; r++) ((__half *)p.yR[r])[(size_t)col * p.ystride + row] = hv;
+                        } else ((__half *)p.y)[(size_t)col * p.ystride + row] = __float2half_rn(sum);
+                    }
+                }
+            }
+        } else
         for (uint32_t ps = 0; ps < passes; ps++) {
             if (passes > 1) load_x(ps * 16);
             float acc[NT][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -388,12 +451,15 @@ __global__ void __launch_bounds__(WARPS * TEAMS * 32, (WARPS * TEAMS == 8) ? 2 :
     if (!F32OUT && p.ep.nranks > 1) ep_publish(p.ep);
 }
 
-template <int GF, int WARPS, int TEAMS, bool F32OUT>
+template <int GF, int WARPS, int TEAMS, bool F32OUT, bool MP = false>
 static cudaError_t qmv_mma2_go(const QmvMmaP &p, int sm_count, cudaStream_t st) {
+    // more than 16 tokens (at most 64): the form that decodes a unit once for all passes
+    static const bool loop_passes = [] { const char *v = getenv("QW_QMV_PASSES"); return v && !strcmp(v, "loop"); }();  // for A/B timing
+    if (!MP && p.nb > 16 && p.nb <= 64 && !loop_passes) return qmv_mma2_go<GF, WARPS, TEAMS, F32OUT, true>(p, sm_count, st);
     const size_t smem = 128 + (GF == 21 ? 65536 : 0) + (size_t)TEAMS * 2 * WARPS * 2 * 32 * 16 +
                         (size_t)TEAMS * (GF == 8 ? 2 : QMV_STAGES) * ((16 * p.rs + 127) & ~127u);
     if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    auto k = qmv_mma2_k<GF, WARPS, TEAMS, F32OUT>;
+    auto k = qmv_mma2_k<GF, WARPS, TEAMS, F32OUT, MP>;
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     int occ = 1;

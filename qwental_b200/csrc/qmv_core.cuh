@@ -309,6 +309,47 @@ __device__ __forceinline__ void unit_mma2(uint32_t u0, uint32_t u1, uint32_t tab
     sub_mma2<7, TS>(u0, u1, t, h0, h1, tabc, zr, xa[7], xb[7], second, acc);
 }
 
+// More than 16 tokens: the decoded A fragments of half a unit (four sub-blocks) stay in registers while the passes of 16 tokens
+// run over them, so the unit is decoded once, not once per pass.  A column sees the same MMAs and the same scale products in the
+// same sub-block order as in unit_mma2: results are bit-identical to the one-pass form.
+struct UnitHalf {
+    uint32_t a0[4][4], a1[4][4];  // A fragments of the two MMAs of sub-block i
+    float da[4], db[4];           // sub-block scales of rows g and g + 8
+};
+template <int HF, int TS>
+__device__ __forceinline__ void iq3s_decode_half(uint32_t u0, uint32_t u1, int t, const Iq3sHdr &h0, const Iq3sHdr &h1, uint32_t tabc, UnitHalf &A) {
+    uint32_t wa[4], wb[4];
+#define QW_HALF_SUB(I)                                                            \
+    A.da[I] = iq3s_sub_h<4 * HF + I, TS>(u0 + 2 * t, u0 + t, h0, tabc, wa);       \
+    A.db[I] = iq3s_sub_h<4 * HF + I, TS>(u1 + 2 * t, u1 + t, h1, tabc, wb);       \
+    A.a0[I][0] = wa[0]; A.a0[I][1] = wb[0]; A.a0[I][2] = wa[1]; A.a0[I][3] = wb[1]; \
+    A.a1[I][0] = wa[2]; A.a1[I][1] = wb[2]; A.a1[I][2] = wa[3]; A.a1[I][3] = wb[3];
+    QW_HALF_SUB(0)
+    QW_HALF_SUB(1)
+    QW_HALF_SUB(2)
+    QW_HALF_SUB(3)
+#undef QW_HALF_SUB
+}
+// sub-block i of the half against the B fragments of two column tiles
+__device__ __forceinline__ void half_mma(const UnitHalf &A, int i, const ZeroRegs &zr, const uint4 &xa, const uint4 &xb, bool second, float (&acc)[2][4]) {
+    float p[4];
+    mma_f16(p, A.a0[i], xa.x, xa.y, zr.z);
+    mma_f16(p, A.a1[i], xa.z, xa.w, p);
+    acc[0][0] = fmaf(A.da[i], p[0], acc[0][0]);
+    acc[0][1] = fmaf(A.da[i], p[1], acc[0][1]);
+    acc[0][2] = fmaf(A.db[i], p[2], acc[0][2]);
+    acc[0][3] = fmaf(A.db[i], p[3], acc[0][3]);
+    if (second) {  // warp-uniform
+        float r[4];
+        mma_f16(r, A.a0[i], xb.x, xb.y, zr.z);
+        mma_f16(r, A.a1[i], xb.z, xb.w, r);
+        acc[1][0] = fmaf(A.da[i], r[0], acc[1][0]);
+        acc[1][1] = fmaf(A.da[i], r[1], acc[1][1]);
+        acc[1][2] = fmaf(A.db[i], r[2], acc[1][2]);
+        acc[1][3] = fmaf(A.db[i], r[3], acc[1][3]);
+    }
+}
+
 // Q8_0 through the same shared-space path: unit = eight 34-byte blocks of a row (src/ggml_dq.c:34-37).  The thread's
 // eight int8 values of block IB sit at byte 34*IB + 2 + 8t: 4-byte aligned for odd IB (two 32-bit loads), 2-byte aligned
 // for even IB (four 16-bit loads).  (q ^ 0x80) | 0x6400 is the half 1024 + (q + 128); subtracting 1152 is exact.
@@ -370,6 +411,22 @@ __device__ __forceinline__ void unit_mma2_q8(uint32_t u0, uint32_t u1, int t, co
     sub_mma2_q8<5>(u0, u1, t, zr, xa[5], xb[5], second, acc);
     sub_mma2_q8<6>(u0, u1, t, zr, xa[6], xb[6], second, acc);
     sub_mma2_q8<7>(u0, u1, t, zr, xa[7], xb[7], second, acc);
+}
+
+// Q8_0 counterpart of iq3s_decode_half: blocks 4 HF .. 4 HF + 3 of the unit
+template <int HF>
+__device__ __forceinline__ void q8_decode_half(uint32_t u0, uint32_t u1, int t, UnitHalf &A) {
+    uint32_t wa[4], wb[4];
+#define QW_HALF_SUB(I)                                                            \
+    A.da[I] = q8_sub_h<4 * HF + I>(u0 + 8 * t, u0, wa);                           \
+    A.db[I] = q8_sub_h<4 * HF + I>(u1 + 8 * t, u1, wb);                           \
+    A.a0[I][0] = wa[0]; A.a0[I][1] = wb[0]; A.a0[I][2] = wa[1]; A.a0[I][3] = wb[1]; \
+    A.a1[I][0] = wa[2]; A.a1[I][1] = wb[2]; A.a1[I][2] = wa[3]; A.a1[I][3] = wb[3];
+    QW_HALF_SUB(0)
+    QW_HALF_SUB(1)
+    QW_HALF_SUB(2)
+    QW_HALF_SUB(3)
+#undef QW_HALF_SUB
 }
 
 __host__ __device__ constexpr int unit_bytes(int GF) { return GF == 21 ? 110 : 272; }

@@ -65,7 +65,7 @@ def test_qmv_gg_bit_exact_vs_canonical_oracle(gpu, qtype, N, K, B):
 
 # config 1: ragged batched matvec shapes (reduced row counts for lm_head so the oracle finishes in seconds)
 @pytest.mark.parametrize("qtype,N,K", [(21, 5120, 2048), (21, 2048, 4096), (8, 4096, 2048), (21, 12352, 2048)])
-@pytest.mark.parametrize("B", [1, 4, 8, 16, 64])
+@pytest.mark.parametrize("B", [1, 4, 8, 16, 17, 40, 64])
 def test_qmv_mma_close_to_fp64_and_rows_independent_of_batch(gpu, qtype, N, K, B):
     rng = np.random.default_rng(1)
     W = synth.quant_rows(rng, qtype, N, K)
