@@ -17,7 +17,8 @@
 //             bytes apart, so the eight rows a warp instruction touches fall into eight different groups of four banks.
 //             IQ3X: one contiguous 34 KB run.
 //   down      stage = 128 rows of the down matrix over all of K = 512 (contiguous: one 1-D bulk copy).
-// and a ring of activation slots (the tokens of an item's columns for its gate/up pieces, its H planes for the down pieces),
+// and a ring of eight activation rows (the tokens of an item's columns for its gate/up pieces, the two planes of its H for the down
+// pieces): an item takes as many rows as it has columns, so the next item's rows are usually copied while this one's are read;
 // filled by the producer with bulk copies.  Consumer warp w = (row group r = w % 8, K half kh = w / 8) owns 16 MMA rows of
 // the stage and one of the stage's two super-blocks; the accumulators live across the stages of a piece, and the two K
 // halves of a row group meet once per piece through shared memory (always low half + high half: the order never depends on
@@ -56,7 +57,6 @@ struct FfnCfg {
     static constexpr int STG = FMT ? 2 : 3;
     static constexpr int SLOT = FMT ? IQ3X_STAGE : 128 * FFN_PITCH;   // 30720 also holds an IQ3_S down tile of 128 x 220 bytes
     static constexpr int TAB = FMT ? 256 : 65536;                      // IQ3_S: the codebook; IQ3X: the multiply-add constants of the 16 scale values
-    static constexpr int NACT = 1;
     static constexpr int OFF_TAB = 128;
     static constexpr int OFF_PRE = OFF_TAB + TAB;                      // uint32 pre[FFN_MAXG] of the selection record, then 2 x FFN_RECS item records of 32 bytes
     static constexpr int OFF_REC = OFF_PRE + FFN_MAXG * 4;
@@ -330,7 +330,7 @@ template <bool PROBE, int FMT>
 __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(const __grid_constant__ CUtensorMap mG, const __grid_constant__ CUtensorMap mU,
                                                            const __grid_constant__ CUtensorMap mSG, const __grid_constant__ CUtensorMap mSU, const FfnP p) {
     using C = FfnCfg<FMT>;
-    constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT, NACT = C::NACT;
+    constexpr int FFN_STG = C::STG, FFN_SLOT = C::SLOT;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = (uint64_t *)smem;
     uint64_t *full = bars, *empty = bars + FFN_STG, *tab_bar = bars + 2 * FFN_STG, *actfull = tab_bar + 1, *actfree = actfull + 2;
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
     constexpr uint32_t D = FFN_D, I = FFN_I, rbI = I / 256 * 110;
     constexpr uint32_t xpitch = D * 2 + 64, hpitch = I * 2 + 64, act_slot = 8 * xpitch;  // a slot holds 8 token rows or 16 H rows
     static_assert(act_slot >= 16 * hpitch, "activation slot");
-    uint8_t *act0 = smem + C::OFF_XS, *stage0 = act0 + NACT * act_slot;
+    uint8_t *act0 = smem + C::OFF_XS, *stage0 = act0 + act_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     constexpr uint32_t KP = D / 512, GT = I / 64, DT = D / 128, KU = I / 256;
 
@@ -412,15 +412,28 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                 mbar_expect_tx(&full[s], bytes);
                 return slot0 + s * FFN_SLOT;
             };
-            auto act_for = [&](uint32_t bytes) {  // the same for the activation slots (tokens of an item, or its H)
-                const uint32_t s = k % NACT, n = k / NACT;
+            // The activation slot is a ring of eight rows (tokens of an item, or the two planes of its H): item k takes the next
+            // ncols rows, so the rows of the next item are usually on their way while the consumers still read this one's.  Two
+            // barrier pairs alternate by item; item k - 2 must have been released, item k - 1 too when the rows would overlap or
+            // the layout changes (fresh).  Returns the first row's index.
+            uint32_t rowbase = 0, prev_n = 8;
+            auto act_for = [&](uint32_t ncols, uint32_t bytes, bool fresh) {
+                const uint32_t s = k & 1, n = k >> 1;
                 if (n >= 1 && ok && !mbar_wait(&actfree[s], (n - 1) & 1)) {
                     ok = false;
                     set_status(p.status, ST_MBAR_TIMEOUT | 7);
                 }
+                if (k >= 1 && (fresh || prev_n + ncols > 8) && ok && !mbar_wait(&actfree[(k - 1) & 1], ((k - 1) >> 1) & 1)) {
+                    ok = false;
+                    set_status(p.status, ST_MBAR_TIMEOUT | 7);
+                }
+                if (fresh) rowbase = 0;
                 fence_proxy_async();
                 mbar_expect_tx(&actfull[s], bytes);
-                return act0 + s * act_slot;
+                const uint32_t r0 = rowbase;
+                rowbase = (rowbase + ncols) & 7;
+                prev_n = ncols;
+                return r0;
             };
             struct Src {
                 const CUtensorMap *tg, *tu;
@@ -462,17 +475,18 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                         tma_box_2d(dst + 64 * FFN_PITCH, sc.tu, xc, yr, &full[j % FFN_STG]);
                     }
                     if (sw && kp == 0) {  // the tokens of a new item's columns, requested after its first weights (the longer wait)
-                        uint8_t *xd = act_for(it.ncols * D * 2);
+                        const uint32_t r0 = act_for(it.ncols, it.ncols * D * 2, false);
                         for (uint32_t c = 0; c < it.ncols; c++) {
                             uint32_t tok, rank;
                             ffn_entry(ms, it, topk, c, tok, rank);
-                            bulk_g2s(xd + c * xpitch, p.x + (size_t)tok * D, D * 2, &actfull[k % NACT]);
+                            bulk_g2s(act0 + ((r0 + c) & 7) * xpitch, p.x + (size_t)tok * D, D * 2, &actfull[k & 1]);
                         }
                         k++;
                     }
                 }
             }
             cur = 0xffffffffu;
+            bool first_dn = true;  // the H rows have another pitch than the tokens: the ring starts over, once the last tokens are released
             for (uint32_t bi = b_lo; bi < b_hi; bi++, j++) {
                 const uint32_t w = bi / DT, dt = bi - w * DT;
                 const bool sw = w != cur;
@@ -497,11 +511,13 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                             }
                     }
                     asm volatile("fence.proxy.async.global;" ::: "memory");  // the H rows were written by ordinary stores; the copy engine reads them
-                    uint8_t *hd = act_for(2 * it.ncols * I * 2);
+                    const uint32_t r0 = act_for(it.ncols, 2 * it.ncols * I * 2, first_dn);
+                    first_dn = false;
                     const __half *Hw = p.H + (size_t)w * 16 * I;
                     for (uint32_t c = 0; c < it.ncols; c++) {
-                        bulk_g2s(hd + c * hpitch, Hw + (size_t)c * I, I * 2, &actfull[k % NACT]);
-                        bulk_g2s(hd + (8 + c) * hpitch, Hw + (size_t)(8 + c) * I, I * 2, &actfull[k % NACT]);
+                        const uint32_t rw = (r0 + c) & 7;
+                        bulk_g2s(act0 + rw * hpitch, Hw + (size_t)c * I, I * 2, &actfull[k & 1]);
+                        bulk_g2s(act0 + (8 + rw) * hpitch, Hw + (size_t)(8 + c) * I, I * 2, &actfull[k & 1]);
                     }
                     k++;
                 }
@@ -529,17 +545,20 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
             j++;
         };
         // activation slot of the next item: waits for its copy, returns its shared address
-        auto act_wait = [&]() {
-            const uint32_t s = k % NACT;
-            if (ok && !mbar_wait(&actfull[s], (k / NACT) & 1)) {
+        // activation rows of the next item (see the producer's act_for): waits for their copy; returns the address of column g's row
+        uint32_t rowbase = 0;
+        auto act_wait = [&](uint32_t ncols, uint32_t pitch) {
+            if (ok && !mbar_wait(&actfull[k & 1], (k >> 1) & 1)) {
                 ok = false;
                 if (lane == 0) set_status(p.status, ST_MBAR_TIMEOUT | 10);
             }
-            return smem_u32(act0) + s * act_slot;
+            const uint32_t a = smem_u32(act0) + ((rowbase + g) & 7) * pitch;
+            rowbase = (rowbase + ncols) & 7;
+            return a;
         };
-        auto act_release = [&]() {  // this warp is done with the current item's slot
+        auto act_release = [&]() {  // this warp is done with the current item's rows
             __syncwarp();
-            if (lane == 0) mbar_arrive(&actfree[k % NACT]);
+            if (lane == 0) mbar_arrive(&actfree[k & 1]);
             k++;
         };
         auto probe_read = [&](uint32_t st, uint32_t bytes, uint32_t &sink) {
@@ -572,7 +591,7 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                 cur = w;
                 ncols = rec_a[w].ncols;
                 have = (uint32_t)g < ncols ? 1u : 0u;
-                xb0 = act_wait() + g * xpitch + t * 16;
+                xb0 = act_wait(ncols, xpitch) + t * 16;
             }
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (uint32_t kp = 0; kp < KP; kp++) {
@@ -618,6 +637,7 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
         if (cur != 0xffffffffu) act_release();
         // ---- down pieces: tiles of 128 output rows; MMA row g is tile row 16 r + 2 g, row g + 8 the next one
         cur = 0xffffffffu;
+        rowbase = 0;
         uint32_t hb0 = 0, oo[2] = {0xffffffffu, 0xffffffffu};  // element offsets of the output rows of columns 2t and 2t + 1
         for (uint32_t bi = b_lo; bi < b_hi; bi++) {
             const uint32_t w = bi / DT, dt = bi - w * DT;
@@ -635,7 +655,7 @@ __global__ void __launch_bounds__(FFN_THREADS, FfnCfg<FMT>::PER_SM) moe_ffn_k(co
                         oo[c] = (tok * (topk + 1) + rank) * D;
                     }
                 }
-                hb0 = act_wait() + g * hpitch + t * 16;
+                hb0 = act_wait(it.ncols, hpitch) + t * 16;
             }
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t st = wait_full();
@@ -744,8 +764,8 @@ static cudaError_t launch_moe_ffn(const QwLaunch &L) {
     QW_CHECK_ARG(D == FFN_D && I == FFN_I && topk < MOE_MAXK && E <= 512);
     const uint32_t rbD = D / 256 * 110, rbI = I / 256 * 110;
     const size_t act = (size_t)8 * (D * 2 + 64);  // an activation slot: 8 token rows, or 16 H rows
-    const size_t smem = x4 ? FfnCfg<1>::OFF_XS + FfnCfg<1>::NACT * act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT
-                           : FfnCfg<0>::OFF_XS + FfnCfg<0>::NACT * act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
+    const size_t smem = x4 ? FfnCfg<1>::OFF_XS + act + (size_t)FfnCfg<1>::STG * FfnCfg<1>::SLOT
+                           : FfnCfg<0>::OFF_XS + act + (size_t)FfnCfg<0>::STG * FfnCfg<0>::SLOT;
     const int per_sm = x4 ? FfnCfg<1>::PER_SM : FfnCfg<0>::PER_SM;
     QW_CHECK_ARG((smem + 1024) * per_sm <= 227 * 1024 + 1024 && 128 * rbI <= FfnCfg<0>::SLOT && (128 * rbI) % 16 == 0);
     const bool shared = L.def("SHARED", 1) != 0;
