@@ -107,18 +107,21 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
 // The MoE-combine form for D = 2048 (the step's hot case: it sits between the expert FFN and the next projection, and
 // nothing else can run beside it).  A token is served by a cluster of 8 blocks of 256 threads, one column per thread: the
 // twelve loads of a column are independent, the blocks are small enough to be resident next to the FFN's blocks while they
-// wait for it, and the sum of squares of the row meets through the cluster's shared memory (the eight partial sums are
-// added in block order by every block, so the result does not depend on timing).  grid (8 nb) x 256, cluster 8.
+// wait for it, and the sum of squares of the row meets through the cluster's shared memory (every block pushes its partial sum to
+// all eight; they are added in block order by every block, so the result does not depend on timing).  grid (8 nb) x 256, cluster 8.
 __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_k(float *h, const float *w, __half *x, const moe_sel *ms, const float *Pg,
                                                                                     uint32_t topk, const unsigned *flags, const unsigned *seq,
                                                                                     uint32_t nranks, unsigned *rowcnt, unsigned *status) {
     constexpr uint32_t D = 2048;
     namespace cg = cooperative_groups;
     __shared__ float tmp[8];
-    __shared__ float part;
+    __shared__ float parts[8];  // the eight blocks' partial sums of squares, each written here by its owner
     cg::cluster_group cl = cg::this_cluster();
     const uint32_t t = blockIdx.x >> 3, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, d = (blockIdx.x & 7) * 256 + tid;
     pdl_launch();
+    // first cluster barrier, split: arrive now, wait just before the partial sums are pushed (by then every block of the cluster
+    // has long arrived, i.e. has started and owns its shared memory)
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     const float wd = w[d];  // the norm weights are static
     if (rowcnt) {
         // One GPU, the one-launch expert FFN before us: do not wait for its whole launch, only for this token's topk + 1 output rows
@@ -155,18 +158,18 @@ __global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(256) cmb_rmsnorm_cl_
     const float ss = warp_sum(v * v);
     if (lane == 0) tmp[warp] = ss;
     __syncthreads();
-    if (tid == 0) {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid < 8) {  // thread r pushes this block's partial sum into block r's array: after the one cluster barrier nobody touches another block's memory
         float b = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; i++) b += tmp[i];
-        part = b;
+        *cl.map_shared_rank(&parts[blockIdx.x & 7], tid) = b;
     }
     cl.sync();
     float tot = 0.f;
 #pragma unroll
-    for (unsigned r = 0; r < 8; r++) tot += *cl.map_shared_rank(&part, r);
+    for (unsigned r = 0; r < 8; r++) tot += parts[r];
     x[(size_t)t * D + d] = __float2half_rn(v * rsqrtf(tot / D + 1e-6f) * wd);
-    cl.sync();  // nobody leaves while its partial sum may still be read
     if (rowcnt) {
         pdl_wait();  // this kernel's completion must imply the FFN's: later kernels rely on the chain of completed predecessors
         if ((blockIdx.x & 7) == 0 && tid <= topk) rowcnt[t * (topk + 1) + tid] = 0;  // cleared for the next layer's launch
