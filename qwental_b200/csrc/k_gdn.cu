@@ -29,24 +29,30 @@ struct dn_epi_args {
 // grid (ceil((C + 2 HV)/256), nb) x 256
 __global__ void __launch_bounds__(256) dn_epi_k(const __half *proj, const float *cw, float *pool, const float *An, const float *dtb, __half *cv,
                                                float *la, float *be, const int32_t *sids, dn_epi_args a, uint32_t C, uint32_t HV) {
-    pdl_sync();
+    pdl_launch();
     const uint32_t g = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     const __half *pr = proj + (size_t)t * a.proj_stride;
     if (g < C) {
+        // the conv state (last written by this kernel one step ago), the static weights and the slot table are read before the wait
+        // for the projection (see gdn_fstep_k for why those writers have completed)
         float *st = pool + ((size_t)sids[t] * a.nlayers + a.layer) * 3 * C;
-        const float s0 = st[g], s1 = st[C + g], s2 = st[2 * C + g], s3 = __half2float(pr[g]);
+        const float s0 = st[g], s1 = st[C + g], s2 = st[2 * C + g];
         const float4 w = *(const float4 *)(cw + 4 * (size_t)g);
+        pdl_wait();
+        const float s3 = __half2float(pr[g]);
         const float y = w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
         cv[(size_t)t * C + g] = __float2half_rn(y / (1.0f + expf(-y)));
         st[g] = s1;
         st[C + g] = s2;
         st[2 * C + g] = s3;
     } else if (g < C + HV) {
+        pdl_wait();
         const uint32_t j = g - C;
         const float xa = __half2float(pr[C + HV * 128 + j]) + dtb[j];
         const float sp = xa > 20.0f ? xa : logf(1.0f + expf(xa));
         la[t * HV + j] = An[j] * sp;
     } else if (g < C + 2 * HV) {
+        pdl_wait();
         const uint32_t j = g - C - HV;
         be[t * HV + j] = 1.0f / (1.0f + expf(-__half2float(pr[C + HV * 128 + HV + j])));
     }
@@ -87,17 +93,21 @@ __global__ void __launch_bounds__(512, 2) gdn_fstep_k(const __half *cv, const fl
     constexpr int DK = 128, DV = 128;
     __shared__ float red[8];
     __shared__ float4 part[2][16][32];  // [S^T k | S^T q][row group][column quad]
-    pdl_sync();
+    pdl_launch();
     const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c4 = tid & 31, rq = tid >> 5, lane = tid & 31, warp = tid >> 5;
     const uint32_t hk = TILED ? hv % HK : hv / (HV / HK);
     const uint32_t C = 2 * HK * DK + HV * DV;
     const __half *row = cv + (size_t)t * C;
     float4 *S = (float4 *)(pool + (((size_t)sids[t] * a.nlayers + a.layer) * HV + hv) * DK * DV) + c4;
 
-    // state rows into registers (issued first: the long-latency part)
+    // State rows into registers: the long-latency part, requested before the wait for the previous kernel.  The state of this
+    // (slot, layer, head) was last written by this kernel one step ago and the slot table at the step's start, both many
+    // launches back: a launch cannot begin before every block of its predecessor has started, and between those writers and this
+    // launch lie kernels that fill the whole device, so they have completed.
     float4 s[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) s[i] = S[(size_t)(8 * rq + i) * (DV / 4)];
+    pdl_wait();  // q, k, v, z, the decay and beta are the previous kernels' output
 
     // q / k L2 normalisation, by every warp for itself (no block barrier): lane l squares elements 4l .. 4l+3, one butterfly
     // gives the head's sum of squares; then the warp's own eight rows 8 rq .. 8 rq + 7 are scaled

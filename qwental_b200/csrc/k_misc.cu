@@ -43,10 +43,14 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
                                                      const float *Pg, uint32_t topk, const unsigned *flags, const unsigned *seq, uint32_t nranks,
                                                      unsigned *status) {
     __shared__ float tmp[32];
-    pdl_sync();
+    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
+    pdl_launch();
+    float wv[4];  // the norm weights are static: read before the wait for the previous kernel
+#pragma unroll
+    for (int it = 0; it < 4; it++) wv[it] = tid + it * nth < D ? w[tid + it * nth] : 0.f;
+    pdl_wait();
     // rows of Pg (MODE 2) or of delta (MODE 1) may have been stored by other ranks: wait until every rank has published
     if (nranks > 1) ep_wait(flags, seq, nranks, status);
-    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nth = blockDim.x;
     float *hr = h + (size_t)t * D;
     float wk[MOE_MAXK];
     if (MODE == 2) {
@@ -100,7 +104,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_k(float *h, const __half *de
 #pragma unroll
     for (int it = 0; it < 4; it++) {
         const uint32_t d = tid + it * nth;
-        if (d < D) x[(size_t)t * D + d] = __float2half_rn(vv[it] * r * w[d]);
+        if (d < D) x[(size_t)t * D + d] = __float2half_rn(vv[it] * r * wv[it]);
     }
     for (uint32_t d = tid + 4 * nth; d < D; d += nth) x[(size_t)t * D + d] = __float2half_rn(hr[d] * r * w[d]);
 }
