@@ -19,7 +19,8 @@ __device__ __forceinline__ void set_status(unsigned *status, unsigned code) {
 
 // ---- programmatic dependent launch: pdl_launch() lets the next kernel of the stream begin launching, pdl_wait() blocks
 // until the previous kernel has completed and its writes are visible (a no-op when the launch carried no such
-// attribute).  Rules of this library: nothing that another kernel reads or writes is touched before pdl_wait(); and data that
+// attribute).  Rules of this library: nothing that another kernel of the same step reads or writes is touched before pdl_wait()
+// (static weights and tables may be; so may per-slot state whose last writer ran one step earlier -- gdn_fstep_k says why); and data that
 // an earlier kernel of the step produced is never read through the non-coherent path (__ldg / ld.global.nc) -- a kernel that
 // started early is already running while its predecessor writes, so that path may serve stale lines.  Such loads use
 // __ldcg (L2) or plain loads; __ldg is kept for weights and tables only.
