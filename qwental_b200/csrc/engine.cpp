@@ -322,7 +322,15 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
     std::vector<std::pair<const char *, long>> ad = {{"QH", c.qh}, {"KVH", c.kvh}, {"HD", c.hd}};
     ok = ok && compile(e, "qsa_prep", "qsa_prep", ad, &e->k_prep) && compile(e, "qsa_attn", "qsa_attn", ad, &e->k_attn) &&
          compile(e, "qsa_merge", "qsa_merge", ad, &e->k_merge);
-    std::vector<std::pair<const char *, long>> gd = {{"HK", c.hk}, {"HV", c.hv}, {"DK", 128}, {"DV", 128}, {"GDN_TILED", 1}};
+    const char *fm = getenv("QW_MOE_FFN");
+    // moe_ffn spreads the pieces of the chosen experts over all blocks, so it is the default at every rank count;
+    // QW_MOE_FFN=split keeps the two-launch family, QW_MOE_FFN=fused runs moe_ffn on the raw IQ3_S blocks
+    e->ffn_fused = e->D == 2048 && e->I == 512 && !(fm && !strcmp(fm, "split"));
+    e->ffn_iq3x = e->ffn_fused && !(fm && !strcmp(fm, "fused"));
+    // EARLY: the GDN kernels read their per-slot state before they wait for the previous kernel.  Allowed when every layer ends in a
+    // launch that fills all SMs (moe_ffn) and there are at least two layers: see gdn_fstep_k.
+    std::vector<std::pair<const char *, long>> gd = {{"HK", c.hk}, {"HV", c.hv}, {"DK", 128}, {"DV", 128}, {"GDN_TILED", 1},
+                                                      {"EARLY", e->ffn_fused && e->L >= 2 ? 1 : 0}};
     ok = ok && compile(e, "dn_epi", "dn_epi", gd, &e->k_epi) && compile(e, "gdn_fstep", "gdn_fstep", gd, &e->k_gdn);
     // expert-parallel: the shared expert is computed by rank 0 only, so the exchange can sum whole buffers
     std::vector<std::pair<const char *, long>> md = {{"E", e->E}, {"EL", e->EL}, {"D", D}, {"I", e->I}, {"TOPK", e->TOPK},
@@ -332,11 +340,6 @@ extern "C" qw_engine *qw_engine_open_synth(qw_gpu *g, const qw_model_cfg *cfg) {
          compile(e, "moe_route", "moe_route", md, &e->k_route) &&
          compile(e, "add_rmsnorm", "cmb_add_rmsnorm", {{"CMB", 1}, {"TOPK", e->TOPK}}, &e->k_norm_cmb);
     {
-        const char *fm = getenv("QW_MOE_FFN");
-        // moe_ffn spreads the pieces of the chosen experts over all blocks, so it is the default at every rank count;
-        // QW_MOE_FFN=split keeps the two-launch family, QW_MOE_FFN=fused runs moe_ffn on the raw IQ3_S blocks
-        e->ffn_fused = e->D == 2048 && e->I == 512 && !(fm && !strcmp(fm, "split"));
-        e->ffn_iq3x = e->ffn_fused && !(fm && !strcmp(fm, "fused"));
         if (ok && e->ffn_fused) {
             auto mf = md;
             mf.push_back({"IQ3X", e->ffn_iq3x ? 1 : 0});

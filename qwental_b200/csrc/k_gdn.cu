@@ -28,17 +28,18 @@ struct dn_epi_args {
 // 6 = la fp32 [nb][HV], 7 = beta fp32 [nb][HV], 8 = slot ids int32 [nb], 9 = dn_epi_args.
 // grid (ceil((C + 2 HV)/256), nb) x 256
 __global__ void __launch_bounds__(256) dn_epi_k(const __half *proj, const float *cw, float *pool, const float *An, const float *dtb, __half *cv,
-                                               float *la, float *be, const int32_t *sids, dn_epi_args a, uint32_t C, uint32_t HV) {
+                                               float *la, float *be, const int32_t *sids, dn_epi_args a, uint32_t C, uint32_t HV, bool early) {
     pdl_launch();
+    if (!early) pdl_wait();
     const uint32_t g = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
     const __half *pr = proj + (size_t)t * a.proj_stride;
     if (g < C) {
-        // the conv state (last written by this kernel one step ago), the static weights and the slot table are read before the wait
-        // for the projection (see gdn_fstep_k for why those writers have completed)
+        // early: the conv state (last written by this kernel one step ago), the static weights and the slot table are read before
+        // the wait for the projection (see gdn_fstep_k for when that is allowed)
         float *st = pool + ((size_t)sids[t] * a.nlayers + a.layer) * 3 * C;
         const float s0 = st[g], s1 = st[C + g], s2 = st[2 * C + g];
         const float4 w = *(const float4 *)(cw + 4 * (size_t)g);
-        pdl_wait();
+        if (early) pdl_wait();
         const float s3 = __half2float(pr[g]);
         const float y = w.x * s0 + w.y * s1 + w.z * s2 + w.w * s3;
         cv[(size_t)t * C + g] = __float2half_rn(y / (1.0f + expf(-y)));
@@ -46,13 +47,13 @@ __global__ void __launch_bounds__(256) dn_epi_k(const __half *proj, const float 
         st[C + g] = s2;
         st[2 * C + g] = s3;
     } else if (g < C + HV) {
-        pdl_wait();
+        if (early) pdl_wait();
         const uint32_t j = g - C;
         const float xa = __half2float(pr[C + HV * 128 + j]) + dtb[j];
         const float sp = xa > 20.0f ? xa : logf(1.0f + expf(xa));
         la[t * HV + j] = An[j] * sp;
     } else if (g < C + 2 * HV) {
-        pdl_wait();
+        if (early) pdl_wait();
         const uint32_t j = g - C - HV;
         be[t * HV + j] = 1.0f / (1.0f + expf(-__half2float(pr[C + HV * 128 + HV + j])));
     }
@@ -70,7 +71,7 @@ static cudaError_t launch_dn_epi(const QwLaunch &L) {
                  L.avail(8) >= (size_t)a.nb * 4);
     qw_launch(dn_epi_k, dim3((C + 2 * HV + 255) / 256, a.nb), 256, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3),
                                                                         L.buf<float>(4), L.buf<__half>(5), L.buf<float>(6), L.buf<float>(7),
-                                                                        L.buf<int32_t>(8), a, C, HV);
+                                                                        L.buf<int32_t>(8), a, C, HV, L.def("EARLY", 0) != 0);
     return cudaGetLastError();
 }
 QW_FAMILY(dn_epi, launch_dn_epi, 256)
@@ -89,25 +90,28 @@ struct gdn_args {
 // defined 1 also 9 = o out fp16 [nb][HV*DV] (the un-normalised output, for tests).  grid (HV, nb) x 512
 template <bool TILED>
 __global__ void __launch_bounds__(512, 2) gdn_fstep_k(const __half *cv, const float *la, const float *beta, float *pool, const __half *z,
-                                                  const float *nw, __half *gy, const int32_t *sids, __half *oo, gdn_args a, uint32_t HK, uint32_t HV) {
+                                                  const float *nw, __half *gy, const int32_t *sids, __half *oo, gdn_args a, uint32_t HK, uint32_t HV,
+                                                  bool early) {
     constexpr int DK = 128, DV = 128;
     __shared__ float red[8];
     __shared__ float4 part[2][16][32];  // [S^T k | S^T q][row group][column quad]
     pdl_launch();
+    if (!early) pdl_wait();
     const uint32_t hv = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, c4 = tid & 31, rq = tid >> 5, lane = tid & 31, warp = tid >> 5;
     const uint32_t hk = TILED ? hv % HK : hv / (HV / HK);
     const uint32_t C = 2 * HK * DK + HV * DV;
     const __half *row = cv + (size_t)t * C;
     float4 *S = (float4 *)(pool + (((size_t)sids[t] * a.nlayers + a.layer) * HV + hv) * DK * DV) + c4;
 
-    // State rows into registers: the long-latency part, requested before the wait for the previous kernel.  The state of this
-    // (slot, layer, head) was last written by this kernel one step ago and the slot table at the step's start, both many
-    // launches back: a launch cannot begin before every block of its predecessor has started, and between those writers and this
-    // launch lie kernels that fill the whole device, so they have completed.
+    // State rows into registers: the long-latency part.  With EARLY defined 1 they are requested before the wait for the previous
+    // kernel.  The state of this (slot, layer, head) was last written by this kernel one step ago and the slot table at the step's
+    // start.  A launch cannot begin before every block of its predecessor has started; the host defines EARLY only when at least two
+    // launches that fill every SM (moe_ffn: as many blocks as fit the device) lie between those writers and this launch -- the later
+    // one cannot have started all its blocks before the earlier one has left, and that one has waited for everything before it.
     float4 s[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) s[i] = S[(size_t)(8 * rq + i) * (DV / 4)];
-    pdl_wait();  // q, k, v, z, the decay and beta are the previous kernels' output
+    if (early) pdl_wait();  // q, k, v, z, the decay and beta are the previous kernels' output
 
     // q / k L2 normalisation, by every warp for itself (no block barrier): lane l squares elements 4l .. 4l+3, one butterfly
     // gives the head's sum of squares; then the warp's own eight rows 8 rq .. 8 rq + 7 are scaled
@@ -196,14 +200,15 @@ static cudaError_t launch_gdn_fstep(const QwLaunch &L) {
                  L.avail(7) >= (size_t)a.nb * 4);
     QW_CHECK_ARG(L.tx == 512);
     const dim3 grid(HV, a.nb);
+    const bool early = L.def("EARLY", 0) != 0;
     __half *oo = L.def("O_OUT", 0) ? L.buf<__half>(9) : nullptr;
     if (L.def("O_OUT", 0)) QW_CHECK_ARG(oo && L.avail(9) >= (size_t)a.nb * HV * DV * 2);
     if (tiled)
         qw_launch(gdn_fstep_k<true>, grid, 512, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
-                                                     L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV);
+                                                     L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV, early);
     else
         qw_launch(gdn_fstep_k<false>, grid, 512, 0, L.stream, L.buf<__half>(0), L.buf<float>(1), L.buf<float>(2), L.buf<float>(3), L.buf<__half>(4),
-                                                      L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV);
+                                                      L.buf<float>(5), L.buf<__half>(6), L.buf<int32_t>(7), oo, a, HK, HV, early);
     return cudaGetLastError();
 }
 QW_FAMILY(gdn_fstep, launch_gdn_fstep, 512)
